@@ -1,0 +1,173 @@
+/*
+ * ommx_b200.h - C ABI of libommx_b200.so: OMMX paged decode attention over a quantized KV
+ * cache, hand-written for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces three pieces of Youngmin17/open_ommx_serve behind their own Python
+ * entry points; each function below names the reference interface it stands in for (paths are
+ * relative to the reference checkout).  Every pointer is a plain device pointer unless the
+ * comment says "host".  Every function returns 0 on success or a negative OMMX_E_* code when
+ * an argument is rejected on the host before anything is launched; ommx_b200_last_error()
+ * then gives the reason as text.  Kernels never trap: out-of-range page or group-slot ids, a
+ * non-finite value handed to the packer or a wait that ran out are reported through the
+ * optional `status` word (device int32, OR-ed OMMX_ST_* bits) and the access is skipped.
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ */
+#ifndef OMMX_B200_H_
+#define OMMX_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OMMX_B200_ABI_VERSION 1
+
+/* host-side argument errors (return values) */
+#define OMMX_E_ARG          (-1)   /* null pointer, bad size, misaligned plane */
+#define OMMX_E_UNSUPPORTED  (-2)   /* a geometry/recipe this build does not implement */
+#define OMMX_E_CUDA         (-3)   /* a CUDA runtime call failed (launch, attribute) */
+
+/* device status bits (OR-ed into *status) */
+#define OMMX_ST_BAD_PAGE     1     /* page id outside [0, num_pages) - access skipped */
+#define OMMX_ST_BAD_GROUP    2     /* group slot outside [0, num_group_slots) - access skipped */
+#define OMMX_ST_NONFINITE    4     /* packer saw NaN/Inf in K or V */
+#define OMMX_ST_TIMEOUT      8     /* a bounded wait inside a kernel ran out */
+#define OMMX_ST_BAD_LENGTH  16     /* b_seq_len needs more groups per split than a CTA can index */
+
+/* element types of q / o / k,v inputs */
+#define OMMX_DT_F32   0
+#define OMMX_DT_BF16  1
+#define OMMX_DT_F16   2
+
+/* how k_scale / v_scale are stored */
+#define OMMX_SCALE_INT8_EXP 0      /* int8 power-of-two exponent (the serving default) */
+#define OMMX_SCALE_BF16     1
+#define OMMX_SCALE_F32      2
+
+/*
+ * The packed KV planes (reference ABI: ommx_gpu_serve/attention/paged_decode.py:2856-2887,
+ * produced by ommx_gpu_serve/attention/pack.py:628-655).  All planes are contiguous.
+ *   k_base / v_main   u8  [num_pages, page_size, n_kv_heads, head_dim/4]   2-bit codes
+ *   v_scale           i8|bf16|f32 [num_pages, page_size, n_kv_heads, head_dim/32]
+ *   v_zp              bf16|f32    [num_pages, page_size, n_kv_heads, head_dim/32]
+ *   k_scale           i8|bf16|f32 [num_group_slots, n_kv_heads, head_dim]
+ *   k_zp, k_mapscale, k_mapcenter  bf16|f32 [num_group_slots, n_kv_heads, head_dim]
+ *   k_obmp            u8  [num_group_slots, n_kv_heads, head_dim, 4]   bit p = token p (LSB first)
+ *   k_oval            u8  [num_group_slots, n_kv_heads, head_dim, ceil(k/2)]  FP4 nibbles,
+ *                                                       nibble s = s-th outlier in token order
+ * A "group" is 32 consecutive tokens; a K vector is (head, channel, group), a V vector is
+ * (token, head, 32 consecutive channels).
+ */
+typedef struct ommx_kv_planes {
+    int32_t n_kv_heads;
+    int32_t head_dim;
+    int32_t page_size;            /* tokens per page: 8, 16 or 32 */
+    int32_t num_pages;
+    int32_t num_group_slots;
+    int32_t outliers_per_vector;  /* k: FP4 outliers per 32-token K vector (0..8) */
+    int32_t kv_outlier_map;       /* 1: outliers use k_mapscale/k_mapcenter, 0: share scale/zp */
+    int32_t scale_kind;           /* OMMX_SCALE_* (zp and map planes are f32 iff OMMX_SCALE_F32) */
+    void *k_base, *k_scale, *k_zp, *k_obmp, *k_oval, *k_mapscale, *k_mapcenter;
+    void *v_main, *v_scale, *v_zp;
+} ommx_kv_planes;
+
+/*
+ * KV quantize + pack ("store").  Replaces ommx_pack_kv_canonical_block
+ * (ommx_gpu_serve/attention/pack.py:293-655) and the per-slot plane copies its callers do
+ * afterwards (attention/kv_store.py:594-610, attention/kv_pool.py:619-635): the block of
+ * num_tokens = 32*n rows is quantized and written straight into the destination pages and
+ * group slots.  Output is bit-identical to the reference packer run on CPU.
+ */
+typedef struct ommx_pack_args {
+    const void *k, *v;            /* [num_tokens, n_kv_heads, head_dim], last dim contiguous */
+    int32_t in_dtype;             /* OMMX_DT_* */
+    int32_t num_tokens;           /* multiple of 32 and of page_size */
+    int64_t stride_token, stride_head;   /* in elements, shared by k and v */
+    const int32_t *dst_pages;     /* [num_tokens/page_size] destination page ids, NULL = 0,1,2.. */
+    const int32_t *dst_groups;    /* [num_tokens/32] destination group slots,  NULL = 0,1,2.. */
+    int32_t outlier_select;       /* 1 = signed (top ceil(k/2) + bottom floor(k/2)), 0 = abs */
+    int32_t use_pow2;             /* 1 = snap scales to powers of two */
+    ommx_kv_planes planes;        /* destination */
+    int32_t *status;              /* optional */
+} ommx_pack_args;
+
+int ommx_b200_pack_kv(const ommx_pack_args *args, void *stream);
+
+/*
+ * Paged decode attention.  Replaces ommx_paged_decode_attention_canonical
+ * (ommx_gpu_serve/attention/paged_decode.py:2768-3549): stage 1 = _canonical_splitkv_stage1
+ * (:1255), stage 2 = _canonical_lse_merge with the bf16 sink/recent rows fused in (:2366).
+ * Writes o / lse in place.  attn_logits is the caller's split workspace
+ * f32 [batch, n_q_heads, num_kv_splits+1, head_dim+1] (lane head_dim = log-sum-exp).
+ * b_seq_len holds PACKED token counts; split s covers tokens [s*per, min((s+1)*per, seq)) with
+ * per = ceil(ceil(seq/num_kv_splits)/32)*32, exactly as the reference.
+ */
+typedef struct ommx_decode_args {
+    const void *q;                /* bf16 [batch, n_q_heads, head_dim] */
+    int32_t q_dtype;              /* OMMX_DT_BF16 */
+    int32_t batch, n_q_heads;
+    int64_t q_stride_b, q_stride_h;
+    ommx_kv_planes planes;
+    const void *k_tail, *v_tail;  /* bf16 [batch, T_tail_max, n_kv_heads, head_dim] */
+    int64_t tail_stride_b, tail_stride_t, tail_stride_h;
+    const int32_t *b_tail_len;    /* [batch] valid residual rows (0 allowed) */
+    const int32_t *b_seq_len;     /* [batch] packed tokens */
+    const void *req_to_token;     /* [batch, >=pages]  page table */
+    const void *req_to_group;     /* [batch, >=groups] group-slot table */
+    int32_t table_is_int64;       /* 0: int32 tables, 1: int64 */
+    int64_t r2t_stride_b, r2g_stride_b;
+    void *o;                      /* [batch, n_q_heads, head_dim] */
+    int32_t o_dtype;              /* OMMX_DT_F32 or OMMX_DT_BF16 */
+    int64_t o_stride_b, o_stride_h;
+    float *lse;                   /* [batch, n_q_heads] */
+    int64_t lse_stride_b;
+    float *attn_logits;
+    int64_t al_stride_b, al_stride_h, al_stride_s;
+    int32_t num_kv_splits;
+    int32_t max_seq_len;          /* upper bound of b_seq_len (sizes nothing on device; checked) */
+    int32_t max_tail_len;
+    int32_t seg_group_base;       /* first group of the attended segment (0 = whole sequence) */
+    int32_t packed_start_offset;  /* must be 0 */
+    float sm_scale, logit_cap;
+    int32_t *status;              /* optional */
+} ommx_decode_args;
+
+int ommx_b200_decode(const ommx_decode_args *args, void *stream);          /* stage 1 + stage 2 */
+int ommx_b200_decode_stage1(const ommx_decode_args *args, void *stream);   /* splits -> attn_logits */
+int ommx_b200_decode_stage2(const ommx_decode_args *args, void *stream);   /* attn_logits + tail -> o,lse */
+
+/*
+ * Split count this library prefers for (max context, batch, local kv heads) on the current
+ * device.  Replaces _auto_num_kv_splits (attention/paged_decode.py:409-461), which callers
+ * use to size attn_logits once.
+ */
+int ommx_b200_auto_num_kv_splits(int32_t max_seq_len, int32_t batch, int32_t n_kv_heads);
+/* Smallest split count ommx_b200_decode accepts for a context of max_seq_len packed tokens. */
+int ommx_b200_min_num_kv_splits(int32_t max_seq_len, int32_t page_size);
+
+/*
+ * Merge P partial softmax states over disjoint KV segments.  Replaces merge_attention_states
+ * (attention/paged_decode.py:3556-3624, kernel :2650-2690).
+ * o_parts f32 [P, R, D], lse_parts f32 [P, R], valid_lens int32 [R] or NULL (all P valid).
+ */
+int ommx_b200_merge_states(const float *o_parts, const float *lse_parts, const int32_t *valid_lens,
+                           int32_t P, int32_t R, int32_t D, float *o, float *lse, void *stream);
+
+/* Host-side twins of the two table-driven decisions inside the packer (no GPU needed):
+ * round_half_even(log2(x)) for x > 0, and the FP4 E2M1 code of m
+ * (reference: attention/pack.py:459-463, attention/codec.py:45-65). */
+int ommx_b200_host_pow2_exponent(float x);
+int ommx_b200_host_fp4_encode(float m);
+
+int ommx_b200_abi_version(void);
+const char *ommx_b200_last_error(void);   /* thread-local text of the last negative return */
+/* Kernels launched by this library since load (or since the last reset), for launch evidence;
+ * mirrors launch_stats()/reset_launch_stats() (attention/paged_decode.py:2728-2739). */
+int64_t ommx_b200_launch_count(void);
+void ommx_b200_reset_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMMX_B200_H_ */

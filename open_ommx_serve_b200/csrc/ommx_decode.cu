@@ -1,0 +1,893 @@
+// Paged decode attention over OMMX-quantized KV planes for sm_100a: split-KV stage 1, stage 2
+// (log-sum-exp combine with the bf16 sink/recent rows fused in) and the partial-state merge.
+//
+// Stage 1 replaces _canonical_splitkv_stage1 (ommx_gpu_serve/attention/paged_decode.py:1255-2284
+// of the reference).  One CTA serves one (split, sequence) pair and ALL local kv heads of its
+// token range, so every page row it touches is a full contiguous line:
+//
+//   producer warp   streams whole pages / group-slot planes into a 4-stage shared-memory ring
+//                   with 1-D bulk async copies (cp.async.bulk + mbarrier transaction counts);
+//                   page ids and group slots of the split are prefetched into shared memory once.
+//   8 consumer warps each own one (group, kv head) unit per stage and keep a private online-
+//                   softmax state.  Per unit:
+//     phase A (lane = 4 channels): walk the outlier bitmask with clz, decode the FP4 nibble,
+//                   and write the outlier value, expressed in code units, into a per-warp
+//                   bf16 tile [token][channel-slot]; clear that lane's 2-bit base code in place.
+//     phase B (mma lanes): 2-bit codes -> bf16 with one LOP3 per pair (magic exponent, value
+//                   128 + code*4^p), per-channel power-of-two scale folded into q, QK^T on
+//                   mma.sync m16n8k16 (GQA rows padded to 16); the outlier tile is a second B
+//                   operand read with ldmatrix; one extra tile row carries zp/scale and one
+//                   carries -128, so q.zp and the magic offset come out of the same MMAs.
+//                   Online softmax with quad shuffles, P in bf16, V dequantized in bf16x2
+//                   (code*vs+vz, as the reference) and P.V on the same MMA shape.
+//
+// Numerics follow the reference kernel's rounding points: q*sm_scale rounded to bf16, exact
+// code*2^e products, fp32 accumulation, P rounded to bf16, V dequantized to bf16.  Two points
+// differ at the bf16-rounding level only: the outlier enters as one bf16 value in code units
+// instead of a bf16 delta, and q.zp uses the bf16 q*sm_scale instead of fp32 q.
+#include "ommx_common.cuh"
+
+namespace ommx {
+
+constexpr int HD = 128;                 // head_dim this build serves
+constexpr int NCW = 8;                  // consumer warps
+constexpr int S1_THREADS = (NCW + 1) * 32;
+constexpr int NSTAGES = 4;
+constexpr int DT_STRIDE = 272;          // bytes per outlier-tile row (256 data + 16 pad)
+constexpr int DT_ROWS = 34;             // 32 tokens + zp row + (-128) row
+constexpr int DT_BYTES = DT_ROWS * DT_STRIDE;
+constexpr int MAX_SPLIT_GROUPS = 512;   // groups one CTA can index (16K tokens per split)
+constexpr int MAX_SPLIT_PAGES = 2048;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;
+
+struct S1Params {
+    const __nv_bfloat16 *q;
+    int64_t q_sb, q_sh;
+    int32_t B, Hq, H, gqa;
+    const uint8_t *k_base, *v_main, *v_scale, *v_zp, *k_scale, *k_zp, *k_ms, *k_mc, *k_obmp, *k_oval;
+    int32_t ps, ppg, num_pages, num_slots, k_out, nb, use_map;
+    const int32_t *b_seq_len;
+    const void *r2t, *r2g;
+    int32_t tbl64;
+    int64_t r2t_sb, r2g_sb;
+    float *al;
+    int64_t al_sb, al_sh, al_ss;
+    int32_t S, seg_group_base;
+    float sm_scale, logit_cap;
+    int32_t *status;
+    // shared-memory layout of one group block (bytes)
+    int32_t GS, gb_bytes, stage_bytes;
+    int32_t o_vm, o_vs, o_vz, o_ks, o_kz, o_ms, o_mc, o_bm, o_ov;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and the caller raises OMMX_ST_TIMEOUT) instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 64) __nanosleep(32);
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// position class of channel-in-word index i (0..7): the 2-bit field sits at bit 2*pc of its half
+// when the LOP3 extracts it, so the extracted bf16 is 128 + code * 4^pc.
+__device__ __forceinline__ int pos_class(int i) { return i < 3 ? i : (i < 6 ? i - 3 : i - 6); }
+
+__device__ __forceinline__ int64_t load_index(const void *tbl, int is64, int64_t i) {
+    return is64 ? reinterpret_cast<const int64_t *>(tbl)[i] : (int64_t) reinterpret_cast<const int32_t *>(tbl)[i];
+}
+
+// Extract the 8 bf16x2 registers of one 32-bit code word: register i holds (code i, code i+8)
+// as bf16 values 128 + code * 4^pos_class(i).
+__device__ __forceinline__ void codes_to_bf16x2(uint32_t w, uint32_t (&r)[8]) {
+    const uint32_t M = 0x43004300u;
+    r[0] = lop3_and_or(w, 0x00030003u, M);
+    r[1] = lop3_and_or(w, 0x000C000Cu, M);
+    r[2] = lop3_and_or(w, 0x00300030u, M);
+    uint32_t t = w >> 6;
+    r[3] = lop3_and_or(t, 0x00030003u, M);
+    r[4] = lop3_and_or(t, 0x000C000Cu, M);
+    r[5] = lop3_and_or(t, 0x00300030u, M);
+    t = w >> 12;
+    r[6] = lop3_and_or(t, 0x00030003u, M);
+    r[7] = lop3_and_or(t, 0x000C000Cu, M);
+}
+
+// =================================================================================================
+// Stage 1
+// =================================================================================================
+__global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int split = blockIdx.x, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- split range (same rounding as the reference, paged_decode.py:1428-1432) ----
+    const int seq = p.b_seq_len[b];
+    if (seq <= 0) return;
+    const int per = (((seq + p.S - 1) / p.S) + 31) / 32 * 32;
+    const int t0 = split * per;
+    const int t1 = min(t0 + per, seq);
+    if (t1 <= t0) return;
+    const int ntok = t1 - t0;
+    int ngroups = (ntok + 31) / 32;
+    if (ngroups > MAX_SPLIT_GROUPS) {                 // host sizing should prevent this
+        if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_LENGTH);
+        return;
+    }
+    const int H = p.H, GS = p.GS;
+    const int n_iters = (ngroups + GS - 1) / GS;
+
+    // ---- shared memory carve-up ----
+    uint8_t *s_stage = smem;                                            // NSTAGES * stage_bytes
+    uint8_t *s_tiles = s_stage + NSTAGES * p.stage_bytes;               // NCW * DT_BYTES
+    int32_t *s_slots = reinterpret_cast<int32_t *>(s_tiles + NCW * DT_BYTES);
+    int32_t *s_pages = s_slots + MAX_SPLIT_GROUPS;
+    float *s_lut = reinterpret_cast<float *>(s_pages + MAX_SPLIT_PAGES);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[NSTAGES], empty[NSTAGES]
+    int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * NSTAGES);
+    const uint32_t bar_full = smem_u32(s_bar), bar_empty = smem_u32(s_bar + NSTAGES);
+
+    // ---- prologue: tables, LUT, barriers ----
+    {
+        const int g0 = p.seg_group_base + t0 / 32;                      // first logical group
+        for (int i = threadIdx.x; i < ngroups; i += S1_THREADS) {
+            int64_t s = load_index(p.r2g, p.tbl64, (int64_t)b * p.r2g_sb + g0 + i);
+            if (s < 0 || s >= p.num_slots) { or_status(p.status, OMMX_ST_BAD_GROUP); s = 0; }
+            s_slots[i] = (int)s;
+        }
+        const int npages = (ntok + p.ps - 1) / p.ps;
+        const int64_t pg0 = ((int64_t)g0 * 32) / p.ps;
+        for (int i = threadIdx.x; i < npages; i += S1_THREADS) {
+            int64_t pg = load_index(p.r2t, p.tbl64, (int64_t)b * p.r2t_sb + pg0 + i);
+            if (pg < 0 || pg >= p.num_pages) { or_status(p.status, OMMX_ST_BAD_PAGE); pg = 0; }
+            s_pages[i] = (int)pg;
+        }
+        if (threadIdx.x < 16) {
+            const int c = threadIdx.x;
+            const int mi = ((c >> 1) & 3) * 2 + (c & 1);                // exp*2 + mant
+            const float mags[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+            s_lut[c] = (c & 8) ? -mags[mi] : mags[mi];
+        }
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < NSTAGES; ++s) {
+                mbar_init(bar_full + 8 * s, 1);
+                mbar_init(bar_empty + 8 * s, NCW);
+            }
+            *s_abort = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    __syncthreads();
+
+    if (warp == NCW) {
+        // =========================== producer warp ===========================
+        const int cpg = 4 * p.ppg + 6;                                  // copies per group
+        const uint32_t page_b = (uint32_t)p.ps * H;                     // rows*heads per page
+        for (int it = 0; it < n_iters; ++it) {
+            const int s = it % NSTAGES;
+            const uint32_t ph = (it / NSTAGES) & 1;
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1)) {
+                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+                break;
+            }
+            const int ng = min(GS, ngroups - it * GS);
+            // transaction bytes of this stage
+            uint32_t total = 0;
+            for (int gi = 0; gi < ng; ++gi) {
+                const int lg = it * GS + gi;
+                const int vp = min(p.ppg, (ntok - 32 * lg + p.ps - 1) / p.ps);
+                total += (uint32_t)vp * page_b * (32 + 32 + 4 + 8) + (uint32_t)H * (128 + 256);
+                if (p.k_out > 0) total += (uint32_t)H * (512 + 128 * p.nb) + (p.use_map ? (uint32_t)H * 512 : 0u);
+            }
+            if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
+            __syncwarp();
+            const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
+            for (int c = lane; c < ng * cpg; c += 32) {
+                const int gi = c / cpg, ci = c - gi * cpg;
+                const int lg = it * GS + gi;
+                const uint32_t gb = sbase + (uint32_t)gi * p.gb_bytes;
+                if (ci < 4 * p.ppg) {
+                    const int pg = ci >> 2, plane = ci & 3;
+                    if (32 * lg + pg * p.ps >= ntok) continue;          // page beyond the live length
+                    const int64_t page = s_pages[lg * p.ppg + pg];
+                    const uint32_t rows = (uint32_t)pg * page_b;        // (token,head) rows before this page
+                    if (plane == 0) bulk_g2s(gb + rows * 32, p.k_base + page * page_b * 32, page_b * 32, bar_full + 8 * s);
+                    else if (plane == 1) bulk_g2s(gb + p.o_vm + rows * 32, p.v_main + page * page_b * 32, page_b * 32, bar_full + 8 * s);
+                    else if (plane == 2) bulk_g2s(gb + p.o_vs + rows * 4, p.v_scale + page * page_b * 4, page_b * 4, bar_full + 8 * s);
+                    else bulk_g2s(gb + p.o_vz + rows * 8, p.v_zp + page * page_b * 8, page_b * 8, bar_full + 8 * s);
+                } else {
+                    const int gp = ci - 4 * p.ppg;
+                    const int64_t slot = s_slots[lg];
+                    const int64_t e = slot * H;                         // (slot, head) rows before
+                    if (gp == 0) bulk_g2s(gb + p.o_ks, p.k_scale + e * 128, H * 128, bar_full + 8 * s);
+                    else if (gp == 1) bulk_g2s(gb + p.o_kz, p.k_zp + e * 256, H * 256, bar_full + 8 * s);
+                    else if (p.k_out > 0) {
+                        if (gp == 2) { if (p.use_map) bulk_g2s(gb + p.o_ms, p.k_ms + e * 256, H * 256, bar_full + 8 * s); }
+                        else if (gp == 3) { if (p.use_map) bulk_g2s(gb + p.o_mc, p.k_mc + e * 256, H * 256, bar_full + 8 * s); }
+                        else if (gp == 4) bulk_g2s(gb + p.o_bm, p.k_obmp + e * 512, H * 512, bar_full + 8 * s);
+                        else bulk_g2s(gb + p.o_ov, p.k_oval + e * 128 * p.nb, H * 128 * p.nb, bar_full + 8 * s);
+                    }
+                }
+            }
+        }
+    } else {
+        // =========================== consumer warps ===========================
+        const int g = lane >> 2, j = lane & 3;
+        const int h = warp % H, gsel = warp / H;
+        const int TS = H * 32;                                          // bytes per token row (all heads)
+        uint8_t *tile = s_tiles + warp * DT_BYTES;
+        const uint32_t tile_s = smem_u32(tile);
+        const float LOG2E = 1.4426950408889634f;
+
+        // ---- per-thread constants ----
+        // q_static: bf16(q*sm_scale) * 2^-1 * 4^-pc for this lane's head row and 32 channel slots
+        uint32_t QS[16];
+        {
+            const bool row_ok = g < p.gqa;
+            const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (row_ok ? g : 0)) * p.q_sh;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const int wi = r >> 3, i = r & 7;
+                const int ch = 32 * j + 16 * wi + i;
+                const float f = 0.5f / (float)(1 << (2 * pos_class(i)));
+                float lo = 0.f, hi = 0.f;
+                if (row_ok) {
+                    lo = bf16_round_f32(__bfloat162float(qrow[ch]) * p.sm_scale) * f;
+                    hi = bf16_round_f32(__bfloat162float(qrow[ch + 8]) * p.sm_scale) * f;
+                }
+                QS[r] = pack_bf16x2(lo, hi);
+            }
+        }
+        // phase-A constants: this lane owns channels 4*lane + c
+        uint32_t pa_col[4];       // byte offset of the channel's column inside an outlier-tile row
+        float pa_f[4];            // 4^pc of the channel's slot
+        uint32_t pa_clr[4];       // mask clearing the channel's 2-bit code inside its 32-bit word
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int d = 4 * lane + c;
+            const int jj = d >> 5, wi = (d >> 4) & 1, i = d & 7, hi = (d >> 3) & 1;
+            pa_col[c] = 2u * (16 * (4 * wi + (i >> 1)) + 8 * (i & 1) + 2 * jj + hi);
+            pa_f[c] = (float)(1 << (2 * pos_class(i)));
+            pa_clr[c] = ~(3u << (8 * (lane & 3) + 2 * c));
+        }
+        // outlier tile: row 33 = -128 in every column (never rewritten); clear the rest once
+        for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(tile)[i] = 0u;
+        __syncwarp();
+        for (int i = lane; i < 64; i += 32) reinterpret_cast<uint32_t *>(tile + 33 * DT_STRIDE)[i] = 0xC300C300u;
+        __syncwarp();
+
+        // ---- online softmax state (row g of the MMA tile) ----
+        float m_run = -INFINITY, l_run = 0.f;
+        float acc[16][4];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+
+        bool aborted = false;
+        for (int it = 0; it < n_iters; ++it) {
+            const int s = it % NSTAGES;
+            const uint32_t ph = (it / NSTAGES) & 1;
+            if (!mbar_wait(bar_full + 8 * s, ph)) {
+                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+                aborted = true;
+                break;
+            }
+            const int lg = it * GS + gsel;                               // local group of this warp
+            if (lg < ngroups) {
+                uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
+                uint8_t *kb = gb + h * 32;                               // + token*TS
+                const uint8_t *vm = gb + p.o_vm + h * 32;
+                const uint8_t *vsc = gb + p.o_vs + h * 4;                // + token*H*4
+                const uint8_t *vzp = gb + p.o_vz + h * 8;                // + token*H*8
+                const uint8_t *ksc = gb + p.o_ks + h * 128;
+                const uint8_t *kzp = gb + p.o_kz + h * 256;
+
+                // ======================= phase A: outliers + zp row =======================
+                {
+                    // clear token rows 0..31 (256 data bytes each)
+#pragma unroll
+                    for (int r2 = 0; r2 < 16; ++r2)
+                        *reinterpret_cast<uint4 *>(tile + (2 * r2 + (lane >> 4)) * DT_STRIDE + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
+                    __syncwarp();
+                    const uint32_t e4 = *reinterpret_cast<const uint32_t *>(ksc + 4 * lane);
+                    const uint2 z4 = *reinterpret_cast<const uint2 *>(kzp + 8 * lane);
+                    uint2 ms4 = make_uint2(0, 0), mc4 = make_uint2(0, 0);
+                    uint4 bm4 = make_uint4(0, 0, 0, 0);
+                    uint32_t st[4] = {0, 0, 0, 0};
+                    if (p.k_out > 0) {
+                        if (p.use_map) {
+                            ms4 = *reinterpret_cast<const uint2 *>(gb + p.o_ms + h * 256 + 8 * lane);
+                            mc4 = *reinterpret_cast<const uint2 *>(gb + p.o_mc + h * 256 + 8 * lane);
+                        }
+                        bm4 = *reinterpret_cast<const uint4 *>(gb + p.o_bm + h * 512 + 16 * lane);
+                        const uint32_t *ov = reinterpret_cast<const uint32_t *>(gb + p.o_ov + h * 128 * p.nb + 4 * p.nb * lane);
+                        if (p.nb == 3) {
+                            const uint32_t w0 = ov[0], w1 = ov[1], w2 = ov[2];
+                            st[0] = w0 & 0xFFFFFFu;
+                            st[1] = (w0 >> 24) | ((w1 & 0xFFFFu) << 8);
+                            st[2] = (w1 >> 16) | ((w2 & 0xFFu) << 16);
+                            st[3] = w2 >> 8;
+                        } else if (p.nb == 4) {
+                            st[0] = ov[0]; st[1] = ov[1]; st[2] = ov[2]; st[3] = ov[3];
+                        } else if (p.nb == 2) {
+                            const uint32_t w0 = ov[0], w1 = ov[1];
+                            st[0] = w0 & 0xFFFFu; st[1] = w0 >> 16; st[2] = w1 & 0xFFFFu; st[3] = w1 >> 16;
+                        } else {
+                            const uint32_t w0 = ov[0];
+                            st[0] = w0 & 0xFFu; st[1] = (w0 >> 8) & 0xFFu; st[2] = (w0 >> 16) & 0xFFu; st[3] = w0 >> 24;
+                        }
+                    }
+                    const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
+                    uint8_t *kbw = kb + (lane & ~3);                     // the word holding this lane's code byte
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int e = (int)(int8_t)(e4 >> (8 * c));
+                        const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
+                        const uint32_t zb = (c & 1) ? ((c & 2 ? z4.y : z4.x) >> 16) : ((c & 2 ? z4.y : z4.x) & 0xFFFFu);
+                        const float zp = bf16_bits_to_f32(zb);
+                        const float fs = inv_s * pa_f[c];
+                        // zp row: zp / scale in slot units (exact power-of-two scaling of a bf16)
+                        *reinterpret_cast<__nv_bfloat16 *>(tile + 32 * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(zp * fs);
+                        if (p.k_out > 0) {
+                            float A, Bc;
+                            if (p.use_map) {
+                                const uint32_t msb = (c & 1) ? ((c & 2 ? ms4.y : ms4.x) >> 16) : ((c & 2 ? ms4.y : ms4.x) & 0xFFFFu);
+                                const uint32_t mcb = (c & 1) ? ((c & 2 ? mc4.y : mc4.x) >> 16) : ((c & 2 ? mc4.y : mc4.x) & 0xFFFFu);
+                                A = __fdividef(fs, bf16_bits_to_f32(msb));
+                                Bc = (bf16_bits_to_f32(mcb) - zp) * fs;
+                            } else {
+                                A = pa_f[c];                              // (lvl*s + zp - zp)/s = lvl
+                                Bc = 0.f;
+                            }
+                            uint32_t bits = bmv[c];
+                            const uint32_t stream = st[c];
+                            int r = __popc(bits) - 1;
+                            while (bits) {
+                                const int pz = 31 - __clz(bits);
+                                bits ^= 1u << pz;
+                                const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
+                                --r;
+                                const float X = fmaf(s_lut[nib], A, Bc);
+                                *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
+                                atomicAnd(reinterpret_cast<unsigned int *>(kbw + pz * TS), pa_clr[c]);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+
+                // ======================= phase B: QK^T =======================
+                uint32_t QQ[16];
+                {
+                    const uint4 ea = *reinterpret_cast<const uint4 *>(ksc + 32 * j);
+                    const uint4 eb = *reinterpret_cast<const uint4 *>(ksc + 32 * j + 16);
+                    const uint32_t E[8] = {ea.x, ea.y, ea.z, ea.w, eb.x, eb.y, eb.z, eb.w};
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int wi = r >> 3, i = r & 7, bsel = i & 3;
+                        const uint32_t sel = (uint32_t)(bsel | (bsel << 4) | ((4 + bsel) << 8) | ((4 + bsel) << 12));
+                        const uint32_t t = __byte_perm(E[4 * wi + (i >> 2)], E[4 * wi + 2 + (i >> 2)], sel);
+                        const uint32_t f = lop3_and_xor(t, 0x00FF00FFu, 0x00800080u) << 7;   // 2^(e+1) pair
+                        QQ[r] = hmul2_bf16(QS[r], f);
+                    }
+                }
+                float C[5][4];
+#pragma unroll
+                for (int nt = 0; nt < 5; ++nt) { C[nt][0] = C[nt][1] = C[nt][2] = C[nt][3] = 0.f; }
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const uint2 kw = *reinterpret_cast<const uint2 *>(kb + (8 * nt + g) * TS + 8 * j);
+                    uint32_t R[8];
+                    codes_to_bf16x2(kw.x, R);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) mma_bf16(C[nt], QQ[2 * kk], 0u, QQ[2 * kk + 1], 0u, R[2 * kk], R[2 * kk + 1]);
+                    codes_to_bf16x2(kw.y, R);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) mma_bf16(C[nt], QQ[8 + 2 * kk], 0u, QQ[8 + 2 * kk + 1], 0u, R[2 * kk], R[2 * kk + 1]);
+                }
+                // outlier tile (+ zp / -128 rows as n-tile 4)
+                {
+                    const int mi = lane >> 3, rr = lane & 7;
+#pragma unroll
+                    for (int nt = 0; nt < 5; ++nt) {
+                        if (nt < 4 && p.k_out == 0) continue;
+                        int row = 8 * nt + rr;
+                        if (row >= DT_ROWS) row -= DT_ROWS;              // rows 34..39 alias rows 0..5 (columns unused)
+#pragma unroll
+                        for (int kp = 0; kp < 4; ++kp) {
+                            const uint32_t addr = tile_s + row * DT_STRIDE + 2 * (16 * (2 * kp + (mi >> 1)) + 8 * (mi & 1));
+                            uint32_t d0, d1, d2, d3;
+                            ldsm_x4(addr, d0, d1, d2, d3);
+                            mma_bf16(C[nt], QQ[4 * kp], 0u, QQ[4 * kp + 1], 0u, d0, d1);
+                            mma_bf16(C[nt], QQ[4 * kp + 2], 0u, QQ[4 * kp + 3], 0u, d2, d3);
+                        }
+                    }
+                }
+                // q.zp - 128*sum(q'') sits in columns 0 and 1 of n-tile 4 (lanes with j == 0)
+                float qzo = C[4][0] + C[4][1];
+                qzo = __shfl_sync(0xFFFFFFFFu, qzo, lane & ~3);
+
+                // ======================= online softmax =======================
+                float x[8];
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) { x[2 * nt] = C[nt][0] + qzo; x[2 * nt + 1] = C[nt][1] + qzo; }
+                if (p.logit_cap > 0.f) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] = p.logit_cap * tanhf(x[i] / p.logit_cap);
+                }
+                const int tok_base = 32 * lg;
+                if (tok_base + 32 > ntok) {
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        if (tok_base + 8 * nt + 2 * j >= ntok) x[2 * nt] = -INFINITY;
+                        if (tok_base + 8 * nt + 2 * j + 1 >= ntok) x[2 * nt + 1] = -INFINITY;
+                    }
+                }
+                float mloc = x[0];
+#pragma unroll
+                for (int i = 1; i < 8; ++i) mloc = fmaxf(mloc, x[i]);
+                mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 1));
+                mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 2));
+                const float m_new = fmaxf(m_run, mloc);
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float corr = fast_exp2((m_run - m_use) * LOG2E);   // m_run = -inf -> 0
+                float psum = 0.f;
+                uint32_t P[4];
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const float p0 = fast_exp2((x[2 * nt] - m_use) * LOG2E);
+                    const float p1 = fast_exp2((x[2 * nt + 1] - m_use) * LOG2E);
+                    psum += p0 + p1;
+                    P[nt] = pack_bf16x2(p0, p1);
+                }
+                l_run = l_run * corr + psum;
+                m_run = m_new;
+                if (__any_sync(0xFFFFFFFFu, corr != 1.0f)) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { acc[i][0] *= corr; acc[i][1] *= corr; }
+                }
+
+                // ======================= P.V =======================
+                // lane (g, j) supplies channel column g of every n-tile: channels 16*g + i, scale group g/2
+#pragma unroll
+                for (int kt = 0; kt < 2; ++kt) {
+                    uint32_t Vr[2][16];
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int ta = 16 * kt + 8 * half + 2 * j, tb = ta + 1;
+                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vm + ta * TS + 4 * g);
+                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vm + tb * TS + 4 * g);
+                        const uint32_t ea = vsc[ta * H * 4 + (g >> 1)], eb2 = vsc[tb * H * 4 + (g >> 1)];
+                        const uint32_t za = *reinterpret_cast<const uint16_t *>(vzp + ta * H * 8 + 2 * (g >> 1));
+                        const uint32_t zb = *reinterpret_cast<const uint16_t *>(vzp + tb * H * 8 + 2 * (g >> 1));
+                        const uint32_t vs2 = (((ea | (eb2 << 16)) ^ 0x00800080u) & 0x00FF00FFu) << 7;   // 2^(e+1) pair
+                        const uint32_t vz2 = za | (zb << 16);
+                        const uint32_t vs_p0 = hmul2_bf16(vs2, 0x3F003F00u);    // * 2^-1
+                        const uint32_t vs_p1 = hmul2_bf16(vs2, 0x3E003E00u);    // * 2^-3
+                        const uint32_t vs_p2 = hmul2_bf16(vs2, 0x3D003D00u);    // * 2^-5
+                        const uint32_t xlo = __byte_perm(wa, wb, 0x5410);       // channels 0..7 of (ta, tb)
+                        const uint32_t xhi = __byte_perm(wa, wb, 0x7632);       // channels 8..15
+                        uint32_t R[8];
+                        const uint32_t K128 = 0x43004300u;
+                        codes_to_bf16x2(xlo, R);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int pc = pos_class(i);
+                            Vr[half][i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
+                        }
+                        codes_to_bf16x2(xhi, R);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int pc = pos_class(i);
+                            Vr[half][8 + i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) mma_bf16(acc[i], P[2 * kt], 0u, P[2 * kt + 1], 0u, Vr[0][i], Vr[1][i]);
+                }
+            }
+            // release the stage (generic-proxy writes into it are ordered before the next bulk copy)
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        }
+
+        // ---- epilogue state hand-off happens after the CTA-wide barrier below ----
+        // park the state in registers; nothing to do here
+        if (aborted) { m_run = -INFINITY; l_run = 0.f; }
+
+        // Wait for every warp (and the producer) before the ring memory is reused as scratch.
+        __syncthreads();
+        float l_tot = l_run;
+        l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 1);
+        l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 2);
+        float *scratch = reinterpret_cast<float *>(s_stage);             // [NCW][32 lanes][34]
+        if (GS > 1) {
+            float *my = scratch + ((size_t)warp * 32 + lane) * 34;
+            if (gsel > 0) {
+                my[0] = m_run; my[1] = l_tot;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { my[2 + 2 * i] = acc[i][0]; my[3 + 2 * i] = acc[i][1]; }
+            }
+        }
+        __syncthreads();
+        if (gsel == 0) {
+            for (int o = 1; o < GS; ++o) {
+                const float *ot = scratch + ((size_t)(o * H + h) * 32 + lane) * 34;
+                const float m2 = ot[0], l2 = ot[1];
+                const float mn = fmaxf(m_run, m2);
+                const float mu = (mn == -INFINITY) ? 0.f : mn;
+                const float c1 = fast_exp2((m_run - mu) * LOG2E), c2 = fast_exp2((m2 - mu) * LOG2E);
+                l_tot = l_tot * c1 + l2 * c2;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    acc[i][0] = acc[i][0] * c1 + ot[2 + 2 * i] * c2;
+                    acc[i][1] = acc[i][1] * c1 + ot[3 + 2 * i] * c2;
+                }
+                m_run = mn;
+            }
+            if (g < p.gqa) {
+                const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+                float *dst = p.al + (int64_t)b * p.al_sb + (int64_t)(h * p.gqa + g) * p.al_sh + (int64_t)split * p.al_ss;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    dst[32 * j + i] = acc[i][0] * inv;                   // column 2j   -> channel 16*(2j) + i
+                    dst[32 * j + 16 + i] = acc[i][1] * inv;              // column 2j+1 -> channel 16*(2j+1) + i
+                }
+                if (j == 0) dst[HD] = l_tot > 0.f ? m_run + logf(l_tot) : -INFINITY;
+            }
+        }
+        return;
+    }
+    // producer falls through to the two CTA-wide barriers of the epilogue
+    __syncthreads();
+    __syncthreads();
+}
+
+// =================================================================================================
+// Stage 2: bf16 sink/recent rows + log-sum-exp combine (reference: paged_decode.py:2366-2500)
+// =================================================================================================
+struct S2Params {
+    const __nv_bfloat16 *q;
+    int64_t q_sb, q_sh;
+    int32_t Hq, gqa, D;
+    const __nv_bfloat16 *k_tail, *v_tail;
+    int64_t t_sb, t_st, t_sh;
+    const int32_t *b_tail_len, *b_seq_len;
+    int32_t max_tail;
+    const float *al;
+    int64_t al_sb, al_sh, al_ss;
+    int32_t S;
+    void *o;
+    int32_t o_bf16;
+    int64_t o_sb, o_sh;
+    float *lse;
+    int64_t lse_sb;
+    float sm_scale, logit_cap;
+};
+
+constexpr int S2_THREADS = 128;
+constexpr int S2_MAX_TAIL = 256;
+
+__global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Params p) {
+    __shared__ float s_q[HD];
+    __shared__ float s_logit[S2_MAX_TAIL];
+    __shared__ float s_red[S2_THREADS / 32];
+    __shared__ float s_acc[S2_THREADS / 32][HD];
+    __shared__ float s_wsum[S2_THREADS / 32];
+    const int hq = blockIdx.x, b = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = hq / p.gqa;
+    const int seq = p.b_seq_len[b];
+    int tail = p.b_tail_len ? p.b_tail_len[b] : 0;
+    tail = max(0, min(tail, min(p.max_tail, S2_MAX_TAIL)));
+    const int D = p.D;                                                   // == HD
+
+    // ---- bf16 residual rows: fp32 attention of this q head ----
+    float t_max = -INFINITY, t_sum = 0.f, o_tail = 0.f;                  // o_tail: channel tid
+    if (tail > 0) {
+        if (tid < D) s_q[tid] = __bfloat162float(p.q[(int64_t)b * p.q_sb + (int64_t)hq * p.q_sh + tid]);
+        __syncthreads();
+        const __nv_bfloat16 *kt = p.k_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
+        for (int r = warp; r < tail; r += S2_THREADS / 32) {
+            const uint2 kv = *reinterpret_cast<const uint2 *>(kt + (int64_t)r * p.t_st + 4 * lane);
+            float d = s_q[4 * lane] * bf16_bits_to_f32(kv.x & 0xFFFFu) + s_q[4 * lane + 1] * bf16_bits_to_f32(kv.x >> 16)
+                    + s_q[4 * lane + 2] * bf16_bits_to_f32(kv.y & 0xFFFFu) + s_q[4 * lane + 3] * bf16_bits_to_f32(kv.y >> 16);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
+            if (lane == 0) {
+                float x = d * p.sm_scale;
+                if (p.logit_cap > 0.f) x = p.logit_cap * tanhf(x / p.logit_cap);
+                s_logit[r] = x;
+            }
+        }
+        __syncthreads();
+        for (int r = 0; r < tail; ++r) t_max = fmaxf(t_max, s_logit[r]);
+        const __nv_bfloat16 *vt = p.v_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
+        for (int r = 0; r < tail; ++r) {
+            const float w = __expf(s_logit[r] - t_max);
+            t_sum += w;
+            if (tid < D) o_tail += w * __bfloat162float(vt[(int64_t)r * p.t_st + tid]);
+        }
+    }
+    const float tail_lse = t_sum > 0.f ? t_max + logf(t_sum) : -INFINITY;
+    if (t_sum > 0.f) o_tail /= t_sum;
+
+    // ---- packed splits: validity recomputed with the stage-1 rounding ----
+    const int per = seq > 0 ? (((seq + p.S - 1) / p.S) + 31) / 32 * 32 : 0;
+    const float *base = p.al + (int64_t)b * p.al_sb + (int64_t)hq * p.al_sh;
+    float mloc = -INFINITY;
+    for (int s = tid; s < p.S; s += S2_THREADS)
+        if (seq > 0 && (int64_t)s * per < seq) mloc = fmaxf(mloc, base[(int64_t)s * p.al_ss + D]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, o));
+    if (lane == 0) s_red[warp] = mloc;
+    __syncthreads();
+    float g_max = tail_lse;
+    for (int w = 0; w < S2_THREADS / 32; ++w) g_max = fmaxf(g_max, s_red[w]);
+    const float g_safe = (g_max == -INFINITY) ? 0.f : g_max;
+
+    // warp w combines splits s = w, w+4, ...; lane owns channels lane, lane+32, lane+64, lane+96
+    // (rows of attn_logits are head_dim+1 floats apart, so only scalar loads are aligned)
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, wsum = 0.f;
+    for (int s = warp; s < p.S; s += S2_THREADS / 32) {
+        if (!(seq > 0 && (int64_t)s * per < seq)) break;
+        const float *row = base + (int64_t)s * p.al_ss;
+        const float w = __expf(row[D] - g_safe);
+        a0 += w * row[lane]; a1 += w * row[lane + 32]; a2 += w * row[lane + 64]; a3 += w * row[lane + 96];
+        wsum += w;
+    }
+    s_acc[warp][lane] = a0; s_acc[warp][lane + 32] = a1;
+    s_acc[warp][lane + 64] = a2; s_acc[warp][lane + 96] = a3;
+    if (lane == 0) s_wsum[warp] = wsum;
+    __syncthreads();
+    if (tid < D) {
+        float acc = 0.f, den = 0.f;
+        for (int w = 0; w < S2_THREADS / 32; ++w) { acc += s_acc[w][tid]; den += s_wsum[w]; }
+        const float tw = t_sum > 0.f ? __expf(tail_lse - g_safe) : 0.f;
+        acc += tw * o_tail;
+        den += tw;
+        const float out = acc / (den > 0.f ? den : 1.f);
+        if (p.o_bf16) reinterpret_cast<__nv_bfloat16 *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = __float2bfloat16_rn(out);
+        else reinterpret_cast<float *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = out;
+        if (tid == 0) p.lse[(int64_t)b * p.lse_sb + hq] = g_max + logf(den);
+    }
+}
+
+// =================================================================================================
+// merge of partial softmax states (reference: paged_decode.py:2650-2690)
+// =================================================================================================
+__global__ void __launch_bounds__(128) merge_states_kernel(const float *o_parts, const float *lse_parts,
+                                                           const int32_t *valid, int P, int R, int D,
+                                                           float *o, float *lse) {
+    const int r = blockIdx.x;
+    int np = P;
+    if (valid) { int v = valid[r]; if (v >= 0) np = min(v, P); }
+    float m = -INFINITY;
+    for (int q = 0; q < np; ++q) m = fmaxf(m, lse_parts[(int64_t)q * R + r]);
+    const float ms = (m == -INFINITY) ? 0.f : m;
+    float den = 0.f;
+    for (int q = 0; q < np; ++q) den += __expf(lse_parts[(int64_t)q * R + r] - ms);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        for (int q = 0; q < np; ++q)
+            acc += __expf(lse_parts[(int64_t)q * R + r] - ms) * o_parts[((int64_t)q * R + r) * D + d];
+        o[(int64_t)r * D + d] = acc / (den > 0.f ? den : 1.f);
+    }
+    if (threadIdx.x == 0) lse[r] = ms + logf(den);
+}
+
+// =================================================================================================
+// host side
+// =================================================================================================
+static int validate_decode(const ommx_decode_args *a) {
+    if (!a) return fail(OMMX_E_ARG, "decode: null args");
+    const ommx_kv_planes &pl = a->planes;
+    if (!a->q || !a->o || !a->lse || !a->attn_logits || !a->b_seq_len)
+        return fail(OMMX_E_ARG, "decode: q/o/lse/attn_logits/b_seq_len must not be null");
+    if (a->q_dtype != OMMX_DT_BF16) return fail(OMMX_E_UNSUPPORTED, "decode: q must be bf16");
+    if (a->o_dtype != OMMX_DT_F32 && a->o_dtype != OMMX_DT_BF16) return fail(OMMX_E_UNSUPPORTED, "decode: o must be f32 or bf16");
+    if (pl.head_dim != HD) return fail(OMMX_E_UNSUPPORTED, "decode: head_dim=%d (this build serves %d)", pl.head_dim, HD);
+    if (pl.n_kv_heads != 1 && pl.n_kv_heads != 2 && pl.n_kv_heads != 4 && pl.n_kv_heads != 8)
+        return fail(OMMX_E_UNSUPPORTED, "decode: n_kv_heads=%d per device must be 1, 2, 4 or 8", pl.n_kv_heads);
+    if (a->batch <= 0 || a->n_q_heads <= 0 || a->n_q_heads % pl.n_kv_heads != 0)
+        return fail(OMMX_E_ARG, "decode: batch=%d n_q_heads=%d n_kv_heads=%d", a->batch, a->n_q_heads, pl.n_kv_heads);
+    if (a->n_q_heads / pl.n_kv_heads > 8)
+        return fail(OMMX_E_UNSUPPORTED, "decode: GQA group of %d query heads per kv head (max 8)", a->n_q_heads / pl.n_kv_heads);
+    if (pl.page_size != 8 && pl.page_size != 16 && pl.page_size != 32)
+        return fail(OMMX_E_UNSUPPORTED, "decode: page_size=%d must be 8, 16 or 32", pl.page_size);
+    if (pl.scale_kind != OMMX_SCALE_INT8_EXP)
+        return fail(OMMX_E_UNSUPPORTED, "decode: only int8 power-of-two scale planes are served (pack with use_pow2)");
+    if (pl.outliers_per_vector < 0 || pl.outliers_per_vector > 8)
+        return fail(OMMX_E_UNSUPPORTED, "decode: outliers_per_vector=%d outside [0,8]", pl.outliers_per_vector);
+    if (a->packed_start_offset != 0) return fail(OMMX_E_UNSUPPORTED, "decode: packed_start_offset must be 0");
+    if (a->seg_group_base < 0) return fail(OMMX_E_ARG, "decode: seg_group_base=%d", a->seg_group_base);
+    if (a->num_kv_splits < 1) return fail(OMMX_E_ARG, "decode: num_kv_splits=%d", a->num_kv_splits);
+    if (a->max_tail_len > S2_MAX_TAIL) return fail(OMMX_E_UNSUPPORTED, "decode: max_tail_len=%d (max %d)", a->max_tail_len, S2_MAX_TAIL);
+    if (a->max_tail_len > 0 && (!a->k_tail || !a->v_tail || !a->b_tail_len))
+        return fail(OMMX_E_ARG, "decode: max_tail_len>0 needs k_tail, v_tail and b_tail_len");
+    if (a->max_seq_len > 0) {
+        if (!a->req_to_token || !a->req_to_group) return fail(OMMX_E_ARG, "decode: page / group tables are null");
+        if (!pl.k_base || !pl.k_scale || !pl.k_zp || !pl.v_main || !pl.v_scale || !pl.v_zp)
+            return fail(OMMX_E_ARG, "decode: a KV plane is null");
+        if (pl.outliers_per_vector > 0 && (!pl.k_obmp || !pl.k_oval))
+            return fail(OMMX_E_ARG, "decode: k>0 needs k_obmp and k_oval");
+        if (pl.outliers_per_vector > 0 && pl.kv_outlier_map && (!pl.k_mapscale || !pl.k_mapcenter))
+            return fail(OMMX_E_ARG, "decode: kv_outlier_map needs k_mapscale and k_mapcenter");
+        const void *pp[] = {pl.k_base, pl.k_scale, pl.k_zp, pl.k_obmp, pl.k_oval, pl.k_mapscale, pl.k_mapcenter,
+                            pl.v_main, pl.v_scale, pl.v_zp};
+        for (const void *x : pp)
+            if (((uintptr_t)x & 15) != 0) return fail(OMMX_E_ARG, "decode: every KV plane must be 16-byte aligned");
+        const int min_s = ommx_b200_min_num_kv_splits(a->max_seq_len, pl.page_size);
+        if (a->num_kv_splits < min_s)
+            return fail(OMMX_E_ARG, "decode: num_kv_splits=%d too small for max_seq_len=%d (need >= %d)",
+                        a->num_kv_splits, a->max_seq_len, min_s);
+    }
+    if (a->al_stride_s < HD + 1) return fail(OMMX_E_ARG, "decode: attn_logits last dim must be head_dim+1");
+    return 0;
+}
+
+static size_t stage1_smem(const S1Params &p) {
+    return (size_t)NSTAGES * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
+           + 2 * NSTAGES * 8 + 16;
+}
+
+static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
+    if (a->max_seq_len <= 0) return 0;                                   // tail-only decode
+    const ommx_kv_planes &pl = a->planes;
+    S1Params p;
+    p.q = (const __nv_bfloat16 *)a->q; p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h;
+    p.B = a->batch; p.Hq = a->n_q_heads; p.H = pl.n_kv_heads; p.gqa = a->n_q_heads / pl.n_kv_heads;
+    p.k_base = (const uint8_t *)pl.k_base; p.v_main = (const uint8_t *)pl.v_main;
+    p.v_scale = (const uint8_t *)pl.v_scale; p.v_zp = (const uint8_t *)pl.v_zp;
+    p.k_scale = (const uint8_t *)pl.k_scale; p.k_zp = (const uint8_t *)pl.k_zp;
+    p.k_ms = (const uint8_t *)pl.k_mapscale; p.k_mc = (const uint8_t *)pl.k_mapcenter;
+    p.k_obmp = (const uint8_t *)pl.k_obmp; p.k_oval = (const uint8_t *)pl.k_oval;
+    p.ps = pl.page_size; p.ppg = 32 / pl.page_size; p.num_pages = pl.num_pages; p.num_slots = pl.num_group_slots;
+    p.k_out = pl.outliers_per_vector; p.nb = (pl.outliers_per_vector + 1) / 2;
+    p.use_map = (pl.kv_outlier_map && pl.outliers_per_vector > 0) ? 1 : 0;
+    p.b_seq_len = a->b_seq_len; p.r2t = a->req_to_token; p.r2g = a->req_to_group; p.tbl64 = a->table_is_int64;
+    p.r2t_sb = a->r2t_stride_b; p.r2g_sb = a->r2g_stride_b;
+    p.al = a->attn_logits; p.al_sb = a->al_stride_b; p.al_sh = a->al_stride_h; p.al_ss = a->al_stride_s;
+    p.S = a->num_kv_splits; p.seg_group_base = a->seg_group_base;
+    p.sm_scale = a->sm_scale; p.logit_cap = a->logit_cap; p.status = a->status;
+    const int H = p.H;
+    p.GS = NCW / H;
+    p.o_vm = H * 1024; p.o_vs = H * 2048; p.o_vz = p.o_vs + H * 128; p.o_ks = p.o_vz + H * 256;
+    p.o_kz = p.o_ks + H * 128; p.o_ms = p.o_kz + H * 256; p.o_mc = p.o_ms + H * 256; p.o_bm = p.o_mc + H * 256;
+    p.o_ov = p.o_bm + H * 512;
+    p.gb_bytes = p.o_ov + H * 128 * (p.nb > 0 ? p.nb : 0);
+    p.gb_bytes = (p.gb_bytes + 127) / 128 * 128;
+    p.stage_bytes = p.GS * p.gb_bytes;
+    const size_t smem = stage1_smem(p);
+    static size_t attr_smem = 0;
+    if (smem > attr_smem) {
+        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_smem = smem;
+    }
+    dim3 grid(a->num_kv_splits, a->batch);
+    decode_stage1_kernel<<<grid, S1_THREADS, smem, st>>>(p);
+    OMMX_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+static int launch_stage2(const ommx_decode_args *a, cudaStream_t st) {
+    const ommx_kv_planes &pl = a->planes;
+    S2Params p;
+    p.q = (const __nv_bfloat16 *)a->q; p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h;
+    p.Hq = a->n_q_heads; p.gqa = a->n_q_heads / pl.n_kv_heads; p.D = pl.head_dim;
+    p.k_tail = (const __nv_bfloat16 *)a->k_tail; p.v_tail = (const __nv_bfloat16 *)a->v_tail;
+    p.t_sb = a->tail_stride_b; p.t_st = a->tail_stride_t; p.t_sh = a->tail_stride_h;
+    p.b_tail_len = a->max_tail_len > 0 ? a->b_tail_len : nullptr; p.b_seq_len = a->b_seq_len;
+    p.max_tail = a->max_tail_len;
+    p.al = a->attn_logits; p.al_sb = a->al_stride_b; p.al_sh = a->al_stride_h; p.al_ss = a->al_stride_s;
+    p.S = a->max_seq_len > 0 ? a->num_kv_splits : 0;
+    p.o = a->o; p.o_bf16 = (a->o_dtype == OMMX_DT_BF16); p.o_sb = a->o_stride_b; p.o_sh = a->o_stride_h;
+    p.lse = a->lse; p.lse_sb = a->lse_stride_b;
+    p.sm_scale = a->sm_scale; p.logit_cap = a->logit_cap;
+    dim3 grid(a->n_q_heads, a->batch);
+    decode_stage2_kernel<<<grid, S2_THREADS, 0, st>>>(p);
+    OMMX_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+}  // namespace ommx
+
+extern "C" int ommx_b200_min_num_kv_splits(int32_t max_seq_len, int32_t page_size) {
+    using namespace ommx;
+    if (max_seq_len <= 0) return 1;
+    int ppg = page_size > 0 && page_size <= 32 ? 32 / page_size : 1;
+    int max_groups = MAX_SPLIT_GROUPS;
+    if (max_groups * ppg > MAX_SPLIT_PAGES) max_groups = MAX_SPLIT_PAGES / ppg;
+    const int groups = (max_seq_len + 31) / 32;
+    return (groups + max_groups - 1) / max_groups;
+}
+
+extern "C" int ommx_b200_auto_num_kv_splits(int32_t max_seq_len, int32_t batch, int32_t n_kv_heads) {
+    (void)n_kv_heads;                       // one CTA serves all local kv heads of its token range
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sm_count = n;
+        else
+            sm_count = 148;
+    }
+    const int groups = max(1, (max_seq_len + 31) / 32);
+    const int b = max(1, batch);
+    int s = (sm_count + b - 1) / b;                                       // one CTA per SM
+    if (b > 1) s = max(s, min(8, groups / 16));                           // ragged batches: finer grain
+    s = min(s, groups);
+    s = max(s, ommx_b200_min_num_kv_splits(max_seq_len, 16));
+    return max(1, s);
+}
+
+extern "C" int ommx_b200_decode_stage1(const ommx_decode_args *a, void *stream) {
+    int rc = ommx::validate_decode(a);
+    if (rc) return rc;
+    return ommx::launch_stage1(a, (cudaStream_t)stream);
+}
+extern "C" int ommx_b200_decode_stage2(const ommx_decode_args *a, void *stream) {
+    int rc = ommx::validate_decode(a);
+    if (rc) return rc;
+    return ommx::launch_stage2(a, (cudaStream_t)stream);
+}
+extern "C" int ommx_b200_decode(const ommx_decode_args *a, void *stream) {
+    int rc = ommx::validate_decode(a);
+    if (rc) return rc;
+    rc = ommx::launch_stage1(a, (cudaStream_t)stream);
+    if (rc) return rc;
+    return ommx::launch_stage2(a, (cudaStream_t)stream);
+}
+
+extern "C" int ommx_b200_merge_states(const float *o_parts, const float *lse_parts, const int32_t *valid_lens,
+                                      int32_t P, int32_t R, int32_t D, float *o, float *lse, void *stream) {
+    using namespace ommx;
+    if (!o_parts || !lse_parts || !o || !lse) return fail(OMMX_E_ARG, "merge: null pointer");
+    if (P < 0 || R < 0 || D <= 0) return fail(OMMX_E_ARG, "merge: P=%d R=%d D=%d", P, R, D);
+    if (R == 0) return 0;
+    merge_states_kernel<<<R, 128, 0, (cudaStream_t)stream>>>(o_parts, lse_parts, valid_lens, P, R, D, o, lse);
+    OMMX_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return 0;
+}
