@@ -1,0 +1,456 @@
+#!/usr/bin/env python3
+"""Benchmark of the OMMX paged decode-attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step"): one decode step of the attention path through a 32-layer stack,
+Llama-3.1-8B geometry (32 query heads, 8 KV heads, head_dim 128), batch 1, context 64K, OMMX
+recipe k=6 / sink 8 / recent 32, 16-token pages behind a seeded random page table.  Each layer
+has its own packed planes, so one step streams 32 x 69 MB - far more than the 126 MB L2; L2
+is flushed between timed steps as well.  Metric: microseconds per layer (lower is better); the
+achieved HBM GB/s (packed-KV bytes / time) and the other contexts are reported beside it.
+
+  value      device-resident inputs, the whole step replayed as one CUDA graph
+  roofline   stage-1 kernel alone: algorithmic bytes per launch / its average duration
+             (CUDA events on the launching stream), against the measured copy bandwidth
+  e2e        the public Python entry with HOST buffers: per layer the step's q and new K/V
+             rows are copied from pinned memory and the output row is copied back
+  cpu_baseline / --impl reference
+             the reference's CPU path (fake-quantize K and V, then dense attention) restated in
+             oracle/, timed on the host cores on ONE layer of the same context
+
+With N > 1 (torchrun) the 8 KV heads are sharded over the ranks, there is no collective inside
+attention, and one NCCL all-gather per layer reassembles the head outputs (timed inside the step).
+Synthetic data throughout: seeded N(0,1) K/V with 4 K channels per head scaled x12.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS, HQ, HKV, D, PAGE = 32, 32, 8, 128, 16
+SINK, RECENT, K_OUT = 8, 32, 6
+CONTEXTS = (1024, 4096, 16384, 32768, 65536)
+HEADLINE_CTX = 65536
+H200_PUBLISHED_US = {65536: 563.2, 32768: 284.1, 16384: 162.3, 4096: 147.3, 1024: 469.6}
+
+
+def packed_len(ctx):
+    return max(0, (ctx - SINK - RECENT) // 32 * 32)
+
+
+def algorithmic_bytes(ctx, batch, hkv):
+    """Bytes the path must read per layer: every plane handed to the kernel + the bf16 rows."""
+    p = packed_len(ctx)
+    return batch * (p * hkv * 132 + (ctx - p) * hkv * D * 2 * 2)
+
+
+def measured_peak_gbs():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for n, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ───────────────────────────── reference arm / CPU baseline ─────────────────────────────
+
+def cpu_reference_layer(ctx, threads=None, steps=3, warmup=1, seed=42):
+    """The reference's CPU path on one layer: fake-quantize K (outliers kept as FP4) and V, then
+    dense attention of one query row over the result (ommx_fakequant/quant_function.py:152,
+    ommx_fakequant/quant_attention.py:688,957 restated in oracle/ommx_oracle.py)."""
+    import numpy as np
+    import torch
+    from oracle import ommx_oracle as O
+    if threads:
+        torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(HQ, D, generator=g)
+    K = torch.randn(ctx, HKV, D, generator=g)
+    V = torch.randn(ctx, HKV, D, generator=g)
+    for h in range(HKV):
+        idx = torch.randperm(D, generator=torch.Generator().manual_seed(seed + 1 + h))[:4]
+        K[:, h, idx] *= 12.0
+    Kh, Vh = K.permute(1, 0, 2).contiguous(), V.permute(1, 0, 2).contiguous()
+    times, qt, at = [], [], []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        Kq = O.fakequant_group_torch(Kh, is_key=True)
+        Vq = O.fakequant_group_torch(Vh, is_key=False, top=0, bottom=0)
+        t1 = time.perf_counter()
+        Kr = Kq.repeat_interleave(HQ // HKV, dim=0)[None]
+        Vr = Vq.repeat_interleave(HQ // HKV, dim=0)[None]
+        out = torch.nn.functional.scaled_dot_product_attention(q[None, :, None, :], Kr, Vr)
+        t2 = time.perf_counter()
+        if i >= warmup:
+            times.append(t2 - t0)
+            qt.append(t1 - t0)
+            at.append(t2 - t1)
+    # correctness of what was timed: dense fp64 attention over the same fake-quantized cache
+    want, _ = O.attention_fp32(q.numpy(), Kq.permute(1, 0, 2).numpy(), Vq.permute(1, 0, 2).numpy(), D ** -0.5)
+    err = float(np.abs(out[0, :, 0].numpy() - want).max())
+    times.sort()
+    return {"us_per_layer": times[len(times) // 2] * 1e6, "quant_ms": sorted(qt)[len(qt) // 2] * 1e3,
+            "attn_ms": sorted(at)[len(at) // 2] * 1e3, "max_abs_vs_dense": err,
+            "threads": torch.get_num_threads(), "cpu_count": os.cpu_count()}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    ctx = args.ctx
+    res = cpu_reference_layer(ctx, steps=max(1, args.steps), warmup=max(0, args.warmup))
+    us = res["us_per_layer"]
+    line = {
+        "impl": "reference", "metric": "ommx_decode_attn_us_per_layer", "value": us, "unit": "us",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": us * LAYERS / 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"llama3.1-8b geometry, {LAYERS} layers, batch 1, ctx {ctx}, OMMX k=6 sink 8 recent 32",
+                   "ctx": ctx, "batch": 1},
+        "cpu_baseline": {"value": us, "unit": "us", "cores": res["threads"], "kind": "port",
+                         "sample": f"1 of {LAYERS} layers at ctx {ctx}: fake-quantize K+V ({res['quant_ms']:.0f} ms) + "
+                                   f"dense attention ({res['attn_ms']:.1f} ms); host has {res['cpu_count']} cpus",
+                         "max_abs_vs_dense_attention": res["max_abs_vs_dense"]},
+        "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "hbm_gbs": algorithmic_bytes(ctx, 1, HKV) / us / 1e3, "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ───────────────────────────── our arm ─────────────────────────────
+
+class LayerStack:
+    """32 layers of pooled planes for one rank's share of the KV heads."""
+
+    def __init__(self, ctx, batch, hkv, hq, device, seed=42):
+        import torch
+        from open_ommx_serve_b200.attention.pack import alloc_planes, ommx_pack_kv_into
+        self.ctx, self.batch, self.hkv, self.hq, self.device = ctx, batch, hkv, hq, device
+        P = packed_len(ctx)
+        self.max_packed, self.max_tail = P, ctx - P
+        pages_per_seq, groups_per_seq = P // PAGE, P // 32
+        n_groups = batch * groups_per_seq
+        n_pages = n_groups * (32 // PAGE)
+        gen = torch.Generator().manual_seed(4242)
+        pperm = torch.randperm(n_pages, generator=gen).to(torch.int32)
+        gperm = torch.randperm(n_groups, generator=torch.Generator().manual_seed(4243)).to(torch.int32)
+        self.req_to_token = pperm.reshape(batch, pages_per_seq).contiguous().to(device)
+        self.req_to_group = gperm.reshape(batch, groups_per_seq).contiguous().to(device)
+        self.layers = []
+        cg = torch.Generator(device=device)
+        chunk = 16384
+        for layer in range(LAYERS):
+            pl = alloc_planes(n_pages, n_groups, hkv, D, page_size=PAGE, outliers_per_vector=K_OUT,
+                              kv_outlier_map=True, device=device)
+            cg.manual_seed(seed + layer)
+            tails_k = torch.empty(batch, 72, hkv, D, dtype=torch.bfloat16, device=device)
+            tails_v = torch.empty_like(tails_k)
+            for b in range(batch):
+                for t0 in range(0, P, chunk):
+                    n = min(chunk, P - t0)
+                    K = torch.randn(n, hkv, D, generator=cg, device=device)
+                    V = torch.randn(n, hkv, D, generator=cg, device=device)
+                    for h in range(hkv):
+                        idx = torch.randperm(D, generator=torch.Generator().manual_seed(seed + 1 + h))[:4].to(device)
+                        K[:, h, idx] *= 12.0
+                    ommx_pack_kv_into(K.bfloat16(), V.bfloat16(), pl,
+                                      dst_pages=self.req_to_token[b, t0 // PAGE:(t0 + n) // PAGE].contiguous(),
+                                      dst_groups=self.req_to_group[b, t0 // 32:(t0 + n) // 32].contiguous(),
+                                      outliers_per_vector=K_OUT)
+                tails_k[b] = torch.randn(72, hkv, D, generator=cg, device=device).bfloat16()
+                tails_v[b] = torch.randn(72, hkv, D, generator=cg, device=device).bfloat16()
+            q = torch.randn(batch, hq, D, generator=cg, device=device).bfloat16()
+            self.layers.append({"planes": pl, "k_tail": tails_k, "v_tail": tails_v, "q": q})
+        self.b_seq_len = torch.full((batch,), P, dtype=torch.int32, device=device)
+        self.b_tail_len = torch.full((batch,), ctx - P, dtype=torch.int32, device=device)
+        self.o = torch.zeros(LAYERS, batch, hq, D, dtype=torch.float32, device=device)
+        self.lse = torch.zeros(LAYERS, batch, hq, dtype=torch.float32, device=device)
+        self.ws = None
+        self.splits = 0
+
+    def set_context(self, ctx):
+        """Serve a shorter context out of the same planes (a prefix of every sequence)."""
+        from open_ommx_serve_b200.attention.paged_decode import _auto_num_kv_splits
+        import torch
+        P = packed_len(ctx)
+        self.cur_ctx, self.cur_packed, self.cur_tail = ctx, P, ctx - P
+        self.b_seq_len.fill_(P)
+        self.b_tail_len.fill_(ctx - P)
+        self.splits = _auto_num_kv_splits(max(P, 1), self.batch, device=self.device, kv_heads=self.hkv)
+        self.ws = torch.empty(self.batch, self.hq, self.splits + 1, D + 1, dtype=torch.float32, device=self.device)
+
+    def decode_layer(self, i, q=None, stage=0):
+        from open_ommx_serve_b200.attention.paged_decode import ommx_paged_decode_attention_canonical
+        L = self.layers[i]
+        p = L["planes"]
+        ommx_paged_decode_attention_canonical(
+            L["q"] if q is None else q, p["k_base"], p["k_scale"], p["k_zp"], None, p["k_oval"],
+            p["v_main"], p["v_scale"], p["v_zp"], L["k_tail"], L["v_tail"], self.b_tail_len,
+            self.o[i], self.lse[i], self.req_to_token, self.req_to_group, self.b_seq_len,
+            sm_scale=D ** -0.5, page_size=PAGE, k_outliers_per_vector=K_OUT, bitmap_read=True,
+            k_obmp=p["k_obmp"], k_fp4_mapscale=p["k_fp4_mapscale"], k_fp4_mapcenter=p["k_fp4_mapcenter"],
+            kv_outlier_map=True, kv_int8_scale=True, num_kv_splits=self.splits,
+            max_seq_len=self.cur_packed, max_tail_len=self.cur_tail, attn_logits=self.ws, _stage=stage)
+
+
+def timed_graph(fn, steps, warmup, flush, torch):
+    """Capture ``fn`` (one step) in a CUDA graph; return per-step device times in ms."""
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        fn()
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return times
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from open_ommx_serve_b200 import _lib
+    from open_ommx_serve_b200.attention import paged_decode as PD
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    hkv, hq = HKV // world, HQ // world
+    stack = LayerStack(args.ctx, 1, hkv, hq, device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    gathered = torch.zeros(LAYERS, world, 1, hq, D, dtype=torch.float32, device=device) if world > 1 else None
+    lib = _lib.load()
+
+    def step_full():
+        for i in range(LAYERS):
+            stack.decode_layer(i)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[i], stack.o[i])
+
+    def step_stage1():
+        for i in range(LAYERS):
+            stack.decode_layer(i, stage=1)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    per_ctx = {}
+    results = {}
+    contexts = [c for c in CONTEXTS if c <= args.ctx] if args.all_contexts else [args.ctx]
+    sampler = ClockSampler(local_rank)
+    for ctx in contexts:
+        stack.set_context(ctx)
+        head = ctx == args.ctx
+        k_steps = args.steps if head else max(3, min(args.steps, 5))
+        barrier()
+        lib.ommx_b200_reset_launch_count()
+        if head:
+            sampler.__enter__()
+        t_full = timed_graph(step_full, k_steps, args.warmup, flush, torch)
+        barrier()
+        launches_step = int(lib.ommx_b200_launch_count()) // (2 + 0)   # eager warm-up + capture each ran the step once
+        t_s1 = timed_graph(step_stage1, k_steps, args.warmup, flush, torch)
+        barrier()
+        if head:
+            sampler.__exit__()
+        ms_step = reduce_max(sum(t_full) / len(t_full))
+        ms_s1 = reduce_max(sum(t_s1) / len(t_s1))
+        bytes_layer = algorithmic_bytes(ctx, 1, HKV)             # whole job (all ranks)
+        bytes_launch = algorithmic_bytes(ctx, 1, hkv) - (ctx - packed_len(ctx)) * hkv * D * 4   # stage 1 reads planes only
+        per_ctx[str(ctx)] = {
+            "us_per_layer": ms_step * 1e3 / LAYERS, "hbm_gbs": bytes_layer / (ms_step / LAYERS) / 1e6,
+            "stage1_us": ms_s1 * 1e3 / LAYERS, "stage1_gbs": bytes_launch / (ms_s1 / LAYERS) / 1e6,
+            "splits": stack.splits, "bytes_per_layer": bytes_layer,
+            "h200_published_us": H200_PUBLISHED_US.get(ctx)}
+        if head:
+            results = {"ms_step": ms_step, "ms_s1": ms_s1, "bytes_layer": bytes_layer,
+                       "bytes_launch": bytes_launch, "launches_step": launches_step}
+
+    # ---- end to end through the public Python entry with host buffers (no graph) ----
+    stack.set_context(args.ctx)
+    q_host = [torch.randn(1, hq, D).bfloat16().pin_memory() for _ in range(LAYERS)]
+    kv_host = [torch.randn(2, 1, hkv, D).bfloat16().pin_memory() for _ in range(LAYERS)]
+    o_host = torch.empty(LAYERS, 1, hq, D, dtype=torch.float32).pin_memory()
+    q_dev = torch.empty(1, hq, D, dtype=torch.bfloat16, device=device)
+    new_row = stack.cur_tail - 1
+
+    def step_e2e():
+        for i in range(LAYERS):
+            L = stack.layers[i]
+            q_dev.copy_(q_host[i], non_blocking=True)
+            L["k_tail"][:, new_row].copy_(kv_host[i][0], non_blocking=True)      # this step's new K/V row
+            L["v_tail"][:, new_row].copy_(kv_host[i][1], non_blocking=True)
+            stack.decode_layer(i, q=q_dev)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[i], stack.o[i])
+            o_host[i].copy_(stack.o[i], non_blocking=True)
+
+    for _ in range(max(3, args.warmup)):
+        step_e2e()
+    barrier()
+    e2e_times = []
+    for _ in range(args.steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step_e2e()
+        b.record()
+        b.synchronize()
+        e2e_times.append(a.elapsed_time(b))
+    barrier()
+    ms_e2e = reduce_max(sum(e2e_times) / len(e2e_times))
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peak_gbs()
+    us_layer = results["ms_step"] * 1e3 / LAYERS
+    ach = results["bytes_launch"] / (results["ms_s1"] / LAYERS) / 1e6
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_layer(args.ctx, steps=2, warmup=1)
+        cpu = {"value": r["us_per_layer"], "unit": "us", "cores": r["threads"], "kind": "port",
+               "sample": f"1 of {LAYERS} layers at ctx {args.ctx}: fake-quantize K+V ({r['quant_ms']:.0f} ms) + dense "
+                         f"attention ({r['attn_ms']:.1f} ms), median of 2; host has {r['cpu_count']} cpus"}
+    line = {
+        "metric": "ommx_decode_attn_us_per_layer", "value": us_layer, "unit": "us", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": results["ms_step"],
+        "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": us_layer / H200_PUBLISHED_US[args.ctx] if args.ctx in H200_PUBLISHED_US else None,
+        "vs_baseline_note": "value / the reference's published H200-NVL microbench time for the same context (other hardware, page 32)",
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"llama3.1-8b geometry, {LAYERS}-layer stack, batch 1, ctx {args.ctx}, OMMX k=6 sink 8 "
+                               f"recent 32, {PAGE}-token pages, random page table",
+                   "ctx": args.ctx, "batch": 1, "kv_heads_per_gpu": hkv, "splits": per_ctx[str(args.ctx)]["splits"],
+                   "l2": "flushed between timed steps (256 MiB memset); one step reads 32 distinct plane sets",
+                   "timing": "CUDA-graph replay of the whole step, CUDA events per step, mean of K, max over ranks",
+                   "collective": "one NCCL all-gather of [1, Hq/N, D] f32 per layer inside the step" if world > 1 else "none"},
+        "hbm_gbs": results["bytes_layer"] / (results["ms_step"] / LAYERS) / 1e6,
+        "tokens_per_s": 1.0 / (results["ms_step"] * 1e-3),
+        "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "decode_stage1_kernel",
+                     "algorithmic_bytes_per_launch": results["bytes_launch"],
+                     "us_per_launch": results["ms_s1"] * 1e3 / LAYERS,
+                     "frac_of_nominal_8TBs": ach / 8000.0},
+        "cpu_baseline": cpu,
+        "e2e": {"value": ms_e2e * 1e3 / LAYERS, "unit": "us",
+                "h2d_bytes_per_step": LAYERS * (hq * D * 2 + 2 * hkv * D * 2),
+                "d2h_bytes_per_step": LAYERS * hq * D * 4,
+                "note": "public Python entry per layer, pinned host q / new K,V rows in, output row out; no CUDA graph"},
+        "gpu_launches": results["launches_step"] * args.steps,
+        "contexts": per_ctx,
+        "clocks": sampler.summary(),
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--ctx", type=int, default=HEADLINE_CTX)
+    ap.add_argument("--no-all-contexts", dest="all_contexts", action="store_false")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if args.steps > 5:
+            args.steps = 5                      # each step is seconds of CPU work
+        run_reference(args, rank, world)
+        return
+    args.warmup = max(3, args.warmup)
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -138,6 +138,7 @@ def ommx_paged_decode_attention_canonical(
     packed_start_offset: int = 0,
     seg_group_base: int = 0,
     status: Any = None,
+    _stage: int = 0,
 ) -> None:
     """Decode attention of one query row per sequence. Writes ``o`` / ``lse`` in place.
 
@@ -148,7 +149,8 @@ def ommx_paged_decode_attention_canonical(
     ``b_seq_len`` packed token counts.  Pass ``max_seq_len``, ``max_tail_len`` and
     ``attn_logits`` (f32 ``[B,Hq,S+1,D+1]``) to avoid every host sync and allocation, which
     is what CUDA-graph capture needs.  ``status`` (int32 ``[1]``, optional, not in the
-    reference) collects device-side error bits instead of a trap.
+    reference) collects device-side error bits instead of a trap.  ``_stage`` (1 or 2) runs one
+    stage alone, for the benchmark's per-kernel timing.
     """
     lib = _lib.load()
     if not q.is_cuda:
@@ -162,6 +164,8 @@ def ommx_paged_decode_attention_canonical(
         if gt not in (16, 32, 64, 128):
             raise ValueError(f"derived GROUP_TOKENS={gt} (pages={pages} page_size={page_size} "
                              f"n_group_slots={ngroups}) must be in {{16,32,64,128}}")
+        if gt != 32:
+            raise NotImplementedError(f"GROUP_TOKENS={gt}: this build serves 32-token K groups")
     vsc = int(v_scale.shape[-1])
     if vsc:
         gc = (int(v_main.shape[-1]) * 4) // vsc
@@ -268,7 +272,8 @@ def ommx_paged_decode_attention_canonical(
     a.status = None if status is None else status.data_ptr()
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
-        _lib.check(lib.ommx_b200_decode(a, stream), "ommx_b200_decode")
+        entry = (lib.ommx_b200_decode, lib.ommx_b200_decode_stage1, lib.ommx_b200_decode_stage2)[int(_stage)]
+        _lib.check(entry(a, stream), "ommx_b200_decode")
     _LAUNCHES["stage1"] += 1
     if bitmap_read:
         _LAUNCHES["bitmap"] += 1

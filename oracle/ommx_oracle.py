@@ -458,3 +458,54 @@ def fakequant_group(x, *, is_key, group=32, sink_front=8, sink_back=32, top=3, b
     full = x.copy()
     full[:, lo:hi, :] = res
     return full
+
+
+def fakequant_group_torch(x, *, is_key, group=32, sink_front=8, sink_back=32, top=3, bottom=3):
+    """Same arithmetic as :func:`fakequant_group` with multi-threaded torch CPU ops - the form
+    the benchmark times as the CPU baseline (``x`` is a torch fp32 tensor ``[Hkv, T, D]``)."""
+    import torch
+    Hh, T, D = x.shape
+    lo, hi = (sink_front if T > sink_front else 0), (T - sink_back if T > sink_back else T)
+    mid = x[:, lo:hi, :]
+    if mid.shape[1] == 0:
+        return x.clone()
+    w = mid.transpose(1, 2) if is_key else mid
+    L = w.shape[-1]
+    pad = (-L) % group
+    wp = torch.nn.functional.pad(w, (0, pad))
+    valid = torch.ones(L + pad, dtype=torch.bool)
+    valid[L:] = False
+    g = wp.reshape(Hh, wp.shape[1], -1, group)
+    gv = valid.reshape(1, 1, -1, group).expand_as(g)
+    omask = torch.zeros_like(g, dtype=torch.bool)
+    fmin, fmax = torch.finfo(torch.float32).min, torch.finfo(torch.float32).max
+    if is_key and top > 0:
+        thr = torch.topk(torch.where(gv, g, torch.tensor(fmin)), top, dim=-1).values[..., -1:]
+        omask |= g >= thr
+    if is_key and bottom > 0:
+        thr = torch.topk(torch.where(gv, g, torch.tensor(fmax)), bottom, dim=-1, largest=False).values[..., -1:]
+        omask |= g <= thr
+    qm = (~omask) & gv
+    base = g * qm
+    far = (~qm).float() * 1e8
+    mn = (base + far).min(-1, keepdim=True).values
+    mxv = (base - far).max(-1, keepdim=True).values
+    rng = mxv - mn
+    scale = rng / 3
+    scale = torch.where(rng <= 1e-8, torch.ones_like(scale), scale)
+    scale = torch.pow(2.0, torch.round(torch.log2(scale.clamp(min=1e-12))))
+    out = torch.where(qm, torch.round((g - mn) / scale).clamp(0, 3) * scale + mn, g)
+    if bool(omask.any()):
+        omn = torch.where(omask, g, torch.tensor(1e8)).min(-1, keepdim=True).values
+        omx = torch.where(omask, g, torch.tensor(-1e8)).max(-1, keepdim=True).values
+        center = (omx + omn) / 2.0
+        mscale = 12.0 / (omx - omn).clamp_min(1e-8)
+        m = (g - center) * mscale
+        idx = torch.bucketize(m.abs().view(torch.int32), torch.from_numpy(FP4_THRESH.astype(np.int32)), right=True)
+        lvl = torch.from_numpy(FP4_LEVELS)[idx] * torch.sign(m)
+        out = torch.where(omask, lvl / mscale + center, out)
+    res = out.reshape(Hh, wp.shape[1], -1)[..., :L]
+    res = res.transpose(1, 2) if is_key else res
+    full = x.clone()
+    full[:, lo:hi, :] = res
+    return full

@@ -75,7 +75,9 @@ class Case:
         tails = [s - p for s, p in zip(seq_lens, packed)]
         n_pages = [p // page_size for p in packed]
         n_groups = [p // 32 for p in packed]
-        tot_pages, tot_groups = sum(n_pages) + spare_pages, sum(n_groups) + spare_pages
+        # pooled planes keep pages*page_size == group_slots*32 (the launcher derives the group size from it)
+        tot_groups = sum(n_groups) + spare_pages
+        tot_pages = tot_groups * (32 // page_size)
         if permute:
             pperm = torch.randperm(tot_pages, generator=torch.Generator().manual_seed(4242)).numpy()
             gperm = torch.randperm(tot_groups, generator=torch.Generator().manual_seed(4243)).numpy()

@@ -57,6 +57,9 @@ def test_fakequant_bit_exact():
     V = np.ascontiguousarray(g["V"].transpose(1, 0, 2))
     assert (O.fakequant_group(K, is_key=True) == g["K_fq"]).all()
     assert (O.fakequant_group(V, is_key=False, top=0, bottom=0) == g["V_fq"]).all()
+    import torch
+    assert (O.fakequant_group_torch(torch.from_numpy(K), is_key=True).numpy() == g["K_fq"]).all()
+    assert (O.fakequant_group_torch(torch.from_numpy(V), is_key=False, top=0, bottom=0).numpy() == g["V_fq"]).all()
 
 
 def _attn_case(name):
