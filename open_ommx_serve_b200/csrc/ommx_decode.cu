@@ -11,8 +11,8 @@
 //   8 consumer warps each own one (group, kv head) unit per stage and keep a private online-
 //                   softmax state.  Per unit:
 //     phase A (lane = 4 channels): walk the outlier bitmask with clz, decode the FP4 nibble,
-//                   and write the outlier value, expressed in code units, into a per-warp
-//                   bf16 tile [token][channel-slot]; clear that lane's 2-bit base code in place.
+//                   and write the delta between the outlier value and the base code it replaces,
+//                   expressed in code units, into a per-warp bf16 tile [token][channel-slot].
 //     phase B (mma lanes): 2-bit codes -> bf16 with one LOP3 per pair (magic exponent, value
 //                   128 + code*4^p), per-channel power-of-two scale folded into q, QK^T on
 //                   mma.sync m16n8k16 (GQA rows padded to 16); the outlier tile is a second B
@@ -22,9 +22,9 @@
 //                   (code*vs+vz, as the reference) and P.V on the same MMA shape.
 //
 // Numerics follow the reference kernel's rounding points: q*sm_scale rounded to bf16, exact
-// code*2^e products, fp32 accumulation, P rounded to bf16, V dequantized to bf16.  Two points
-// differ at the bf16-rounding level only: the outlier enters as one bf16 value in code units
-// instead of a bf16 delta, and q.zp uses the bf16 q*sm_scale instead of fp32 q.
+// code*2^e products, the outlier delta rounded to bf16, fp32 accumulation, P rounded to bf16, V
+// dequantized to bf16.  One point differs at the bf16-rounding level: q.zp uses the bf16
+// q*sm_scale instead of fp32 q.
 #include "ommx_common.cuh"
 
 namespace ommx {
@@ -279,14 +279,12 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
         // phase-A constants: this lane owns channels 4*lane + c
         uint32_t pa_col[4];       // byte offset of the channel's column inside an outlier-tile row
         float pa_f[4];            // 4^pc of the channel's slot
-        uint32_t pa_clr[4];       // mask clearing the channel's 2-bit code inside its 32-bit word
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int d = 4 * lane + c;
             const int jj = d >> 5, wi = (d >> 4) & 1, i = d & 7, hi = (d >> 3) & 1;
             pa_col[c] = 2u * (16 * (4 * wi + (i >> 1)) + 8 * (i & 1) + 2 * jj + hi);
             pa_f[c] = (float)(1 << (2 * pos_class(i)));
-            pa_clr[c] = ~(3u << (8 * (lane & 3) + 2 * c));
         }
         // outlier tile: row 33 = -128 in every column (never rewritten); clear the rest once
         for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(tile)[i] = 0u;
@@ -355,7 +353,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                         }
                     }
                     const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
-                    uint8_t *kbw = kb + (lane & ~3);                     // the word holding this lane's code byte
+                    const uint8_t *kbl = kb + lane;                      // this lane's code byte (channels 4*lane..+3)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int e = (int)(int8_t)(e4 >> (8 * c));
@@ -384,9 +382,12 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                                 bits ^= 1u << pz;
                                 const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
                                 --r;
-                                const float X = fmaf(s_lut[nib], A, Bc);
+                                // delta between the outlier value and the base code it replaces, in code
+                                // units: ((lvl/ms + mc) - (code*s + zp)) / s, rounded to bf16 as the
+                                // reference rounds its delta (the scaling by 1/s and 4^pc is exact)
+                                const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
+                                const float X = fmaf(-cf, pa_f[c], fmaf(s_lut[nib], A, Bc));
                                 *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
-                                atomicAnd(reinterpret_cast<unsigned int *>(kbw + pz * TS), pa_clr[c]);
                             }
                         }
                     }
@@ -523,8 +524,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                     for (int i = 0; i < 16; ++i) mma_bf16(acc[i], P[2 * kt], 0u, P[2 * kt + 1], 0u, Vr[0][i], Vr[1][i]);
                 }
             }
-            // release the stage (generic-proxy writes into it are ordered before the next bulk copy)
-            fence_proxy_async();
+            // release the stage
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);
         }

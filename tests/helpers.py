@@ -149,10 +149,27 @@ class Case:
             bitmap_read=self.k > 0, k_obmp=p.get("k_obmp"),
             k_fp4_mapscale=p.get("k_fp4_mapscale"), k_fp4_mapcenter=p.get("k_fp4_mapcenter"),
             kv_outlier_map=self.outlier_map, kv_int8_scale=True, num_kv_splits=num_kv_splits,
-            max_seq_len=max(self.packed + [0]) if kw.pop("pass_max", True) else None,
-            max_tail_len=max(self.tails + [0]) if kw.pop("pass_max_tail", True) else None,
+            max_seq_len=kw.pop("max_seq_len", max(self.packed + [0]) if kw.pop("pass_max", True) else None),
+            max_tail_len=kw.pop("max_tail_len", max(self.tails + [0]) if kw.pop("pass_max_tail", True) else None),
             attn_logits=attn_logits, status=status, **kw)
         torch.cuda.synchronize()
+        return o, lse
+
+    def oracle_kernel_arith(self, num_kv_splits=1, split_pv=False):
+        """The reference kernel's arithmetic (bf16 rounding points, split + merge) restated on CPU."""
+        B = len(self.seq_lens)
+        o = np.zeros((B, self.Hq, self.D), dtype=np.float32)
+        lse = np.zeros((B, self.Hq), dtype=np.float32)
+        empty = np.zeros((0, self.H, self.D), dtype=np.float32)
+        for b, rec in enumerate(self.per_seq):
+            Kt = rec["K"][rec["tail_idx"]].numpy()
+            Vt = rec["V"][rec["tail_idx"]].numpy()
+            q = self.q[b].float().numpy()
+            if rec["planes"] is not None:
+                o[b], lse[b], _ = O.decode_split_kv(q, rec["planes"], Kt, Vt, self.sm_scale, num_kv_splits,
+                                                    split_pv=split_pv)
+            else:
+                o[b], lse[b] = O.attention_fp32(q, Kt, Vt, self.sm_scale)
         return o, lse
 
     def oracle(self):
@@ -170,10 +187,22 @@ class Case:
         return o, lse
 
 
-def check_close(got, want, *, cos_min=0.9999, max_abs=2e-2, ctx=""):
-    """The attention gate: max-abs <= 2e-2 and cosine >= 0.9999 (stated tolerance of the path)."""
+def check_close(got, want, *, cos_min=0.9999, max_abs=2e-2, rel_l2_max=None, ctx=""):
+    """The attention gate of the path: max-abs <= 2e-2 and cosine >= 0.9999 against the
+    reference kernel's arithmetic.  Against plain fp32 attention the reference's own gate
+    applies instead (cos >= 0.999, rel-L2 <= 0.02): pass ``cos_min=0.999, max_abs=None,
+    rel_l2_max=0.02``."""
     g = got.detach().float().cpu().numpy() if isinstance(got, torch.Tensor) else got
     assert np.isfinite(g).all(), f"{ctx}: non-finite output"
     cos, mabs, rel = O.compare(g, want)
-    assert mabs <= max_abs and cos >= cos_min, f"{ctx}: cos={cos:.6f} max_abs={mabs:.3e} rel_l2={rel:.3e}"
+    if os.environ.get("OMMX_TEST_LOG"):
+        with open(os.environ["OMMX_TEST_LOG"], "a") as f:
+            f.write(f"{ctx}: cos={cos:.7f} max_abs={mabs:.3e} rel_l2={rel:.3e}\n")
+    ok = cos >= cos_min and (max_abs is None or mabs <= max_abs) and (rel_l2_max is None or rel <= rel_l2_max)
+    assert ok, f"{ctx}: cos={cos:.6f} max_abs={mabs:.3e} rel_l2={rel:.3e}"
     return cos, mabs, rel
+
+
+def check_fp32(got, want, ctx=""):
+    """The reference's own kernel-vs-fp32-oracle gate (attention/oracle.py: COS_MIN, REL_L2_MAX)."""
+    return check_close(got, want, cos_min=0.999, max_abs=None, rel_l2_max=0.02, ctx=ctx)

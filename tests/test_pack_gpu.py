@@ -142,4 +142,5 @@ def test_pack_refusals():
     with pytest.raises(NotImplementedError):
         pack(K, V, outliers_per_vector=6, outlier_repr="relidx7", device="cuda")
     with pytest.raises(NotImplementedError):
-        pack(K, V, outliers_per_vector=6, outlier_repr="bitmap", group_tokens=64, device="cuda")
+        pack(torch.cat([K, K]), torch.cat([V, V]), outliers_per_vector=6, outlier_repr="bitmap",
+             group_tokens=64, device="cuda")
