@@ -290,6 +290,15 @@ def run_ours(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=device)
     hkv, hq = HKV // world, HQ // world
     stack = LayerStack(args.ctx, 1, hkv, hq, device)
+    if args.profile:
+        # plain eager launches for a profiler: no graph, no timing, no JSON line
+        stack.set_context(args.ctx)
+        for _ in range(args.steps):
+            for i in range(LAYERS):
+                stack.decode_layer(i)
+        torch.cuda.synchronize()
+        print(f"profile run: {args.steps} x {LAYERS} decode calls at ctx {args.ctx}, splits {stack.splits}", file=sys.stderr)
+        return
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     gathered = torch.zeros(LAYERS, world, 1, hq, D, dtype=torch.float32, device=device) if world > 1 else None
     lib = _lib.load()
@@ -439,7 +448,10 @@ def main():
     ap.add_argument("--ctx", type=int, default=HEADLINE_CTX)
     ap.add_argument("--no-all-contexts", dest="all_contexts", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers in the stack (32 = the benchmark)")
+    ap.add_argument("--profile", action="store_true", help="eager launches only, for ncu (use a small --layers)")
     args = ap.parse_args()
+    globals()["LAYERS"] = args.layers
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

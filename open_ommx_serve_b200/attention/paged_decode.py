@@ -185,7 +185,7 @@ def ommx_paged_decode_attention_canonical(
     if int(k_base.shape[1]) != int(page_size):
         raise ValueError(f"k_base is [pages, {k_base.shape[1]}, h, w] but page_size={page_size}")
     for name, t in (("k_base", k_base), ("v_main", v_main), ("v_scale", v_scale), ("v_zp", v_zp)):
-        if pages and t.stride(0) != int(page_size) * t.stride(1) or t.stride(-1) != 1:
+        if pages and (t.stride(0) != int(page_size) * t.stride(1) or t.stride(-1) != 1):
             raise ValueError(f"{name} must be a contiguous [pages, page_size, h, w] plane")
     start_offset = int(packed_start_offset or 0)
     if start_offset < 0 or start_offset >= int(page_size):

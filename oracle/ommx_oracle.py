@@ -338,9 +338,13 @@ def decode_split_kv(q, planes, k_tail, v_tail, sm_scale, num_splits, *, seq=None
                 for i in range(ov.shape[-1]):
                     stream |= ov[..., i].astype(np.uint64) << np.uint64(8 * i)
                 lvl = fp4_decode((stream >> (4 * rank).astype(np.uint64)) & np.uint64(0xF))
-                ms = bf16_from_bits(planes["k_fp4_mapscale"][gslot, kh])
-                mc = bf16_from_bits(planes["k_fp4_mapcenter"][gslot, kh])
-                d = bf16_round(((lvl / ms + mc) - (kbase + zp)).astype(F32))
+                if planes["kv_outlier_map"]:
+                    ms = bf16_from_bits(planes["k_fp4_mapscale"][gslot, kh])
+                    mc = bf16_from_bits(planes["k_fp4_mapcenter"][gslot, kh])
+                    ov = (lvl / ms + mc).astype(F32)
+                else:
+                    ov = (lvl * sc + zp).astype(F32)
+                d = bf16_round((ov - (kbase + zp)).astype(F32))
                 delta = np.where(isout, d, F32(0))
             vcode = _unpack2(vm[loc, kh]).astype(F32).reshape(len(toks), D // 32, 32)
             vs = np.ldexp(F32(1.0), vsc[loc, kh].astype(np.int32)).astype(F32)[..., None]
@@ -351,20 +355,27 @@ def decode_split_kv(q, planes, k_tail, v_tail, sm_scale, num_splits, *, seq=None
             else:
                 vdq = bf16_round((vcode * vs + vz).astype(F32)).reshape(len(toks), D)
                 vbias = None
+            kfull = kbase.astype(np.float64) + delta.astype(np.float64)
             for j in range(per_h):
                 h = kh * per_h + j
                 qzp = (zp.astype(np.float64) @ q[h].astype(np.float64)).astype(F32) * F32(sm_scale)
-                logit = ((kbase.astype(np.float64) + delta.astype(np.float64))
-                         @ qc[h].astype(np.float64)).astype(F32) + qzp
-                m = logit.max()
-                p = np.exp((logit - m).astype(F32)).astype(F32)
-                pb = bf16_round(p).astype(np.float64)
-                acc = pb @ vdq.astype(np.float64)
-                if vbias is not None:
-                    acc = acc + pb @ vbias.astype(np.float64)
-                esum = p.astype(np.float64).sum()
-                mid[h, s, :D] = (acc / esum).astype(F32)
-                mid[h, s, D] = F32(m + math.log(esum))
+                logit = (kfull @ qc[h].astype(np.float64)).astype(F32) + qzp
+                # online softmax over 32-token tiles, as the kernel runs it (paged_decode.py:2060-2068)
+                e_max, e_sum = F32(-np.inf), 0.0
+                acc = np.zeros(D, dtype=np.float64)
+                for g0 in range(0, len(toks), GROUP_TOKENS):
+                    x = logit[g0:g0 + GROUP_TOKENS]
+                    n_max = max(e_max, x.max())
+                    re = math.exp(float(e_max) - float(n_max)) if np.isfinite(e_max) else 0.0
+                    p = np.exp((x - n_max).astype(F32)).astype(F32)
+                    pb = bf16_round(p).astype(np.float64)
+                    acc = acc * re + pb @ vdq[g0:g0 + GROUP_TOKENS].astype(np.float64)
+                    if vbias is not None:
+                        acc = acc + pb @ vbias[g0:g0 + GROUP_TOKENS].astype(np.float64)
+                    e_sum = e_sum * re + float(p.astype(np.float64).sum())
+                    e_max = n_max
+                mid[h, s, :D] = (acc / e_sum).astype(F32)
+                mid[h, s, D] = F32(float(e_max) + math.log(e_sum))
     o_t, lse_t = attention_fp32(q, k_tail, v_tail, sm_scale)
     o = np.zeros((Hq, D), dtype=F32)
     lse = np.zeros((Hq,), dtype=F32)

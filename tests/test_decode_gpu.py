@@ -161,8 +161,8 @@ def test_decode_segments_and_merge_states():
     case.b_seq_len.copy_(saved_seq)
     case.b_tail_len.copy_(saved_tail)
     o, l = merge_attention_states(torch.stack(parts_o), torch.stack(parts_l))
-    assert (o - full_o[0]).abs().max().item() < 1e-4
-    assert (l - full_lse[0]).abs().max().item() < 1e-4
+    assert (o - full_o[0]).abs().max().item() < 2e-3        # different split boundaries, bf16 P rounding
+    assert (l - full_lse[0]).abs().max().item() < 2e-3
     # ragged merge: only the first part counts for row 0
     valid = torch.tensor([1] + [3] * (o.shape[0] - 1), dtype=torch.int32, device="cuda")
     o2, l2 = merge_attention_states(torch.stack(parts_o), torch.stack(parts_l), valid_lens=valid)
