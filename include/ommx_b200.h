@@ -131,6 +131,9 @@ typedef struct ommx_decode_args {
     int32_t packed_start_offset;  /* must be 0 */
     float sm_scale, logit_cap;
     int32_t *status;              /* optional */
+    int32_t abl_flags;            /* differential-timing ablations (break parity), 0 in service:
+                                     1 skip outlier splice, 2 skip V/PV, 4 skip K code dequant
+                                     (reference: OMMX_ABL_* knobs, attention/paged_decode.py:3267-3279) */
 } ommx_decode_args;
 
 int ommx_b200_decode(const ommx_decode_args *args, void *stream);          /* stage 1 + stage 2 */

@@ -53,7 +53,8 @@ class DecodeArgs(C.Structure):
                 ("al_stride_b", C.c_int64), ("al_stride_h", C.c_int64), ("al_stride_s", C.c_int64),
                 ("num_kv_splits", C.c_int32), ("max_seq_len", C.c_int32), ("max_tail_len", C.c_int32),
                 ("seg_group_base", C.c_int32), ("packed_start_offset", C.c_int32),
-                ("sm_scale", C.c_float), ("logit_cap", C.c_float), ("status", C.c_void_p)]
+                ("sm_scale", C.c_float), ("logit_cap", C.c_float), ("status", C.c_void_p),
+                ("abl_flags", C.c_int32)]
 
 
 #: every symbol include/ommx_b200.h declares: name -> (restype, argtypes)

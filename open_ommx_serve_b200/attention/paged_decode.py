@@ -270,6 +270,10 @@ def ommx_paged_decode_attention_canonical(
     a.seg_group_base, a.packed_start_offset = seg_group_base, start_offset
     a.sm_scale, a.logit_cap = float(sm_scale), float(logit_cap)
     a.status = None if status is None else status.data_ptr()
+    # ablation knobs (differential timing only; recorded so a leaked export cannot pass as served)
+    abl = sum(1 << i for i, n in enumerate(ABL_FLAG_NAMES[:3]) if env_truthy(os.environ.get(n)))
+    a.abl_flags = abl
+    _LAUNCHES["abl"] |= abl
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
         entry = (lib.ommx_b200_decode, lib.ommx_b200_decode_stage1, lib.ommx_b200_decode_stage2)[int(_stage)]

@@ -55,6 +55,7 @@ struct S1Params {
     int32_t S, seg_group_base;
     float sm_scale, logit_cap;
     int32_t *status;
+    int32_t abl;
     // shared-memory layout of one group block (bytes)
     int32_t GS, gb_bytes, stage_bytes;
     int32_t o_vm, o_vs, o_vz, o_ks, o_kz, o_ms, o_mc, o_bm, o_ov;
@@ -134,6 +135,17 @@ __device__ __forceinline__ void codes_to_bf16x2(uint32_t w, uint32_t (&r)[8]) {
 // =================================================================================================
 // Stage 1
 // =================================================================================================
+// Ablation bits (differential timing only, they break parity; mirror of the reference's
+// OMMX_ABL_* knobs, paged_decode.py:3267-3279): 1 = skip the outlier splice, 2 = skip V dequant
+// and P.V, 4 = skip the K code dequant and its MMAs.
+constexpr int ABL_NO_OUTLIER = 1, ABL_NO_V = 2, ABL_NO_K = 4;
+
+// KOUT: outliers per K vector known at compile time (static, unrolled splice) or -1 (runtime).
+// VFOLD: GQA groups of at most 4 query heads.  The 16 MMA rows are (query head, V scale group)
+//        pairs, the per-(token, group) power-of-two V scale is folded into P, and V enters the
+//        MMA as raw 128 + code*4^pc values: no per-element V arithmetic at all.  The offset comes
+//        back out through a row-sum column, the zero-points through a small bias MMA.
+template <int KOUT, bool VFOLD>
 __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int split = blockIdx.x, b = blockIdx.y;
@@ -154,6 +166,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
     }
     const int H = p.H, GS = p.GS;
     const int n_iters = (ngroups + GS - 1) / GS;
+    const int k_out = KOUT >= 0 ? KOUT : p.k_out;
 
     // ---- shared memory carve-up ----
     uint8_t *s_stage = smem;                                            // NSTAGES * stage_bytes
@@ -183,8 +196,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
         if (threadIdx.x < 16) {
             const int c = threadIdx.x;
             const int mi = ((c >> 1) & 3) * 2 + (c & 1);                // exp*2 + mant
-            const float mags[8] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-            s_lut[c] = (c & 8) ? -mags[mi] : mags[mi];
+            const float mag = mi == 0 ? 0.f : (mi == 1 ? .5f : (float)(2 + (mi & 1)) * (float)(1 << (mi >> 1)) * 0.25f);
+            s_lut[c] = (c & 8) ? -mag : mag;
         }
         if (threadIdx.x == 0) {
             for (int s = 0; s < NSTAGES; ++s) {
@@ -215,7 +228,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                 const int lg = it * GS + gi;
                 const int vp = min(p.ppg, (ntok - 32 * lg + p.ps - 1) / p.ps);
                 total += (uint32_t)vp * page_b * (32 + 32 + 4 + 8) + (uint32_t)H * (128 + 256);
-                if (p.k_out > 0) total += (uint32_t)H * (512 + 128 * p.nb) + (p.use_map ? (uint32_t)H * 512 : 0u);
+                if (k_out > 0) total += (uint32_t)H * (512 + 128 * p.nb) + (p.use_map ? (uint32_t)H * 512 : 0u);
             }
             if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
             __syncwarp();
@@ -239,7 +252,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                     const int64_t e = slot * H;                         // (slot, head) rows before
                     if (gp == 0) bulk_g2s(gb + p.o_ks, p.k_scale + e * 128, H * 128, bar_full + 8 * s);
                     else if (gp == 1) bulk_g2s(gb + p.o_kz, p.k_zp + e * 256, H * 256, bar_full + 8 * s);
-                    else if (p.k_out > 0) {
+                    else if (k_out > 0) {
                         if (gp == 2) { if (p.use_map) bulk_g2s(gb + p.o_ms, p.k_ms + e * 256, H * 256, bar_full + 8 * s); }
                         else if (gp == 3) { if (p.use_map) bulk_g2s(gb + p.o_mc, p.k_mc + e * 256, H * 256, bar_full + 8 * s); }
                         else if (gp == 4) bulk_g2s(gb + p.o_bm, p.k_obmp + e * 512, H * 512, bar_full + 8 * s);
@@ -248,170 +261,206 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                 }
             }
         }
-    } else {
-        // =========================== consumer warps ===========================
-        const int g = lane >> 2, j = lane & 3;
-        const int h = warp % H, gsel = warp / H;
-        const int TS = H * 32;                                          // bytes per token row (all heads)
-        uint8_t *tile = s_tiles + warp * DT_BYTES;
-        const uint32_t tile_s = smem_u32(tile);
-        const float LOG2E = 1.4426950408889634f;
+        // fall through to the two CTA-wide barriers of the epilogue
+        __syncthreads();
+        __syncthreads();
+        return;
+    }
 
-        // ---- per-thread constants ----
-        // q_static: bf16(q*sm_scale) * 2^-1 * 4^-pc for this lane's head row and 32 channel slots
-        uint32_t QS[16];
-        {
-            const bool row_ok = g < p.gqa;
-            const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (row_ok ? g : 0)) * p.q_sh;
+    // =========================== consumer warps ===========================
+    const int g = lane >> 2, j = lane & 3;
+    const int h = warp % H, gsel = warp / H;
+    const int TS = H * 32;                                          // bytes per token row (all heads)
+    uint8_t *tile = s_tiles + warp * DT_BYTES;
+    const uint32_t tile_s = smem_u32(tile);
+    const float LOG2E = 1.4426950408889634f;
+    const bool no_outlier = (p.abl & ABL_NO_OUTLIER) != 0;
+
+    // ---- per-thread constants ----
+    // MMA row g carries query head (g % 4) when VFOLD (rows 4..7 repeat rows 0..3), else head g.
+    const int row_head = VFOLD ? (g & 3) : g;
+    const bool row_ok = row_head < p.gqa;
+    // q_static: bf16(q*sm_scale) * 2^-1 * 4^-pc for this lane's head row and 32 channel slots
+    uint32_t QS[16];
+    {
+        const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (row_ok ? row_head : 0)) * p.q_sh;
 #pragma unroll
-            for (int r = 0; r < 16; ++r) {
-                const int wi = r >> 3, i = r & 7;
-                const int ch = 32 * j + 16 * wi + i;
-                const float f = 0.5f / (float)(1 << (2 * pos_class(i)));
-                float lo = 0.f, hi = 0.f;
-                if (row_ok) {
-                    lo = bf16_round_f32(__bfloat162float(qrow[ch]) * p.sm_scale) * f;
-                    hi = bf16_round_f32(__bfloat162float(qrow[ch + 8]) * p.sm_scale) * f;
-                }
-                QS[r] = pack_bf16x2(lo, hi);
+        for (int r = 0; r < 16; ++r) {
+            const int wi = r >> 3, i = r & 7;
+            const int ch = 32 * j + 16 * wi + i;
+            const float f = 0.5f / (float)(1 << (2 * pos_class(i)));
+            float lo = 0.f, hi = 0.f;
+            if (row_ok) {
+                lo = bf16_round_f32(__bfloat162float(qrow[ch]) * p.sm_scale) * f;
+                hi = bf16_round_f32(__bfloat162float(qrow[ch + 8]) * p.sm_scale) * f;
             }
+            QS[r] = pack_bf16x2(lo, hi);
         }
-        // phase-A constants: this lane owns channels 4*lane + c
-        uint32_t pa_col[4];       // byte offset of the channel's column inside an outlier-tile row
-        float pa_f[4];            // 4^pc of the channel's slot
+    }
+    // phase-A constants: this lane owns channels 4*lane + c
+    uint32_t pa_col[4];       // byte offset of the channel's column inside an outlier-tile row
+    float pa_f[4];            // 4^pc of the channel's slot
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int d = 4 * lane + c;
-            const int jj = d >> 5, wi = (d >> 4) & 1, i = d & 7, hi = (d >> 3) & 1;
-            pa_col[c] = 2u * (16 * (4 * wi + (i >> 1)) + 8 * (i & 1) + 2 * jj + hi);
-            pa_f[c] = (float)(1 << (2 * pos_class(i)));
+    for (int c = 0; c < 4; ++c) {
+        const int d = 4 * lane + c;
+        const int jj = d >> 5, wi = (d >> 4) & 1, i = d & 7, hi = (d >> 3) & 1;
+        pa_col[c] = 2u * (16 * (4 * wi + (i >> 1)) + 8 * (i & 1) + 2 * jj + hi);
+        pa_f[c] = (float)(1 << (2 * pos_class(i)));
+    }
+    // V-fold constants: byte selectors of this row pair's two V scale groups
+    const int cgA = g >> 2, cgB = 2 + (g >> 2);
+    const uint32_t selA = (uint32_t)(cgA | (cgA << 4) | ((4 + cgA) << 8) | ((4 + cgA) << 12));
+    const uint32_t selB = (uint32_t)(cgB | (cgB << 4) | ((4 + cgB) << 8) | ((4 + cgB) << 12));
+    // outlier tile: row 33 = -128 in every column (never rewritten); clear the rest once
+    for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(tile)[i] = 0u;
+    __syncwarp();
+    for (int i = lane; i < 64; i += 32) reinterpret_cast<uint32_t *>(tile + 33 * DT_STRIDE)[i] = 0xC300C300u;
+    __syncwarp();
+
+    // ---- online softmax state (row g of the MMA tile) ----
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    float acc_rs[4] = {0.f, 0.f, 0.f, 0.f};      // VFOLD: sum_t P'[row][t]        (x128 offset)
+    float acc_vz[4] = {0.f, 0.f, 0.f, 0.f};      // VFOLD: sum_t P[row][t] * vz[t][cg = column]
+
+    for (int it = 0; it < n_iters; ++it) {
+        const int s = it % NSTAGES;
+        const uint32_t ph = (it / NSTAGES) & 1;
+        if (!mbar_wait(bar_full + 8 * s, ph)) {
+            if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+            m_run = -INFINITY; l_run = 0.f;
+            break;
         }
-        // outlier tile: row 33 = -128 in every column (never rewritten); clear the rest once
-        for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(tile)[i] = 0u;
-        __syncwarp();
-        for (int i = lane; i < 64; i += 32) reinterpret_cast<uint32_t *>(tile + 33 * DT_STRIDE)[i] = 0xC300C300u;
-        __syncwarp();
+        const int lg = it * GS + gsel;                               // local group of this warp
+        if (lg < ngroups) {
+            uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
+            const uint8_t *kb = gb + h * 32;                         // + token*TS
+            const uint8_t *vm = gb + p.o_vm + h * 32;
+            const uint8_t *vsc = gb + p.o_vs + h * 4;                // + token*H*4
+            const uint8_t *vzp = gb + p.o_vz + h * 8;                // + token*H*8
+            const uint8_t *ksc = gb + p.o_ks + h * 128;
+            const uint8_t *kzp = gb + p.o_kz + h * 256;
 
-        // ---- online softmax state (row g of the MMA tile) ----
-        float m_run = -INFINITY, l_run = 0.f;
-        float acc[16][4];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-
-        bool aborted = false;
-        for (int it = 0; it < n_iters; ++it) {
-            const int s = it % NSTAGES;
-            const uint32_t ph = (it / NSTAGES) & 1;
-            if (!mbar_wait(bar_full + 8 * s, ph)) {
-                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
-                aborted = true;
-                break;
-            }
-            const int lg = it * GS + gsel;                               // local group of this warp
-            if (lg < ngroups) {
-                uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
-                uint8_t *kb = gb + h * 32;                               // + token*TS
-                const uint8_t *vm = gb + p.o_vm + h * 32;
-                const uint8_t *vsc = gb + p.o_vs + h * 4;                // + token*H*4
-                const uint8_t *vzp = gb + p.o_vz + h * 8;                // + token*H*8
-                const uint8_t *ksc = gb + p.o_ks + h * 128;
-                const uint8_t *kzp = gb + p.o_kz + h * 256;
-
-                // ======================= phase A: outliers + zp row =======================
-                {
+            // ======================= phase A: outlier deltas + zp row =======================
+            {
+                const bool splice = k_out > 0 && !no_outlier;
+                if (splice) {
                     // clear token rows 0..31 (256 data bytes each)
 #pragma unroll
                     for (int r2 = 0; r2 < 16; ++r2)
                         *reinterpret_cast<uint4 *>(tile + (2 * r2 + (lane >> 4)) * DT_STRIDE + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
                     __syncwarp();
-                    const uint32_t e4 = *reinterpret_cast<const uint32_t *>(ksc + 4 * lane);
-                    const uint2 z4 = *reinterpret_cast<const uint2 *>(kzp + 8 * lane);
-                    uint2 ms4 = make_uint2(0, 0), mc4 = make_uint2(0, 0);
-                    uint4 bm4 = make_uint4(0, 0, 0, 0);
-                    uint32_t st[4] = {0, 0, 0, 0};
-                    if (p.k_out > 0) {
-                        if (p.use_map) {
-                            ms4 = *reinterpret_cast<const uint2 *>(gb + p.o_ms + h * 256 + 8 * lane);
-                            mc4 = *reinterpret_cast<const uint2 *>(gb + p.o_mc + h * 256 + 8 * lane);
-                        }
-                        bm4 = *reinterpret_cast<const uint4 *>(gb + p.o_bm + h * 512 + 16 * lane);
-                        const uint32_t *ov = reinterpret_cast<const uint32_t *>(gb + p.o_ov + h * 128 * p.nb + 4 * p.nb * lane);
-                        if (p.nb == 3) {
-                            const uint32_t w0 = ov[0], w1 = ov[1], w2 = ov[2];
-                            st[0] = w0 & 0xFFFFFFu;
-                            st[1] = (w0 >> 24) | ((w1 & 0xFFFFu) << 8);
-                            st[2] = (w1 >> 16) | ((w2 & 0xFFu) << 16);
-                            st[3] = w2 >> 8;
-                        } else if (p.nb == 4) {
-                            st[0] = ov[0]; st[1] = ov[1]; st[2] = ov[2]; st[3] = ov[3];
-                        } else if (p.nb == 2) {
-                            const uint32_t w0 = ov[0], w1 = ov[1];
-                            st[0] = w0 & 0xFFFFu; st[1] = w0 >> 16; st[2] = w1 & 0xFFFFu; st[3] = w1 >> 16;
-                        } else {
-                            const uint32_t w0 = ov[0];
-                            st[0] = w0 & 0xFFu; st[1] = (w0 >> 8) & 0xFFu; st[2] = (w0 >> 16) & 0xFFu; st[3] = w0 >> 24;
-                        }
+                }
+                const uint32_t e4 = *reinterpret_cast<const uint32_t *>(ksc + 4 * lane);
+                const uint2 z4 = *reinterpret_cast<const uint2 *>(kzp + 8 * lane);
+                uint2 ms4 = make_uint2(0, 0), mc4 = make_uint2(0, 0);
+                uint4 bm4 = make_uint4(0, 0, 0, 0);
+                uint32_t st[4] = {0, 0, 0, 0};
+                if (splice) {
+                    if (p.use_map) {
+                        ms4 = *reinterpret_cast<const uint2 *>(gb + p.o_ms + h * 256 + 8 * lane);
+                        mc4 = *reinterpret_cast<const uint2 *>(gb + p.o_mc + h * 256 + 8 * lane);
                     }
-                    const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
-                    const uint8_t *kbl = kb + lane;                      // this lane's code byte (channels 4*lane..+3)
+                    bm4 = *reinterpret_cast<const uint4 *>(gb + p.o_bm + h * 512 + 16 * lane);
+                    const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
+                    const uint32_t *ov = reinterpret_cast<const uint32_t *>(gb + p.o_ov + h * 128 * nb + 4 * nb * lane);
+                    if (nb == 3) {
+                        const uint32_t w0 = ov[0], w1 = ov[1], w2 = ov[2];
+                        st[0] = w0 & 0xFFFFFFu;
+                        st[1] = (w0 >> 24) | ((w1 & 0xFFFFu) << 8);
+                        st[2] = (w1 >> 16) | ((w2 & 0xFFu) << 16);
+                        st[3] = w2 >> 8;
+                    } else if (nb == 4) {
+                        st[0] = ov[0]; st[1] = ov[1]; st[2] = ov[2]; st[3] = ov[3];
+                    } else if (nb == 2) {
+                        const uint32_t w0 = ov[0], w1 = ov[1];
+                        st[0] = w0 & 0xFFFFu; st[1] = w0 >> 16; st[2] = w1 & 0xFFFFu; st[3] = w1 >> 16;
+                    } else {
+                        const uint32_t w0 = ov[0];
+                        st[0] = w0 & 0xFFu; st[1] = (w0 >> 8) & 0xFFu; st[2] = (w0 >> 16) & 0xFFu; st[3] = w0 >> 24;
+                    }
+                }
+                const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
+                const uint8_t *kbl = kb + lane;                      // this lane's code byte (channels 4*lane..+3)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int e = (int)(int8_t)(e4 >> (8 * c));
-                        const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
-                        const uint32_t zb = (c & 1) ? ((c & 2 ? z4.y : z4.x) >> 16) : ((c & 2 ? z4.y : z4.x) & 0xFFFFu);
-                        const float zp = bf16_bits_to_f32(zb);
-                        const float fs = inv_s * pa_f[c];
-                        // zp row: zp / scale in slot units (exact power-of-two scaling of a bf16)
-                        *reinterpret_cast<__nv_bfloat16 *>(tile + 32 * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(zp * fs);
-                        if (p.k_out > 0) {
-                            float A, Bc;
-                            if (p.use_map) {
-                                const uint32_t msb = (c & 1) ? ((c & 2 ? ms4.y : ms4.x) >> 16) : ((c & 2 ? ms4.y : ms4.x) & 0xFFFFu);
-                                const uint32_t mcb = (c & 1) ? ((c & 2 ? mc4.y : mc4.x) >> 16) : ((c & 2 ? mc4.y : mc4.x) & 0xFFFFu);
-                                A = __fdividef(fs, bf16_bits_to_f32(msb));
-                                Bc = (bf16_bits_to_f32(mcb) - zp) * fs;
+                for (int c = 0; c < 4; ++c) {
+                    const int e = (int)(int8_t)(e4 >> (8 * c));
+                    const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
+                    const uint32_t zw = (c & 2) ? z4.y : z4.x;
+                    const float zp = bf16_bits_to_f32((c & 1) ? (zw >> 16) : (zw & 0xFFFFu));
+                    const float fs = inv_s * pa_f[c];
+                    // zp row: zp / scale in slot units (exact power-of-two scaling of a bf16)
+                    *reinterpret_cast<__nv_bfloat16 *>(tile + 32 * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(zp * fs);
+                    if (splice) {
+                        float A, Bc;
+                        if (p.use_map) {
+                            const uint32_t msw = (c & 2) ? ms4.y : ms4.x, mcw = (c & 2) ? mc4.y : mc4.x;
+                            const float ms = bf16_bits_to_f32((c & 1) ? (msw >> 16) : (msw & 0xFFFFu));
+                            const float mc = bf16_bits_to_f32((c & 1) ? (mcw >> 16) : (mcw & 0xFFFFu));
+                            A = __fdividef(fs, ms);
+                            Bc = (mc - zp) * fs;
+                        } else {
+                            A = pa_f[c];                              // (lvl*s + zp - zp)/s = lvl
+                            Bc = 0.f;
+                        }
+                        uint32_t bits = bmv[c];
+                        const uint32_t stream = st[c];
+                        const float nf = -pa_f[c];
+                        // delta between the outlier value and the base code it replaces, in code units:
+                        // ((lvl/ms + mc) - (code*s + zp)) / s, rounded to bf16 as the reference rounds
+                        // its delta (the scaling by 1/s and 4^pc is exact)
+                        if (KOUT > 0) {
+                            if (__popc(bits) == KOUT) {
+#pragma unroll
+                                for (int r = KOUT - 1; r >= 0; --r) {
+                                    const int pz = 31 - __clz(bits);
+                                    bits ^= 1u << pz;
+                                    const uint32_t nib = (stream >> (4 * r)) & 0xFu;
+                                    const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
+                                    const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
+                                    *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
+                                }
                             } else {
-                                A = pa_f[c];                              // (lvl*s + zp - zp)/s = lvl
-                                Bc = 0.f;
+                                or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
                             }
-                            uint32_t bits = bmv[c];
-                            const uint32_t stream = st[c];
+                        } else {
                             int r = __popc(bits) - 1;
                             while (bits) {
                                 const int pz = 31 - __clz(bits);
                                 bits ^= 1u << pz;
                                 const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
                                 --r;
-                                // delta between the outlier value and the base code it replaces, in code
-                                // units: ((lvl/ms + mc) - (code*s + zp)) / s, rounded to bf16 as the
-                                // reference rounds its delta (the scaling by 1/s and 4^pc is exact)
                                 const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
-                                const float X = fmaf(-cf, pa_f[c], fmaf(s_lut[nib], A, Bc));
+                                const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
                                 *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
                             }
                         }
                     }
-                    __syncwarp();
                 }
+                __syncwarp();
+            }
 
-                // ======================= phase B: QK^T =======================
-                uint32_t QQ[16];
-                {
-                    const uint4 ea = *reinterpret_cast<const uint4 *>(ksc + 32 * j);
-                    const uint4 eb = *reinterpret_cast<const uint4 *>(ksc + 32 * j + 16);
-                    const uint32_t E[8] = {ea.x, ea.y, ea.z, ea.w, eb.x, eb.y, eb.z, eb.w};
+            // ======================= phase B: QK^T =======================
+            uint32_t QQ[16];
+            {
+                const uint4 ea = *reinterpret_cast<const uint4 *>(ksc + 32 * j);
+                const uint4 eb = *reinterpret_cast<const uint4 *>(ksc + 32 * j + 16);
+                const uint32_t E[8] = {ea.x, ea.y, ea.z, ea.w, eb.x, eb.y, eb.z, eb.w};
 #pragma unroll
-                    for (int r = 0; r < 16; ++r) {
-                        const int wi = r >> 3, i = r & 7, bsel = i & 3;
-                        const uint32_t sel = (uint32_t)(bsel | (bsel << 4) | ((4 + bsel) << 8) | ((4 + bsel) << 12));
-                        const uint32_t t = __byte_perm(E[4 * wi + (i >> 2)], E[4 * wi + 2 + (i >> 2)], sel);
-                        const uint32_t f = lop3_and_xor(t, 0x00FF00FFu, 0x00800080u) << 7;   // 2^(e+1) pair
-                        QQ[r] = hmul2_bf16(QS[r], f);
-                    }
+                for (int r = 0; r < 16; ++r) {
+                    const int wi = r >> 3, i = r & 7, bsel = i & 3;
+                    const uint32_t sel = (uint32_t)(bsel | (bsel << 4) | ((4 + bsel) << 8) | ((4 + bsel) << 12));
+                    const uint32_t t = __byte_perm(E[4 * wi + (i >> 2)], E[4 * wi + 2 + (i >> 2)], sel);
+                    const uint32_t f = lop3_and_xor(t, 0x00FF00FFu, 0x00800080u) << 7;   // 2^(e+1) pair
+                    QQ[r] = hmul2_bf16(QS[r], f);
                 }
-                float C[5][4];
+            }
+            float C[5][4];
 #pragma unroll
-                for (int nt = 0; nt < 5; ++nt) { C[nt][0] = C[nt][1] = C[nt][2] = C[nt][3] = 0.f; }
+            for (int nt = 0; nt < 5; ++nt) { C[nt][0] = C[nt][1] = C[nt][2] = C[nt][3] = 0.f; }
+            if (!(p.abl & ABL_NO_K)) {
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     const uint2 kw = *reinterpret_cast<const uint2 *>(kb + (8 * nt + g) * TS + 8 * j);
@@ -423,162 +472,229 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) mma_bf16(C[nt], QQ[8 + 2 * kk], 0u, QQ[8 + 2 * kk + 1], 0u, R[2 * kk], R[2 * kk + 1]);
                 }
-                // outlier tile (+ zp / -128 rows as n-tile 4)
-                {
-                    const int mi = lane >> 3, rr = lane & 7;
+            }
+            // outlier tile (+ zp / -128 rows as n-tile 4)
+            {
+                const int mi = lane >> 3, rr = lane & 7;
 #pragma unroll
-                    for (int nt = 0; nt < 5; ++nt) {
-                        if (nt < 4 && p.k_out == 0) continue;
-                        int row = 8 * nt + rr;
-                        if (row >= DT_ROWS) row -= DT_ROWS;              // rows 34..39 alias rows 0..5 (columns unused)
+                for (int nt = 0; nt < 5; ++nt) {
+                    if (nt < 4 && (k_out == 0 || no_outlier)) continue;
+                    int row = 8 * nt + rr;
+                    if (row >= DT_ROWS) row -= DT_ROWS;              // rows 34..39 alias rows 0..5 (columns unused)
+                    const uint32_t base = tile_s + row * DT_STRIDE + 2 * (16 * (mi >> 1) + 8 * (mi & 1));
 #pragma unroll
-                        for (int kp = 0; kp < 4; ++kp) {
-                            const uint32_t addr = tile_s + row * DT_STRIDE + 2 * (16 * (2 * kp + (mi >> 1)) + 8 * (mi & 1));
-                            uint32_t d0, d1, d2, d3;
-                            ldsm_x4(addr, d0, d1, d2, d3);
-                            mma_bf16(C[nt], QQ[4 * kp], 0u, QQ[4 * kp + 1], 0u, d0, d1);
-                            mma_bf16(C[nt], QQ[4 * kp + 2], 0u, QQ[4 * kp + 3], 0u, d2, d3);
-                        }
+                    for (int kp = 0; kp < 4; ++kp) {
+                        uint32_t d0, d1, d2, d3;
+                        ldsm_x4(base + 64 * kp, d0, d1, d2, d3);
+                        mma_bf16(C[nt], QQ[4 * kp], 0u, QQ[4 * kp + 1], 0u, d0, d1);
+                        mma_bf16(C[nt], QQ[4 * kp + 2], 0u, QQ[4 * kp + 3], 0u, d2, d3);
                     }
                 }
-                // q.zp - 128*sum(q'') sits in columns 0 and 1 of n-tile 4 (lanes with j == 0)
-                float qzo = C[4][0] + C[4][1];
-                qzo = __shfl_sync(0xFFFFFFFFu, qzo, lane & ~3);
+            }
+            // q.zp - 128*sum(q'') sits in columns 0 and 1 of n-tile 4 (lanes with j == 0)
+            float qzo = C[4][0] + C[4][1];
+            qzo = __shfl_sync(0xFFFFFFFFu, qzo, lane & ~3);
 
-                // ======================= online softmax =======================
-                float x[8];
+            // ======================= online softmax =======================
+            float x[8];
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) { x[2 * nt] = C[nt][0] + qzo; x[2 * nt + 1] = C[nt][1] + qzo; }
-                if (p.logit_cap > 0.f) {
+            for (int nt = 0; nt < 4; ++nt) { x[2 * nt] = C[nt][0] + qzo; x[2 * nt + 1] = C[nt][1] + qzo; }
+            if (p.logit_cap > 0.f) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) x[i] = p.logit_cap * tanhf(x[i] / p.logit_cap);
-                }
-                const int tok_base = 32 * lg;
-                if (tok_base + 32 > ntok) {
-#pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) {
-                        if (tok_base + 8 * nt + 2 * j >= ntok) x[2 * nt] = -INFINITY;
-                        if (tok_base + 8 * nt + 2 * j + 1 >= ntok) x[2 * nt + 1] = -INFINITY;
-                    }
-                }
-                float mloc = x[0];
-#pragma unroll
-                for (int i = 1; i < 8; ++i) mloc = fmaxf(mloc, x[i]);
-                mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 1));
-                mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 2));
-                const float m_new = fmaxf(m_run, mloc);
-                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                const float corr = fast_exp2((m_run - m_use) * LOG2E);   // m_run = -inf -> 0
-                float psum = 0.f;
-                uint32_t P[4];
+                for (int i = 0; i < 8; ++i) x[i] = p.logit_cap * tanhf(x[i] / p.logit_cap);
+            }
+            const int tok_base = 32 * lg;
+            if (tok_base + 32 > ntok) {
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
-                    const float p0 = fast_exp2((x[2 * nt] - m_use) * LOG2E);
-                    const float p1 = fast_exp2((x[2 * nt + 1] - m_use) * LOG2E);
-                    psum += p0 + p1;
-                    P[nt] = pack_bf16x2(p0, p1);
+                    if (tok_base + 8 * nt + 2 * j >= ntok) x[2 * nt] = -INFINITY;
+                    if (tok_base + 8 * nt + 2 * j + 1 >= ntok) x[2 * nt + 1] = -INFINITY;
                 }
-                l_run = l_run * corr + psum;
-                m_run = m_new;
-                if (__any_sync(0xFFFFFFFFu, corr != 1.0f)) {
+            }
+            float mloc = x[0];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) { acc[i][0] *= corr; acc[i][1] *= corr; }
+            for (int i = 1; i < 8; ++i) mloc = fmaxf(mloc, x[i]);
+            mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 1));
+            mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 2));
+            const float m_new = fmaxf(m_run, mloc);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float corr = fast_exp2((m_run - m_use) * LOG2E);   // m_run = -inf -> 0
+            const float mneg = -m_use * LOG2E;
+            float psum = 0.f;
+            uint32_t P[4];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float p0 = fast_exp2(fmaf(x[2 * nt], LOG2E, mneg));
+                const float p1 = fast_exp2(fmaf(x[2 * nt + 1], LOG2E, mneg));
+                psum += p0 + p1;
+                P[nt] = pack_bf16x2(p0, p1);
+            }
+            l_run = l_run * corr + psum;
+            m_run = m_new;
+            if (__any_sync(0xFFFFFFFFu, corr != 1.0f)) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    acc[i][0] *= corr; acc[i][1] *= corr;
+                    if (VFOLD) { acc[i][2] *= corr; acc[i][3] *= corr; }
                 }
+                if (VFOLD) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { acc_rs[i] *= corr; acc_vz[i] *= corr; }
+                }
+            }
 
-                // ======================= P.V =======================
-                // lane (g, j) supplies channel column g of every n-tile: channels 16*g + i, scale group g/2
+            // ======================= P.V =======================
+            // lane (g, j) supplies channel column g of every n-tile: channels 16*g + i, scale group g/2
+            if (!(p.abl & ABL_NO_V)) {
+                if (VFOLD) {
+                    // P'[row][t] = P[head][t] * 2^(e_v[t][cg(row)] + 1)   (exact)
+                    uint32_t PA[4], PB[4];
 #pragma unroll
-                for (int kt = 0; kt < 2; ++kt) {
-                    uint32_t Vr[2][16];
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        const int ta = 16 * kt + 8 * half + 2 * j, tb = ta + 1;
-                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vm + ta * TS + 4 * g);
-                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vm + tb * TS + 4 * g);
-                        const uint32_t ea = vsc[ta * H * 4 + (g >> 1)], eb2 = vsc[tb * H * 4 + (g >> 1)];
-                        const uint32_t za = *reinterpret_cast<const uint16_t *>(vzp + ta * H * 8 + 2 * (g >> 1));
-                        const uint32_t zb = *reinterpret_cast<const uint16_t *>(vzp + tb * H * 8 + 2 * (g >> 1));
-                        const uint32_t vs2 = (((ea | (eb2 << 16)) ^ 0x00800080u) & 0x00FF00FFu) << 7;   // 2^(e+1) pair
-                        const uint32_t vz2 = za | (zb << 16);
-                        const uint32_t vs_p0 = hmul2_bf16(vs2, 0x3F003F00u);    // * 2^-1
-                        const uint32_t vs_p1 = hmul2_bf16(vs2, 0x3E003E00u);    // * 2^-3
-                        const uint32_t vs_p2 = hmul2_bf16(vs2, 0x3D003D00u);    // * 2^-5
-                        const uint32_t xlo = __byte_perm(wa, wb, 0x5410);       // channels 0..7 of (ta, tb)
-                        const uint32_t xhi = __byte_perm(wa, wb, 0x7632);       // channels 8..15
-                        uint32_t R[8];
-                        const uint32_t K128 = 0x43004300u;
-                        codes_to_bf16x2(xlo, R);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int pc = pos_class(i);
-                            Vr[half][i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
-                        }
-                        codes_to_bf16x2(xhi, R);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int pc = pos_class(i);
-                            Vr[half][8 + i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
-                        }
+                    for (int nt = 0; nt < 4; ++nt) {
+                        const int ta = 8 * nt + 2 * j;
+                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vsc + ta * H * 4);
+                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vsc + (ta + 1) * H * 4);
+                        const uint32_t fa = lop3_and_xor(__byte_perm(wa, wb, selA), 0x00FF00FFu, 0x00800080u) << 7;
+                        const uint32_t fb = lop3_and_xor(__byte_perm(wa, wb, selB), 0x00FF00FFu, 0x00800080u) << 7;
+                        PA[nt] = hmul2_bf16(P[nt], fa);
+                        PB[nt] = hmul2_bf16(P[nt], fb);
                     }
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) mma_bf16(acc[i], P[2 * kt], 0u, P[2 * kt + 1], 0u, Vr[0][i], Vr[1][i]);
+                    for (int kt = 0; kt < 2; ++kt) {
+                        const int ta = 16 * kt + 2 * j;
+                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vm + ta * TS + 4 * g);
+                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vm + (ta + 1) * TS + 4 * g);
+                        const uint32_t wc = *reinterpret_cast<const uint32_t *>(vm + (ta + 8) * TS + 4 * g);
+                        const uint32_t wd = *reinterpret_cast<const uint32_t *>(vm + (ta + 9) * TS + 4 * g);
+                        uint32_t R0[8], R1[8];
+                        codes_to_bf16x2(__byte_perm(wa, wb, 0x5410), R0);       // channels 0..7 of (ta, tb)
+                        codes_to_bf16x2(__byte_perm(wc, wd, 0x5410), R1);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) mma_bf16(acc[i], PA[2 * kt], PB[2 * kt], PA[2 * kt + 1], PB[2 * kt + 1], R0[i], R1[i]);
+                        codes_to_bf16x2(__byte_perm(wa, wb, 0x7632), R0);       // channels 8..15
+                        codes_to_bf16x2(__byte_perm(wc, wd, 0x7632), R1);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) mma_bf16(acc[8 + i], PA[2 * kt], PB[2 * kt], PA[2 * kt + 1], PB[2 * kt + 1], R0[i], R1[i]);
+                        // row sums of P' (the magic +128 of every raw V value comes back out through them)
+                        mma_bf16(acc_rs, PA[2 * kt], PB[2 * kt], PA[2 * kt + 1], PB[2 * kt + 1], 0x3F803F80u, 0x3F803F80u);
+                        // zero-point bias: column n = scale group n (n < 4), B[k = token][n] = vz[token][n]
+                        uint32_t z0 = 0u, z1 = 0u;
+                        if (g < 4) {
+                            z0 = (uint32_t)*reinterpret_cast<const uint16_t *>(vzp + ta * H * 8 + 2 * g)
+                               | ((uint32_t)*reinterpret_cast<const uint16_t *>(vzp + (ta + 1) * H * 8 + 2 * g) << 16);
+                            z1 = (uint32_t)*reinterpret_cast<const uint16_t *>(vzp + (ta + 8) * H * 8 + 2 * g)
+                               | ((uint32_t)*reinterpret_cast<const uint16_t *>(vzp + (ta + 9) * H * 8 + 2 * g) << 16);
+                        }
+                        mma_bf16(acc_vz, P[2 * kt], P[2 * kt], P[2 * kt + 1], P[2 * kt + 1], z0, z1);
+                    }
+                } else {
+#pragma unroll
+                    for (int kt = 0; kt < 2; ++kt) {
+                        uint32_t Vr[2][16];
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int ta = 16 * kt + 8 * half + 2 * j, tb = ta + 1;
+                            const uint32_t wa = *reinterpret_cast<const uint32_t *>(vm + ta * TS + 4 * g);
+                            const uint32_t wb = *reinterpret_cast<const uint32_t *>(vm + tb * TS + 4 * g);
+                            const uint32_t ea = vsc[ta * H * 4 + (g >> 1)], eb2 = vsc[tb * H * 4 + (g >> 1)];
+                            const uint32_t za = *reinterpret_cast<const uint16_t *>(vzp + ta * H * 8 + 2 * (g >> 1));
+                            const uint32_t zb = *reinterpret_cast<const uint16_t *>(vzp + tb * H * 8 + 2 * (g >> 1));
+                            const uint32_t vs2 = (((ea | (eb2 << 16)) ^ 0x00800080u) & 0x00FF00FFu) << 7;   // 2^(e+1) pair
+                            const uint32_t vz2 = za | (zb << 16);
+                            const uint32_t vs_p0 = hmul2_bf16(vs2, 0x3F003F00u);    // * 2^-1
+                            const uint32_t vs_p1 = hmul2_bf16(vs2, 0x3E003E00u);    // * 2^-3
+                            const uint32_t vs_p2 = hmul2_bf16(vs2, 0x3D003D00u);    // * 2^-5
+                            uint32_t R[8];
+                            const uint32_t K128 = 0x43004300u;
+                            codes_to_bf16x2(__byte_perm(wa, wb, 0x5410), R);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int pc = pos_class(i);
+                                Vr[half][i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
+                            }
+                            codes_to_bf16x2(__byte_perm(wa, wb, 0x7632), R);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int pc = pos_class(i);
+                                Vr[half][8 + i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) mma_bf16(acc[i], P[2 * kt], 0u, P[2 * kt + 1], 0u, Vr[0][i], Vr[1][i]);
+                    }
                 }
             }
-            // release the stage
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
         }
-
-        // ---- epilogue state hand-off happens after the CTA-wide barrier below ----
-        // park the state in registers; nothing to do here
-        if (aborted) { m_run = -INFINITY; l_run = 0.f; }
-
-        // Wait for every warp (and the producer) before the ring memory is reused as scratch.
-        __syncthreads();
-        float l_tot = l_run;
-        l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 1);
-        l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 2);
-        float *scratch = reinterpret_cast<float *>(s_stage);             // [NCW][32 lanes][34]
-        if (GS > 1) {
-            float *my = scratch + ((size_t)warp * 32 + lane) * 34;
-            if (gsel > 0) {
-                my[0] = m_run; my[1] = l_tot;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) { my[2 + 2 * i] = acc[i][0]; my[3 + 2 * i] = acc[i][1]; }
-            }
-        }
-        __syncthreads();
-        if (gsel == 0) {
-            for (int o = 1; o < GS; ++o) {
-                const float *ot = scratch + ((size_t)(o * H + h) * 32 + lane) * 34;
-                const float m2 = ot[0], l2 = ot[1];
-                const float mn = fmaxf(m_run, m2);
-                const float mu = (mn == -INFINITY) ? 0.f : mn;
-                const float c1 = fast_exp2((m_run - mu) * LOG2E), c2 = fast_exp2((m2 - mu) * LOG2E);
-                l_tot = l_tot * c1 + l2 * c2;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    acc[i][0] = acc[i][0] * c1 + ot[2 + 2 * i] * c2;
-                    acc[i][1] = acc[i][1] * c1 + ot[3 + 2 * i] * c2;
-                }
-                m_run = mn;
-            }
-            if (g < p.gqa) {
-                const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-                float *dst = p.al + (int64_t)b * p.al_sb + (int64_t)(h * p.gqa + g) * p.al_sh + (int64_t)split * p.al_ss;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    dst[32 * j + i] = acc[i][0] * inv;                   // column 2j   -> channel 16*(2j) + i
-                    dst[32 * j + 16 + i] = acc[i][1] * inv;              // column 2j+1 -> channel 16*(2j+1) + i
-                }
-                if (j == 0) dst[HD] = l_tot > 0.f ? m_run + logf(l_tot) : -INFINITY;
-            }
-        }
-        return;
+        // release the stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * s);
     }
-    // producer falls through to the two CTA-wide barriers of the epilogue
+
+    // ---- epilogue: finalize this lane's 32 output channels, merge warps that share a head ----
+    // Every lane ends up with outv[0..15] = channels 32j + i and outv[16..31] = channels 32j + 16 + i of
+    // one (head, split) row, un-normalised; `useful` marks the lanes whose row is real.
+    float l_tot = l_run;
+    l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 1);
+    l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 2);
+    float outv[32];
+    bool useful;
+    if (VFOLD) {
+        // lane (g, j): columns 2j, 2j+1 are channels of scale group j; row g has group g/4, row g+8 group 2+g/4
+        const bool lo_row = (g >> 2) == j, hi_row = (2 + (g >> 2)) == j;
+        useful = row_ok && (lo_row || hi_row);
+        const float rs = hi_row ? acc_rs[2] : acc_rs[0];
+        // bias of (head, group j) sits in lane (g, j/2), register j&1
+        const float b0 = __shfl_sync(0xFFFFFFFFu, acc_vz[0], (lane & ~3) | (j >> 1));
+        const float b1 = __shfl_sync(0xFFFFFFFFu, acc_vz[1], (lane & ~3) | (j >> 1));
+        const float bias = (j & 1) ? b1 : b0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float f = 0.5f / (float)(1 << (2 * pos_class(i & 7)));
+            const float a0 = hi_row ? acc[i][2] : acc[i][0], a1 = hi_row ? acc[i][3] : acc[i][1];
+            outv[i] = fmaf(a0 - 128.f * rs, f, bias);
+            outv[16 + i] = fmaf(a1 - 128.f * rs, f, bias);
+        }
+    } else {
+        useful = row_ok;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { outv[i] = acc[i][0]; outv[16 + i] = acc[i][1]; }
+    }
+    const int out_head = h * p.gqa + row_head;
+
+    // Wait for every warp (and the producer) before the ring memory is reused as scratch.
     __syncthreads();
+    float *scratch = reinterpret_cast<float *>(s_stage);             // [NCW][32 lanes][34]
+    if (GS > 1 && gsel > 0) {
+        float *my = scratch + ((size_t)warp * 32 + lane) * 34;
+        my[0] = m_run; my[1] = l_tot;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) my[2 + i] = outv[i];
+    }
     __syncthreads();
+    if (gsel == 0) {
+        for (int o = 1; o < GS; ++o) {
+            const float *ot = scratch + ((size_t)(o * H + h) * 32 + lane) * 34;
+            const float m2 = ot[0], l2 = ot[1];
+            const float mn = fmaxf(m_run, m2);
+            const float mu = (mn == -INFINITY) ? 0.f : mn;
+            const float c1 = fast_exp2((m_run - mu) * LOG2E), c2 = fast_exp2((m2 - mu) * LOG2E);
+            l_tot = l_tot * c1 + l2 * c2;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) outv[i] = outv[i] * c1 + ot[2 + i] * c2;
+            m_run = mn;
+        }
+        if (useful) {
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+            float *dst = p.al + (int64_t)b * p.al_sb + (int64_t)out_head * p.al_sh + (int64_t)split * p.al_ss;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                dst[32 * j + i] = outv[i] * inv;
+                dst[32 * j + 16 + i] = outv[16 + i] * inv;
+            }
+            const bool lse_writer = VFOLD ? (g < 4 && j == 0) : (j == 0);
+            if (lse_writer) dst[HD] = l_tot > 0.f ? m_run + logf(l_tot) : -INFINITY;
+        }
+    }
 }
 
 // =================================================================================================
@@ -603,15 +719,20 @@ struct S2Params {
     float sm_scale, logit_cap;
 };
 
-constexpr int S2_THREADS = 128;
+constexpr int S2_THREADS = 512;
+constexpr int S2_WARPS = S2_THREADS / 32;
 constexpr int S2_MAX_TAIL = 256;
+constexpr int S2_MAX_SPLITS = 1024;
 
+// One CTA per (query head, sequence).  Warps stripe over the bf16 residual rows for the logits,
+// then over the splits for the combine; every loop keeps many independent loads in flight,
+// because this kernel is pure latency (a few hundred KB through L2).
 __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Params p) {
     __shared__ float s_q[HD];
     __shared__ float s_logit[S2_MAX_TAIL];
-    __shared__ float s_red[S2_THREADS / 32];
-    __shared__ float s_acc[S2_THREADS / 32][HD];
-    __shared__ float s_wsum[S2_THREADS / 32];
+    __shared__ float s_w[S2_MAX_SPLITS];
+    __shared__ float s_red[S2_WARPS];
+    __shared__ float s_acc[S2_WARPS][HD];
     const int hq = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = hq / p.gqa;
@@ -619,14 +740,23 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
     int tail = p.b_tail_len ? p.b_tail_len[b] : 0;
     tail = max(0, min(tail, min(p.max_tail, S2_MAX_TAIL)));
     const int D = p.D;                                                   // == HD
+    const int per = (seq > 0 && p.S > 0) ? (((seq + p.S - 1) / p.S) + 31) / 32 * 32 : 0;
+    const int nsplit = per > 0 ? min(p.S, (seq + per - 1) / per) : 0;    // splits s with s*per < seq
+    const float *base = p.al + (int64_t)b * p.al_sb + (int64_t)hq * p.al_sh;
 
-    // ---- bf16 residual rows: fp32 attention of this q head ----
-    float t_max = -INFINITY, t_sum = 0.f, o_tail = 0.f;                  // o_tail: channel tid
+    // ---- issue the split log-sum-exp loads first, they are the longest dependency ----
+    float mloc = -INFINITY;
+    for (int s = tid; s < nsplit; s += S2_THREADS) {
+        const float l = base[(int64_t)s * p.al_ss + D];
+        s_w[s] = l;
+        mloc = fmaxf(mloc, l);
+    }
+    // ---- bf16 residual rows: logits of this q head ----
     if (tail > 0) {
         if (tid < D) s_q[tid] = __bfloat162float(p.q[(int64_t)b * p.q_sb + (int64_t)hq * p.q_sh + tid]);
         __syncthreads();
         const __nv_bfloat16 *kt = p.k_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
-        for (int r = warp; r < tail; r += S2_THREADS / 32) {
+        for (int r = warp; r < tail; r += S2_WARPS) {
             const uint2 kv = *reinterpret_cast<const uint2 *>(kt + (int64_t)r * p.t_st + 4 * lane);
             float d = s_q[4 * lane] * bf16_bits_to_f32(kv.x & 0xFFFFu) + s_q[4 * lane + 1] * bf16_bits_to_f32(kv.x >> 16)
                     + s_q[4 * lane + 2] * bf16_bits_to_f32(kv.y & 0xFFFFu) + s_q[4 * lane + 3] * bf16_bits_to_f32(kv.y >> 16);
@@ -638,52 +768,56 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
                 s_logit[r] = x;
             }
         }
-        __syncthreads();
-        for (int r = 0; r < tail; ++r) t_max = fmaxf(t_max, s_logit[r]);
-        const __nv_bfloat16 *vt = p.v_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
-        for (int r = 0; r < tail; ++r) {
-            const float w = __expf(s_logit[r] - t_max);
-            t_sum += w;
-            if (tid < D) o_tail += w * __bfloat162float(vt[(int64_t)r * p.t_st + tid]);
-        }
     }
-    const float tail_lse = t_sum > 0.f ? t_max + logf(t_sum) : -INFINITY;
-    if (t_sum > 0.f) o_tail /= t_sum;
-
-    // ---- packed splits: validity recomputed with the stage-1 rounding ----
-    const int per = seq > 0 ? (((seq + p.S - 1) / p.S) + 31) / 32 * 32 : 0;
-    const float *base = p.al + (int64_t)b * p.al_sb + (int64_t)hq * p.al_sh;
-    float mloc = -INFINITY;
-    for (int s = tid; s < p.S; s += S2_THREADS)
-        if (seq > 0 && (int64_t)s * per < seq) mloc = fmaxf(mloc, base[(int64_t)s * p.al_ss + D]);
+    __syncthreads();
+    // ---- global max over split lse values and residual logits ----
+    for (int r = tid; r < tail; r += S2_THREADS) mloc = fmaxf(mloc, s_logit[r]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, o));
     if (lane == 0) s_red[warp] = mloc;
     __syncthreads();
-    float g_max = tail_lse;
-    for (int w = 0; w < S2_THREADS / 32; ++w) g_max = fmaxf(g_max, s_red[w]);
+    float g_max = s_red[0];
+#pragma unroll
+    for (int w = 1; w < S2_WARPS; ++w) g_max = fmaxf(g_max, s_red[w]);
     const float g_safe = (g_max == -INFINITY) ? 0.f : g_max;
+    __syncthreads();
+    // weights: splits enter with exp(lse_s - max), residual rows with exp(logit - max)
+    float wsum = 0.f;
+    for (int s = tid; s < nsplit; s += S2_THREADS) { const float w = __expf(s_w[s] - g_safe); s_w[s] = w; wsum += w; }
+    for (int r = tid; r < tail; r += S2_THREADS) { const float w = __expf(s_logit[r] - g_safe); s_logit[r] = w; wsum += w; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xFFFFFFFFu, wsum, o);
+    if (lane == 0) s_red[warp] = wsum;
+    __syncthreads();
+    float den = 0.f;
+#pragma unroll
+    for (int w = 0; w < S2_WARPS; ++w) den += s_red[w];
 
-    // warp w combines splits s = w, w+4, ...; lane owns channels lane, lane+32, lane+64, lane+96
-    // (rows of attn_logits are head_dim+1 floats apart, so only scalar loads are aligned)
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, wsum = 0.f;
-    for (int s = warp; s < p.S; s += S2_THREADS / 32) {
-        if (!(seq > 0 && (int64_t)s * per < seq)) break;
+    // ---- weighted sum: warp w takes splits / rows w, w+16, ...; lane owns channels lane + 32*i ----
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+    for (int s = warp; s < nsplit; s += S2_WARPS) {
         const float *row = base + (int64_t)s * p.al_ss;
-        const float w = __expf(row[D] - g_safe);
+        const float w = s_w[s];
         a0 += w * row[lane]; a1 += w * row[lane + 32]; a2 += w * row[lane + 64]; a3 += w * row[lane + 96];
-        wsum += w;
+    }
+    if (tail > 0) {
+        const __nv_bfloat16 *vt = p.v_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
+#pragma unroll 4
+        for (int r = warp; r < tail; r += S2_WARPS) {
+            const __nv_bfloat16 *row = vt + (int64_t)r * p.t_st;
+            const float w = s_logit[r];
+            a0 += w * __bfloat162float(row[lane]); a1 += w * __bfloat162float(row[lane + 32]);
+            a2 += w * __bfloat162float(row[lane + 64]); a3 += w * __bfloat162float(row[lane + 96]);
+        }
     }
     s_acc[warp][lane] = a0; s_acc[warp][lane + 32] = a1;
     s_acc[warp][lane + 64] = a2; s_acc[warp][lane + 96] = a3;
-    if (lane == 0) s_wsum[warp] = wsum;
     __syncthreads();
     if (tid < D) {
-        float acc = 0.f, den = 0.f;
-        for (int w = 0; w < S2_THREADS / 32; ++w) { acc += s_acc[w][tid]; den += s_wsum[w]; }
-        const float tw = t_sum > 0.f ? __expf(tail_lse - g_safe) : 0.f;
-        acc += tw * o_tail;
-        den += tw;
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < S2_WARPS; ++w) acc += s_acc[w][tid];
         const float out = acc / (den > 0.f ? den : 1.f);
         if (p.o_bf16) reinterpret_cast<__nv_bfloat16 *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = __float2bfloat16_rn(out);
         else reinterpret_cast<float *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = out;
@@ -740,6 +874,7 @@ static int validate_decode(const ommx_decode_args *a) {
     if (a->packed_start_offset != 0) return fail(OMMX_E_UNSUPPORTED, "decode: packed_start_offset must be 0");
     if (a->seg_group_base < 0) return fail(OMMX_E_ARG, "decode: seg_group_base=%d", a->seg_group_base);
     if (a->num_kv_splits < 1) return fail(OMMX_E_ARG, "decode: num_kv_splits=%d", a->num_kv_splits);
+    if (a->num_kv_splits > S2_MAX_SPLITS) return fail(OMMX_E_UNSUPPORTED, "decode: num_kv_splits=%d (max %d)", a->num_kv_splits, S2_MAX_SPLITS);
     if (a->max_tail_len > S2_MAX_TAIL) return fail(OMMX_E_UNSUPPORTED, "decode: max_tail_len=%d (max %d)", a->max_tail_len, S2_MAX_TAIL);
     if (a->max_tail_len > 0 && (!a->k_tail || !a->v_tail || !a->b_tail_len))
         return fail(OMMX_E_ARG, "decode: max_tail_len>0 needs k_tail, v_tail and b_tail_len");
@@ -769,6 +904,20 @@ static size_t stage1_smem(const S1Params &p) {
            + 2 * NSTAGES * 8 + 16;
 }
 
+template <int KOUT, bool VFOLD>
+static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st) {
+    static size_t attr_smem = 0;                       // one per instantiation
+    if (smem > attr_smem) {
+        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel<KOUT, VFOLD>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_smem = smem;
+    }
+    decode_stage1_kernel<KOUT, VFOLD><<<grid, S1_THREADS, smem, st>>>(p);
+    OMMX_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
 static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     if (a->max_seq_len <= 0) return 0;                                   // tail-only decode
     const ommx_kv_planes &pl = a->planes;
@@ -796,17 +945,13 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.gb_bytes = p.o_ov + H * 128 * (p.nb > 0 ? p.nb : 0);
     p.gb_bytes = (p.gb_bytes + 127) / 128 * 128;
     p.stage_bytes = p.GS * p.gb_bytes;
+    p.abl = a->abl_flags;
     const size_t smem = stage1_smem(p);
-    static size_t attr_smem = 0;
-    if (smem > attr_smem) {
-        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_smem = smem;
-    }
     dim3 grid(a->num_kv_splits, a->batch);
-    decode_stage1_kernel<<<grid, S1_THREADS, smem, st>>>(p);
-    OMMX_CUDA_TRY(cudaGetLastError());
-    count_launch();
-    return 0;
+    const bool vfold = p.gqa <= 4;
+    if (p.k_out == 6) return vfold ? launch_s1<6, true>(p, grid, smem, st) : launch_s1<6, false>(p, grid, smem, st);
+    if (p.k_out == 0) return vfold ? launch_s1<0, true>(p, grid, smem, st) : launch_s1<0, false>(p, grid, smem, st);
+    return vfold ? launch_s1<-1, true>(p, grid, smem, st) : launch_s1<-1, false>(p, grid, smem, st);
 }
 
 static int launch_stage2(const ommx_decode_args *a, cudaStream_t st) {
