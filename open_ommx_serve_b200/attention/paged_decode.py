@@ -26,7 +26,7 @@ from .pack import planes_struct
 _LAUNCHES = {"stage1": 0, "bitmap": 0, "abl": 0}
 
 ABL_FLAG_NAMES = ("OMMX_ABL_NO_OUTLIER", "OMMX_ABL_V_NODEQUANT", "OMMX_ABL_K_NODEQUANT",
-                  "OMMX_ABL_NO_UNPACK")
+                  "OMMX_ABL_NO_UNPACK")          # here bit 3 streams the planes and computes nothing
 RECIPE_ALTERING_ENV_PREFIXES = ("OMMX_ABL_", "OMMX_W_ABL_")
 RECIPE_ALTERING_ENV_KEYS = ("OMMX_ATTN_V_BF16", "OMMX_ATTN_FP8_QK")
 
@@ -271,7 +271,7 @@ def ommx_paged_decode_attention_canonical(
     a.sm_scale, a.logit_cap = float(sm_scale), float(logit_cap)
     a.status = None if status is None else status.data_ptr()
     # ablation knobs (differential timing only; recorded so a leaked export cannot pass as served)
-    abl = sum(1 << i for i, n in enumerate(ABL_FLAG_NAMES[:3]) if env_truthy(os.environ.get(n)))
+    abl = sum(1 << i for i, n in enumerate(ABL_FLAG_NAMES) if env_truthy(os.environ.get(n)))
     a.abl_flags = abl
     _LAUNCHES["abl"] |= abl
     with torch.cuda.device(q.device):

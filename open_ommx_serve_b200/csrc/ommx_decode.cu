@@ -38,7 +38,7 @@ constexpr int DT_ROWS = 34;             // 32 tokens + zp row + (-128) row
 constexpr int DT_BYTES = DT_ROWS * DT_STRIDE;
 constexpr int MAX_SPLIT_GROUPS = 512;   // groups one CTA can index (16K tokens per split)
 constexpr int MAX_SPLIT_PAGES = 2048;
-constexpr uint32_t SPIN_LIMIT = 1u << 24;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // about a second of SM clock: the wait has failed
 
 struct S1Params {
     const __nv_bfloat16 *q;
@@ -80,12 +80,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false (and the caller raises OMMX_ST_TIMEOUT) instead of spinning forever.
+// try_wait already parks the warp in hardware for a short while.  The limit is counted on the SM
+// clock (cheap to read); nanosleep or the global timer in this loop would put their own latency
+// on every producer/consumer hand-off.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) __nanosleep(32);
+    const long long t_end = clock64() + WAIT_LIMIT_CYCLES;
+#pragma unroll 1
+    for (uint32_t i = 1;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0 && clock64() > t_end) return false;
     }
-    return false;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -138,7 +145,7 @@ __device__ __forceinline__ void codes_to_bf16x2(uint32_t w, uint32_t (&r)[8]) {
 // Ablation bits (differential timing only, they break parity; mirror of the reference's
 // OMMX_ABL_* knobs, paged_decode.py:3267-3279): 1 = skip the outlier splice, 2 = skip V dequant
 // and P.V, 4 = skip the K code dequant and its MMAs.
-constexpr int ABL_NO_OUTLIER = 1, ABL_NO_V = 2, ABL_NO_K = 4;
+constexpr int ABL_NO_OUTLIER = 1, ABL_NO_V = 2, ABL_NO_K = 4, ABL_NO_COMPUTE = 8;   // 8: stream the planes only
 
 // KOUT: outliers per K vector known at compile time (static, unrolled splice) or -1 (runtime).
 // VFOLD: GQA groups of at most 4 query heads.  The 16 MMA rows are (query head, V scale group)
@@ -171,49 +178,89 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
     // ---- shared memory carve-up ----
     uint8_t *s_stage = smem;                                            // NSTAGES * stage_bytes
     uint8_t *s_tiles = s_stage + NSTAGES * p.stage_bytes;               // NCW * DT_BYTES
-    int32_t *s_slots = reinterpret_cast<int32_t *>(s_tiles + NCW * DT_BYTES);
-    int32_t *s_pages = s_slots + MAX_SPLIT_GROUPS;
-    float *s_lut = reinterpret_cast<float *>(s_pages + MAX_SPLIT_PAGES);
+    int32_t *s_tab = reinterpret_cast<int32_t *>(s_tiles + NCW * DT_BYTES);   // page ids, then group slots
+    float *s_lut = reinterpret_cast<float *>(s_tab + MAX_SPLIT_PAGES + MAX_SPLIT_GROUPS);
     uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[NSTAGES], empty[NSTAGES]
     int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * NSTAGES);
     const uint32_t bar_full = smem_u32(s_bar), bar_empty = smem_u32(s_bar + NSTAGES);
 
-    // ---- prologue: tables, LUT, barriers ----
-    {
-        const int g0 = p.seg_group_base + t0 / 32;                      // first logical group
-        for (int i = threadIdx.x; i < ngroups; i += S1_THREADS) {
-            int64_t s = load_index(p.r2g, p.tbl64, (int64_t)b * p.r2g_sb + g0 + i);
-            if (s < 0 || s >= p.num_slots) { or_status(p.status, OMMX_ST_BAD_GROUP); s = 0; }
-            s_slots[i] = (int)s;
+    // ---- prologue: LUT, barriers (the producer warp alone loads the page / slot tables) ----
+    if (threadIdx.x < 16) {
+        const int c = threadIdx.x;
+        const int mi = ((c >> 1) & 3) * 2 + (c & 1);                    // exp*2 + mant
+        const float mag = mi == 0 ? 0.f : (mi == 1 ? .5f : (float)(2 + (mi & 1)) * (float)(1 << (mi >> 1)) * 0.25f);
+        s_lut[c] = (c & 8) ? -mag : mag;
+    }
+    if (threadIdx.x == 32) {
+        for (int s = 0; s < NSTAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, NCW);
         }
-        const int npages = (ntok + p.ps - 1) / p.ps;
-        const int64_t pg0 = ((int64_t)g0 * 32) / p.ps;
-        for (int i = threadIdx.x; i < npages; i += S1_THREADS) {
-            int64_t pg = load_index(p.r2t, p.tbl64, (int64_t)b * p.r2t_sb + pg0 + i);
-            if (pg < 0 || pg >= p.num_pages) { or_status(p.status, OMMX_ST_BAD_PAGE); pg = 0; }
-            s_pages[i] = (int)pg;
-        }
-        if (threadIdx.x < 16) {
-            const int c = threadIdx.x;
-            const int mi = ((c >> 1) & 3) * 2 + (c & 1);                // exp*2 + mant
-            const float mag = mi == 0 ? 0.f : (mi == 1 ? .5f : (float)(2 + (mi & 1)) * (float)(1 << (mi >> 1)) * 0.25f);
-            s_lut[c] = (c & 8) ? -mag : mag;
-        }
-        if (threadIdx.x == 0) {
-            for (int s = 0; s < NSTAGES; ++s) {
-                mbar_init(bar_full + 8 * s, 1);
-                mbar_init(bar_empty + 8 * s, NCW);
-            }
-            *s_abort = 0;
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     if (warp == NCW) {
         // =========================== producer warp ===========================
+        // Every lane owns up to MAXPASS fixed copy roles (group-in-stage, plane); the loop body is
+        // one table lookup, one multiply-add and one bulk copy per role, with no divergent paths,
+        // because this single warp's issue latency bounds how fast stages can be refilled.
         const int cpg = 4 * p.ppg + 6;                                  // copies per group
-        const uint32_t page_b = (uint32_t)p.ps * H;                     // rows*heads per page
+        const uint32_t page_b = (uint32_t)p.ps * H;                     // (token, head) rows per page
+        constexpr int MAXPASS = 6;
+        const uint8_t *d_src[MAXPASS];
+        uint32_t d_unit[MAXPASS], d_dst[MAXPASS];
+        int d_tbase[MAXPASS], d_tmul[MAXPASS], d_gi[MAXPASS], d_tok0[MAXPASS];
+        uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
+#pragma unroll
+        for (int ps_ = 0; ps_ < MAXPASS; ++ps_) {
+            const int c = lane + 32 * ps_;
+            d_unit[ps_] = 0; d_src[ps_] = nullptr; d_dst[ps_] = 0; d_tbase[ps_] = 0; d_tmul[ps_] = 0; d_gi[ps_] = 0; d_tok0[ps_] = 0;
+            if (c < GS * cpg) {
+                const int gi = c / cpg, ci = c - gi * cpg;
+                d_gi[ps_] = gi;
+                const uint32_t gbo = (uint32_t)gi * p.gb_bytes;
+                if (ci < 4 * p.ppg) {
+                    const int pg = ci >> 2, plane = ci & 3;
+                    const uint32_t w = plane < 2 ? 32u : (plane == 2 ? 4u : 8u);
+                    d_src[ps_] = plane == 0 ? p.k_base : (plane == 1 ? p.v_main : (plane == 2 ? p.v_scale : p.v_zp));
+                    d_unit[ps_] = page_b * w;
+                    d_dst[ps_] = gbo + (plane == 0 ? 0u : (plane == 1 ? (uint32_t)p.o_vm : (plane == 2 ? (uint32_t)p.o_vs : (uint32_t)p.o_vz)))
+                               + (uint32_t)pg * page_b * w;
+                    d_tbase[ps_] = pg; d_tmul[ps_] = p.ppg; d_tok0[ps_] = pg * p.ps;
+                } else {
+                    const int gp = ci - 4 * p.ppg;
+                    const bool on = gp < 2 || (k_out > 0 && (gp >= 4 || p.use_map));
+                    if (on) {
+                        const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 512u : (gp == 5 ? 128u * p.nb : 256u));
+                        d_src[ps_] = gp == 0 ? p.k_scale : (gp == 1 ? p.k_zp : (gp == 2 ? p.k_ms : (gp == 3 ? p.k_mc : (gp == 4 ? p.k_obmp : p.k_oval))));
+                        d_unit[ps_] = (uint32_t)H * w;
+                        d_dst[ps_] = gbo + (uint32_t)(gp == 0 ? p.o_ks : (gp == 1 ? p.o_kz : (gp == 2 ? p.o_ms : (gp == 3 ? p.o_mc : (gp == 4 ? p.o_bm : p.o_ov)))));
+                        d_tbase[ps_] = MAX_SPLIT_PAGES; d_tmul[ps_] = 1;
+                    }
+                }
+            }
+            full_total += d_unit[ps_];
+        }
+        full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
+        {   // page ids first (s_tab[0..)), group slots behind them
+            const int g0 = p.seg_group_base + t0 / 32;                  // first logical group
+            const int npages = (ntok + p.ps - 1) / p.ps;
+            const int64_t pg0 = ((int64_t)g0 * 32) / p.ps;
+            for (int i = lane; i < npages; i += 32) {
+                int64_t pg = load_index(p.r2t, p.tbl64, (int64_t)b * p.r2t_sb + pg0 + i);
+                if (pg < 0 || pg >= p.num_pages) { or_status(p.status, OMMX_ST_BAD_PAGE); pg = 0; }
+                s_tab[i] = (int)pg;
+            }
+            for (int i = lane; i < ngroups; i += 32) {
+                int64_t sl = load_index(p.r2g, p.tbl64, (int64_t)b * p.r2g_sb + g0 + i);
+                if (sl < 0 || sl >= p.num_slots) { or_status(p.status, OMMX_ST_BAD_GROUP); sl = 0; }
+                s_tab[MAX_SPLIT_PAGES + i] = (int)sl;
+            }
+            __syncwarp();
+        }
+        const int whole_groups = ntok / 32;
         for (int it = 0; it < n_iters; ++it) {
             const int s = it % NSTAGES;
             const uint32_t ph = (it / NSTAGES) & 1;
@@ -221,43 +268,26 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
             }
-            const int ng = min(GS, ngroups - it * GS);
-            // transaction bytes of this stage
-            uint32_t total = 0;
-            for (int gi = 0; gi < ng; ++gi) {
-                const int lg = it * GS + gi;
-                const int vp = min(p.ppg, (ntok - 32 * lg + p.ps - 1) / p.ps);
-                total += (uint32_t)vp * page_b * (32 + 32 + 4 + 8) + (uint32_t)H * (128 + 256);
-                if (k_out > 0) total += (uint32_t)H * (512 + 128 * p.nb) + (p.use_map ? (uint32_t)H * 512 : 0u);
+            const int lg0 = it * GS;
+            uint32_t total = full_total;
+            if (lg0 + GS > whole_groups) {                              // last stage: fewer groups or a partial group
+                uint32_t mine = 0;
+#pragma unroll
+                for (int ps_ = 0; ps_ < MAXPASS; ++ps_) {
+                    const int lg = lg0 + d_gi[ps_];
+                    if (d_unit[ps_] && lg < ngroups && 32 * lg + d_tok0[ps_] < ntok) mine += d_unit[ps_];
+                }
+                total = __reduce_add_sync(0xFFFFFFFFu, mine);
             }
             if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
             __syncwarp();
             const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
-            for (int c = lane; c < ng * cpg; c += 32) {
-                const int gi = c / cpg, ci = c - gi * cpg;
-                const int lg = it * GS + gi;
-                const uint32_t gb = sbase + (uint32_t)gi * p.gb_bytes;
-                if (ci < 4 * p.ppg) {
-                    const int pg = ci >> 2, plane = ci & 3;
-                    if (32 * lg + pg * p.ps >= ntok) continue;          // page beyond the live length
-                    const int64_t page = s_pages[lg * p.ppg + pg];
-                    const uint32_t rows = (uint32_t)pg * page_b;        // (token,head) rows before this page
-                    if (plane == 0) bulk_g2s(gb + rows * 32, p.k_base + page * page_b * 32, page_b * 32, bar_full + 8 * s);
-                    else if (plane == 1) bulk_g2s(gb + p.o_vm + rows * 32, p.v_main + page * page_b * 32, page_b * 32, bar_full + 8 * s);
-                    else if (plane == 2) bulk_g2s(gb + p.o_vs + rows * 4, p.v_scale + page * page_b * 4, page_b * 4, bar_full + 8 * s);
-                    else bulk_g2s(gb + p.o_vz + rows * 8, p.v_zp + page * page_b * 8, page_b * 8, bar_full + 8 * s);
-                } else {
-                    const int gp = ci - 4 * p.ppg;
-                    const int64_t slot = s_slots[lg];
-                    const int64_t e = slot * H;                         // (slot, head) rows before
-                    if (gp == 0) bulk_g2s(gb + p.o_ks, p.k_scale + e * 128, H * 128, bar_full + 8 * s);
-                    else if (gp == 1) bulk_g2s(gb + p.o_kz, p.k_zp + e * 256, H * 256, bar_full + 8 * s);
-                    else if (k_out > 0) {
-                        if (gp == 2) { if (p.use_map) bulk_g2s(gb + p.o_ms, p.k_ms + e * 256, H * 256, bar_full + 8 * s); }
-                        else if (gp == 3) { if (p.use_map) bulk_g2s(gb + p.o_mc, p.k_mc + e * 256, H * 256, bar_full + 8 * s); }
-                        else if (gp == 4) bulk_g2s(gb + p.o_bm, p.k_obmp + e * 512, H * 512, bar_full + 8 * s);
-                        else bulk_g2s(gb + p.o_ov, p.k_oval + e * 128 * p.nb, H * 128 * p.nb, bar_full + 8 * s);
-                    }
+#pragma unroll
+            for (int ps_ = 0; ps_ < MAXPASS; ++ps_) {
+                const int lg = lg0 + d_gi[ps_];
+                if (d_unit[ps_] && lg < ngroups && 32 * lg + d_tok0[ps_] < ntok) {
+                    const int64_t idx = s_tab[d_tbase[ps_] + lg * d_tmul[ps_]];
+                    bulk_g2s(sbase + d_dst[ps_], d_src[ps_] + idx * d_unit[ps_], d_unit[ps_], bar_full + 8 * s);
                 }
             }
         }
@@ -334,7 +364,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
             break;
         }
         const int lg = it * GS + gsel;                               // local group of this warp
-        if (lg < ngroups) {
+        if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
             uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
             const uint8_t *kb = gb + h * 32;                         // + token*TS
             const uint8_t *vm = gb + p.o_vm + h * 32;

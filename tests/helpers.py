@@ -125,6 +125,9 @@ class Case:
             pooled = {"k_base": np.zeros((0, page_size, H, D // 4), np.uint8), "v_main": np.zeros((0, page_size, H, D // 4), np.uint8),
                       "v_scale": np.zeros((0, page_size, H, D // 32), np.int8), "v_zp": np.zeros((0, page_size, H, D // 32), np.uint16),
                       "k_scale": np.zeros((0, H, D), np.int8), "k_zp": np.zeros((0, H, D), np.uint16)}
+            if k > 0:
+                pooled.update(k_obmp=np.zeros((0, H, D, 4), np.uint8), k_oval=np.zeros((0, H, D, (k + 1) // 2), np.uint8),
+                              k_fp4_mapscale=np.zeros((0, H, D), np.uint16), k_fp4_mapcenter=np.zeros((0, H, D), np.uint16))
         self.pooled_np = pooled
         self.planes = {n: plane_to_torch(n, a, dev) for n, a in pooled.items()}
         self.req_to_token = torch.from_numpy(r2t).to(tables_dtype).to(dev)
