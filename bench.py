@@ -281,8 +281,7 @@ def timed_graph(fn, steps, warmup, flush, torch):
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
-    from open_ommx_serve_b200 import _lib
-    from open_ommx_serve_b200.attention import paged_decode as PD
+    from open_ommx_serve_b200 import _lib, sharding
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -307,7 +306,7 @@ def run_ours(args, rank, world, local_rank):
         for i in range(LAYERS):
             stack.decode_layer(i)
             if world > 1:
-                dist.all_gather_into_tensor(gathered[i], stack.o[i])
+                sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
 
     def step_stage1():
         for i in range(LAYERS):
@@ -374,7 +373,7 @@ def run_ours(args, rank, world, local_rank):
             L["v_tail"][:, new_row].copy_(kv_host[i][1], non_blocking=True)
             stack.decode_layer(i, q=q_dev)
             if world > 1:
-                dist.all_gather_into_tensor(gathered[i], stack.o[i])
+                sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
             o_host[i].copy_(stack.o[i], non_blocking=True)
 
     for _ in range(max(3, args.warmup)):
