@@ -27,7 +27,7 @@ def _run_and_check(case, **kw):
     np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=lse_atol, rtol=0)
     f_o, f_lse = case.oracle()
     check_fp32(o, f_o, ctx="fp32 " + ctx)
-    np.testing.assert_allclose(lse.cpu().numpy(), f_lse, atol=max(5e-2, lse_atol), rtol=0)
+    np.testing.assert_allclose(lse.cpu().numpy(), f_lse, atol=max(5e-2, 1.5 * lse_atol), rtol=0)
     return o, lse
 
 
@@ -80,7 +80,7 @@ def test_decode_head_geometries(H, Hq):
 @pytest.mark.parametrize("k", [0, 2, 4, 6, 8])
 @pytest.mark.parametrize("mag", [4.0, 30.0])
 def test_decode_outlier_sweep(k, mag):
-    _run_and_check(Case([2048], seed=k + 1, k=k, mag=mag), lse_atol=2e-2 if mag < 20 else 8e-2)
+    _run_and_check(Case([2048], seed=k + 1, k=k, mag=mag), lse_atol=2e-2 if mag < 20 else 0.15)
 
 
 def test_decode_base_shared_outlier_map():
