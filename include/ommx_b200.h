@@ -141,6 +141,22 @@ int ommx_b200_decode_stage1(const ommx_decode_args *args, void *stream);   /* sp
 int ommx_b200_decode_stage2(const ommx_decode_args *args, void *stream);   /* attn_logits + tail -> o,lse */
 
 /*
+ * ommx_b200_decode with the split workspace taken from a fixed 8 MiB array inside the library
+ * instead of args->attn_logits (which is ignored, as are its strides).  This entry point has no
+ * counterpart in the reference.  It is for hosts that must not allocate device memory while
+ * serving - an engine whose memory pool is frozen after start-up, or a plug-in that receives
+ * buffers but no allocator: it calls no cudaMalloc/cudaFree and nothing that allocates.
+ * Limit: batch * n_q_heads * num_kv_splits * (head_dim + 1) <= 2 Mi floats, else OMMX_E_ARG.
+ * The first call on each device looks up the array's device address (one runtime query, no
+ * allocation); make that first call outside any stream capture.  All calls on a device share
+ * the one array: two calls that overlap on the GPU (different streams) race; calls ordered on
+ * one stream are safe.  Nothing needs clearing between calls - stage 2 reads only the split
+ * slots stage 1 of the same call wrote - and the array keeps its last contents otherwise.
+ * Every GPU that loads the library holds the 8 MiB until the process exits.
+ */
+int ommx_b200_decode_static_ws(const ommx_decode_args *args, void *stream);
+
+/*
  * Split count this library prefers for (max context, batch, local kv heads) on the current
  * device.  Replaces _auto_num_kv_splits (attention/paged_decode.py:409-461), which callers
  * use to size attn_logits once.

@@ -63,6 +63,7 @@ SYMBOLS = {
     "ommx_b200_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_decode_stage1": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_decode_stage2": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "ommx_b200_decode_static_ws": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_auto_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
     "ommx_b200_min_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32]),
     "ommx_b200_merge_states": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,

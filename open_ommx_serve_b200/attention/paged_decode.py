@@ -139,6 +139,7 @@ def ommx_paged_decode_attention_canonical(
     seg_group_base: int = 0,
     status: Any = None,
     _stage: int = 0,
+    static_workspace: bool = False,
 ) -> None:
     """Decode attention of one query row per sequence. Writes ``o`` / ``lse`` in place.
 
@@ -151,6 +152,13 @@ def ommx_paged_decode_attention_canonical(
     is what CUDA-graph capture needs.  ``status`` (int32 ``[1]``, optional, not in the
     reference) collects device-side error bits instead of a trap.  ``_stage`` (1 or 2) runs one
     stage alone, for the benchmark's per-kernel timing.
+
+    ``static_workspace=True`` (not in the reference) is for callers that may not allocate on
+    the device while serving, e.g. under an engine whose memory pool is frozen after start-up:
+    ``attn_logits`` is neither needed nor created, the split partials go to an 8 MiB array built
+    into the library (``ommx_b200_decode_static_ws``).  ``batch * Hq * num_kv_splits * (D+1)`` must
+    stay within 2 Mi floats (``ValueError`` beyond); calls that overlap on the GPU share the array
+    and race; make the first call on a device outside stream capture.
     """
     lib = _lib.load()
     if not q.is_cuda:
@@ -220,12 +228,15 @@ def ommx_paged_decode_attention_canonical(
     if num_kv_splits is None:
         num_kv_splits = _auto_num_kv_splits(max(max_seq, 1), batch, device=q.device, kv_heads=n_kv_heads)
     num_kv_splits = max(1, int(num_kv_splits))
-    if attn_logits is None:
-        attn_logits = _make_attn_logits(batch, head_num, num_kv_splits + 1, D, q.device)
-    if int(attn_logits.shape[-1]) != D + 1 or attn_logits.stride(-1) != 1:
-        raise ValueError(f"attn_logits last dim must be head_dim+1={D + 1} and contiguous")
-    if int(attn_logits.shape[2]) < num_kv_splits:
-        raise ValueError(f"attn_logits holds {attn_logits.shape[2]} split slots, fewer than num_kv_splits={num_kv_splits}")
+    if static_workspace:
+        attn_logits = None
+    else:
+        if attn_logits is None:
+            attn_logits = _make_attn_logits(batch, head_num, num_kv_splits + 1, D, q.device)
+        if int(attn_logits.shape[-1]) != D + 1 or attn_logits.stride(-1) != 1:
+            raise ValueError(f"attn_logits last dim must be head_dim+1={D + 1} and contiguous")
+        if int(attn_logits.shape[2]) < num_kv_splits:
+            raise ValueError(f"attn_logits holds {attn_logits.shape[2]} split slots, fewer than num_kv_splits={num_kv_splits}")
     if q.dtype != torch.bfloat16:
         raise NotImplementedError(f"q dtype {q.dtype}: this build serves bfloat16 queries")
     if q.stride(-1) != 1 or o.stride(-1) != 1:
@@ -264,8 +275,9 @@ def ommx_paged_decode_attention_canonical(
     a.lse, a.lse_stride_b = lse.data_ptr(), int(lse.stride(0))
     if lse.dtype != torch.float32:
         raise ValueError("lse must be float32")
-    a.attn_logits = attn_logits.data_ptr()
-    a.al_stride_b, a.al_stride_h, a.al_stride_s = (int(s) for s in attn_logits.stride()[:3])
+    if attn_logits is not None:
+        a.attn_logits = attn_logits.data_ptr()
+        a.al_stride_b, a.al_stride_h, a.al_stride_s = (int(s) for s in attn_logits.stride()[:3])
     a.num_kv_splits, a.max_seq_len, a.max_tail_len = num_kv_splits, max_seq, max_tail
     a.seg_group_base, a.packed_start_offset = seg_group_base, start_offset
     a.sm_scale, a.logit_cap = float(sm_scale), float(logit_cap)
@@ -276,8 +288,12 @@ def ommx_paged_decode_attention_canonical(
     _LAUNCHES["abl"] |= abl
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
-        entry = (lib.ommx_b200_decode, lib.ommx_b200_decode_stage1, lib.ommx_b200_decode_stage2)[int(_stage)]
-        _lib.check(entry(a, stream), "ommx_b200_decode")
+        if static_workspace:
+            entry, what = lib.ommx_b200_decode_static_ws, "ommx_b200_decode_static_ws"
+        else:
+            entry = (lib.ommx_b200_decode, lib.ommx_b200_decode_stage1, lib.ommx_b200_decode_stage2)[int(_stage)]
+            what = "ommx_b200_decode"
+        _lib.check(entry(a, stream), what)
     _LAUNCHES["stage1"] += 1
     if bitmap_read:
         _LAUNCHES["bitmap"] += 1

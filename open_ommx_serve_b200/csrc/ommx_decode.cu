@@ -1055,6 +1055,63 @@ extern "C" int ommx_b200_decode(const ommx_decode_args *a, void *stream) {
     return ommx::launch_stage2(a, (cudaStream_t)stream);
 }
 
+// -------------------------------------------------------------------------------------------------
+// Decode with the split workspace owned by the library.
+//
+// Some hosts that embed this library may not allocate device memory at all on their serving path:
+// a runtime whose allocator has been frozen after start-up (every later cudaMalloc would fragment or
+// overrun a pool sized to the last megabyte), or a plug-in that is handed tensors but no allocator.
+// ommx_b200_decode needs a workspace for the per-split partial results; this entry point takes it
+// from a fixed array inside the library image instead, so the caller passes only inputs and outputs.
+// The array is part of the module: every GPU that loads the library holds its 8 MiB until exit.
+constexpr size_t STATIC_WS_FLOATS = (size_t)2 << 20;                      // 2 Mi floats = 8 MiB
+static __device__ __align__(256) float g_static_ws[STATIC_WS_FLOATS];
+
+// In host code the name g_static_ws is only a handle, not a device address; the address each
+// device gave the array is asked for once per device, with that device current, and kept.
+static int static_ws_address(float **out) {
+    static std::atomic<float *> cache[64];
+    int dev = -1;
+    OMMX_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return ommx::fail(OMMX_E_UNSUPPORTED, "decode_static_ws: device ordinal %d", dev);
+    float *ptr = cache[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
+        void *sym = nullptr;
+        OMMX_CUDA_TRY(cudaGetSymbolAddress(&sym, g_static_ws));
+        if (sym == nullptr) return ommx::fail(OMMX_E_CUDA, "decode_static_ws: the workspace symbol has no address on device %d", dev);
+        ptr = static_cast<float *>(sym);
+        cache[dev].store(ptr, std::memory_order_release);
+    }
+    *out = ptr;
+    return 0;
+}
+
+extern "C" int ommx_b200_decode_static_ws(const ommx_decode_args *a, void *stream) {
+    using namespace ommx;
+    if (!a) return fail(OMMX_E_ARG, "decode_static_ws: null args");
+    if (a->batch <= 0 || a->n_q_heads <= 0 || a->num_kv_splits <= 0)
+        return fail(OMMX_E_ARG, "decode_static_ws: batch=%d n_q_heads=%d num_kv_splits=%d", a->batch, a->n_q_heads, a->num_kv_splits);
+    const size_t row = (size_t)HD + 1;
+    const size_t need = (size_t)a->batch * a->n_q_heads * a->num_kv_splits * row;
+    if (need > STATIC_WS_FLOATS)
+        return fail(OMMX_E_ARG, "decode_static_ws: batch*n_q_heads*num_kv_splits*(head_dim+1) = %zu floats exceeds the "
+                                "built-in workspace of %zu floats (8 MiB); use ommx_b200_decode with your own attn_logits",
+                    need, (size_t)STATIC_WS_FLOATS);
+    float *ws = nullptr;
+    int rc = static_ws_address(&ws);
+    if (rc) return rc;
+    ommx_decode_args b = *a;
+    b.attn_logits = ws;
+    b.al_stride_s = (int64_t)row;
+    b.al_stride_h = (int64_t)a->num_kv_splits * (int64_t)row;
+    b.al_stride_b = (int64_t)a->n_q_heads * b.al_stride_h;
+    rc = validate_decode(&b);
+    if (rc) return rc;
+    rc = launch_stage1(&b, (cudaStream_t)stream);
+    if (rc) return rc;
+    return launch_stage2(&b, (cudaStream_t)stream);
+}
+
 extern "C" int ommx_b200_merge_states(const float *o_parts, const float *lse_parts, const int32_t *valid_lens,
                                       int32_t P, int32_t R, int32_t D, float *o, float *lse, void *stream) {
     using namespace ommx;
