@@ -30,8 +30,14 @@
 namespace ommx {
 
 constexpr int HD = 128;                 // head_dim this build serves
-constexpr int NCW = 8;                  // consumer warps
-constexpr int S1_THREADS = (NCW + 1) * 32;
+constexpr int NCW = 8;                  // (group, head) units in flight per CTA: 8 MMA warps + 8 decode warps
+constexpr int NDW = 11;                 // decode warps (stateless tile builders, items dealt round-robin)
+constexpr int PRODUCER_WARP = NCW + NDW;  // warp 19 streams the planes
+constexpr int S1_THREADS = (NCW + NDW + 1) * 32;
+// Register budget per role (setmaxnreg, warpgroup granularity).  Only what the CTA was launched with
+// can be moved around: 640 threads x 96 = 61440 >= 256*152 (MMA) + 384*56 (decode + producer) = 60416.
+#define OMMX_REGS_MMA "152"
+#define OMMX_REGS_DECODE "56"
 constexpr int NSTAGES = 4;
 constexpr int DT_STRIDE = 272;          // bytes per outlier-tile row (256 data + 16 pad)
 constexpr int DT_ROWS = 34;             // 32 tokens + zp row + (-128) row
@@ -60,6 +66,15 @@ struct S1Params {
     int32_t GS, gb_bytes, stage_bytes;
     int32_t o_vm, o_vs, o_vz, o_ks, o_kz, o_ms, o_mc, o_bm, o_ov;
 };
+
+// One bulk copy of a stage: source plane, bytes, destination inside the stage, and which table entry
+// (page id or group slot) selects the source block.
+struct __align__(16) CopyDesc {
+    const uint8_t *src;
+    uint32_t unit, dst;
+    int32_t tbase, tmul, gi, tok0;
+};
+constexpr int MAX_STAGE_COPIES = 8 * (4 * 4 + 6);                    // 8 groups per stage, 8-token pages
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -180,9 +195,11 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
     uint8_t *s_tiles = s_stage + NSTAGES * p.stage_bytes;               // NCW * DT_BYTES
     int32_t *s_tab = reinterpret_cast<int32_t *>(s_tiles + NCW * DT_BYTES);   // page ids, then group slots
     float *s_lut = reinterpret_cast<float *>(s_tab + MAX_SPLIT_PAGES + MAX_SPLIT_GROUPS);
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[NSTAGES], empty[NSTAGES]
-    int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * NSTAGES);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[NSTAGES], empty[NSTAGES], tile_full[NCW], tile_empty[NCW][NSTAGES]
+    int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * NSTAGES + (1 + NSTAGES) * NCW);
+    CopyDesc *s_desc = reinterpret_cast<CopyDesc *>(s_abort + 4);
     const uint32_t bar_full = smem_u32(s_bar), bar_empty = smem_u32(s_bar + NSTAGES);
+    const uint32_t bar_tfull = smem_u32(s_bar + 2 * NSTAGES), bar_tempty = smem_u32(s_bar + 2 * NSTAGES + NCW);
 
     // ---- prologue: LUT, barriers (the producer warp alone loads the page / slot tables) ----
     if (threadIdx.x < 16) {
@@ -194,54 +211,59 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
     if (threadIdx.x == 32) {
         for (int s = 0; s < NSTAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, NCW);
+            mbar_init(bar_empty + 8 * s, 2 * NCW);
+        }
+        for (int u = 0; u < NCW; ++u) {
+            mbar_init(bar_tfull + 8 * u, 1);
+            for (int k2 = 0; k2 < NSTAGES; ++k2) mbar_init(bar_tempty + 8 * (NSTAGES * u + k2), 1);
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    // Stage 2 is launched as a programmatic dependent: it may start its own prologue (residual-row
+    // logits, which do not depend on this kernel) as soon as SM resources free up, and waits for this
+    // grid to finish before it reads the split partials.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (warp == NCW) {
+    // ---- roles; each branch starts by resizing its warpgroups' register budget and never rejoins ----
+    if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
+    if (warp == PRODUCER_WARP) {
         // =========================== producer warp ===========================
-        // Every lane owns up to MAXPASS fixed copy roles (group-in-stage, plane); the loop body is
-        // one table lookup, one multiply-add and one bulk copy per role, with no divergent paths,
-        // because this single warp's issue latency bounds how fast stages can be refilled.
+        // Copy roles (group-in-stage, plane) are tabulated once in shared memory; the loop body is one
+        // descriptor load, one table lookup, one multiply-add and one bulk copy per role, with no
+        // divergent paths, because this single warp's issue latency bounds how fast stages refill.
         const int cpg = 4 * p.ppg + 6;                                  // copies per group
+        const int ncopies = GS * cpg;
         const uint32_t page_b = (uint32_t)p.ps * H;                     // (token, head) rows per page
-        constexpr int MAXPASS = 6;
-        const uint8_t *d_src[MAXPASS];
-        uint32_t d_unit[MAXPASS], d_dst[MAXPASS];
-        int d_tbase[MAXPASS], d_tmul[MAXPASS], d_gi[MAXPASS], d_tok0[MAXPASS];
         uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
-#pragma unroll
-        for (int ps_ = 0; ps_ < MAXPASS; ++ps_) {
-            const int c = lane + 32 * ps_;
-            d_unit[ps_] = 0; d_src[ps_] = nullptr; d_dst[ps_] = 0; d_tbase[ps_] = 0; d_tmul[ps_] = 0; d_gi[ps_] = 0; d_tok0[ps_] = 0;
-            if (c < GS * cpg) {
-                const int gi = c / cpg, ci = c - gi * cpg;
-                d_gi[ps_] = gi;
-                const uint32_t gbo = (uint32_t)gi * p.gb_bytes;
-                if (ci < 4 * p.ppg) {
-                    const int pg = ci >> 2, plane = ci & 3;
-                    const uint32_t w = plane < 2 ? 32u : (plane == 2 ? 4u : 8u);
-                    d_src[ps_] = plane == 0 ? p.k_base : (plane == 1 ? p.v_main : (plane == 2 ? p.v_scale : p.v_zp));
-                    d_unit[ps_] = page_b * w;
-                    d_dst[ps_] = gbo + (plane == 0 ? 0u : (plane == 1 ? (uint32_t)p.o_vm : (plane == 2 ? (uint32_t)p.o_vs : (uint32_t)p.o_vz)))
-                               + (uint32_t)pg * page_b * w;
-                    d_tbase[ps_] = pg; d_tmul[ps_] = p.ppg; d_tok0[ps_] = pg * p.ps;
-                } else {
-                    const int gp = ci - 4 * p.ppg;
-                    const bool on = gp < 2 || (k_out > 0 && (gp >= 4 || p.use_map));
-                    if (on) {
-                        const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 512u : (gp == 5 ? 128u * p.nb : 256u));
-                        d_src[ps_] = gp == 0 ? p.k_scale : (gp == 1 ? p.k_zp : (gp == 2 ? p.k_ms : (gp == 3 ? p.k_mc : (gp == 4 ? p.k_obmp : p.k_oval))));
-                        d_unit[ps_] = (uint32_t)H * w;
-                        d_dst[ps_] = gbo + (uint32_t)(gp == 0 ? p.o_ks : (gp == 1 ? p.o_kz : (gp == 2 ? p.o_ms : (gp == 3 ? p.o_mc : (gp == 4 ? p.o_bm : p.o_ov)))));
-                        d_tbase[ps_] = MAX_SPLIT_PAGES; d_tmul[ps_] = 1;
-                    }
+        for (int c = lane; c < ncopies; c += 32) {
+            CopyDesc d;
+            d.src = nullptr; d.unit = 0; d.dst = 0; d.tbase = 0; d.tmul = 0; d.gi = 0; d.tok0 = 0;
+            const int gi = c / cpg, ci = c - gi * cpg;
+            d.gi = gi;
+            const uint32_t gbo = (uint32_t)gi * p.gb_bytes;
+            if (ci < 4 * p.ppg) {
+                const int pg = ci >> 2, plane = ci & 3;
+                const uint32_t w = plane < 2 ? 32u : (plane == 2 ? 4u : 8u);
+                d.src = plane == 0 ? p.k_base : (plane == 1 ? p.v_main : (plane == 2 ? p.v_scale : p.v_zp));
+                d.unit = page_b * w;
+                d.dst = gbo + (plane == 0 ? 0u : (plane == 1 ? (uint32_t)p.o_vm : (plane == 2 ? (uint32_t)p.o_vs : (uint32_t)p.o_vz)))
+                      + (uint32_t)pg * page_b * w;
+                d.tbase = pg; d.tmul = p.ppg; d.tok0 = pg * p.ps;
+            } else {
+                const int gp = ci - 4 * p.ppg;
+                const bool on = gp < 2 || (k_out > 0 && (gp >= 4 || p.use_map));
+                if (on) {
+                    const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 512u : (gp == 5 ? 128u * p.nb : 256u));
+                    d.src = gp == 0 ? p.k_scale : (gp == 1 ? p.k_zp : (gp == 2 ? p.k_ms : (gp == 3 ? p.k_mc : (gp == 4 ? p.k_obmp : p.k_oval))));
+                    d.unit = (uint32_t)H * w;
+                    d.dst = gbo + (uint32_t)(gp == 0 ? p.o_ks : (gp == 1 ? p.o_kz : (gp == 2 ? p.o_ms : (gp == 3 ? p.o_mc : (gp == 4 ? p.o_bm : p.o_ov)))));
+                    d.tbase = MAX_SPLIT_PAGES; d.tmul = 1;
                 }
             }
-            full_total += d_unit[ps_];
+            s_desc[c] = d;
+            full_total += d.unit;
         }
         full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
         {   // page ids first (s_tab[0..)), group slots behind them
@@ -272,22 +294,22 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
             uint32_t total = full_total;
             if (lg0 + GS > whole_groups) {                              // last stage: fewer groups or a partial group
                 uint32_t mine = 0;
-#pragma unroll
-                for (int ps_ = 0; ps_ < MAXPASS; ++ps_) {
-                    const int lg = lg0 + d_gi[ps_];
-                    if (d_unit[ps_] && lg < ngroups && 32 * lg + d_tok0[ps_] < ntok) mine += d_unit[ps_];
+                for (int c = lane; c < ncopies; c += 32) {
+                    const CopyDesc d = s_desc[c];
+                    const int lg = lg0 + d.gi;
+                    if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) mine += d.unit;
                 }
                 total = __reduce_add_sync(0xFFFFFFFFu, mine);
             }
             if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
             __syncwarp();
             const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
-#pragma unroll
-            for (int ps_ = 0; ps_ < MAXPASS; ++ps_) {
-                const int lg = lg0 + d_gi[ps_];
-                if (d_unit[ps_] && lg < ngroups && 32 * lg + d_tok0[ps_] < ntok) {
-                    const int64_t idx = s_tab[d_tbase[ps_] + lg * d_tmul[ps_]];
-                    bulk_g2s(sbase + d_dst[ps_], d_src[ps_] + idx * d_unit[ps_], d_unit[ps_], bar_full + 8 * s);
+            for (int c = lane; c < ncopies; c += 32) {
+                const CopyDesc d = s_desc[c];
+                const int lg = lg0 + d.gi;
+                if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) {
+                    const int64_t idx = s_tab[d.tbase + lg * d.tmul];
+                    bulk_g2s(sbase + d.dst, d.src + idx * d.unit, d.unit, bar_full + 8 * s);
                 }
             }
         }
@@ -297,15 +319,177 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
         return;
     }
 
-    // =========================== consumer warps ===========================
+    // =========================== decode + MMA warps ===========================
+    // MMA warp w owns unit w = (group-in-stage, kv head) and its softmax state.  The decode warps are
+    // stateless: work item (iteration, unit) number n goes to decode warp n % NDW.
     const int g = lane >> 2, j = lane & 3;
-    const int h = warp % H, gsel = warp / H;
     const int TS = H * 32;                                          // bytes per token row (all heads)
-    uint8_t *tile = s_tiles + warp * DT_BYTES;
-    const uint32_t tile_s = smem_u32(tile);
     const float LOG2E = 1.4426950408889634f;
     const bool no_outlier = (p.abl & ABL_NO_OUTLIER) != 0;
 
+    if (warp >= NCW) {
+        // =========================== decode warps (phase A) ===========================
+        // Build a unit's outlier-delta tile one group ahead of its MMA warp: wait until the MMA warp
+        // has read the previous tile of that unit, write the new one, publish it.
+        const int dw = warp - NCW;
+        // this lane owns channels 4*lane + c
+        uint32_t pa_col[4];       // byte offset of the channel's column inside an outlier-tile row
+        float pa_f[4];            // 4^pc of the channel's slot
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int d = 4 * lane + c;
+            const int jj = d >> 5, wi = (d >> 4) & 1, i = d & 7, hi = (d >> 3) & 1;
+            pa_col[c] = 2u * (16 * (4 * wi + (i >> 1)) + 8 * (i & 1) + 2 * jj + hi);
+            pa_f[c] = (float)(1 << (2 * pos_class(i)));
+        }
+        if (dw < NCW) {           // item (0, dw) is this warp's: it is the first to touch tile dw
+            uint8_t *t0p = s_tiles + dw * DT_BYTES;
+            // row 33 = -128 in every column (never rewritten); clear the rest once
+            for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(t0p)[i] = 0u;
+            __syncwarp();
+            for (int i = lane; i < 64; i += 32) reinterpret_cast<uint32_t *>(t0p + 33 * DT_STRIDE)[i] = 0xC300C300u;
+            __syncwarp();
+        }
+        for (int n = dw; n < n_iters * NCW; n += NDW) {
+            const int it = n / NCW, unit = n % NCW;
+            const int h = unit % H, gsel = unit / H;
+            uint8_t *tile = s_tiles + unit * DT_BYTES;
+            const int s = it % NSTAGES;
+            const uint32_t ph = (it / NSTAGES) & 1;
+            if (!mbar_wait(bar_full + 8 * s, ph)) {
+                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+                break;
+            }
+            const int lg = it * GS + gsel;                           // local group of this unit
+            if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
+                // Tile `it` of a unit may be written once the MMA warp has read tile it-1.  Decode warps
+                // run up to NSTAGES groups ahead and the tiles of one unit are built by different warps,
+                // so "tile k was read" events rotate over NSTAGES barriers per unit (barrier k % NSTAGES,
+                // phase k / NSTAGES): the newest event a waiter can be missing is then always the one it
+                // waits for, never an older phase of the same parity.
+                uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
+                const uint8_t *kb = gb + h * 32;                     // + token*TS
+                const uint8_t *ksc = gb + p.o_ks + h * 128;
+                const uint8_t *kzp = gb + p.o_kz + h * 256;
+                if (it > 0 && !mbar_wait(bar_tempty + 8 * (NSTAGES * unit + ((it - 1) % NSTAGES)),
+                                         (uint32_t)((it - 1) / NSTAGES) & 1u)) {
+                    if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+                    break;
+                }
+            {
+                    const bool splice = k_out > 0 && !no_outlier;
+                    if (splice) {
+                        // clear token rows 0..31 (256 data bytes each)
+#pragma unroll
+                        for (int r2 = 0; r2 < 16; ++r2)
+                            *reinterpret_cast<uint4 *>(tile + (2 * r2 + (lane >> 4)) * DT_STRIDE + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
+                        __syncwarp();
+                    }
+                    const uint32_t e4 = *reinterpret_cast<const uint32_t *>(ksc + 4 * lane);
+                    const uint2 z4 = *reinterpret_cast<const uint2 *>(kzp + 8 * lane);
+                    uint2 ms4 = make_uint2(0, 0), mc4 = make_uint2(0, 0);
+                    uint4 bm4 = make_uint4(0, 0, 0, 0);
+                    uint32_t st[4] = {0, 0, 0, 0};
+                    if (splice) {
+                        if (p.use_map) {
+                            ms4 = *reinterpret_cast<const uint2 *>(gb + p.o_ms + h * 256 + 8 * lane);
+                            mc4 = *reinterpret_cast<const uint2 *>(gb + p.o_mc + h * 256 + 8 * lane);
+                        }
+                        bm4 = *reinterpret_cast<const uint4 *>(gb + p.o_bm + h * 512 + 16 * lane);
+                        const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
+                        const uint32_t *ov = reinterpret_cast<const uint32_t *>(gb + p.o_ov + h * 128 * nb + 4 * nb * lane);
+                        if (nb == 3) {
+                            const uint32_t w0 = ov[0], w1 = ov[1], w2 = ov[2];
+                            st[0] = w0 & 0xFFFFFFu;
+                            st[1] = (w0 >> 24) | ((w1 & 0xFFFFu) << 8);
+                            st[2] = (w1 >> 16) | ((w2 & 0xFFu) << 16);
+                            st[3] = w2 >> 8;
+                        } else if (nb == 4) {
+                            st[0] = ov[0]; st[1] = ov[1]; st[2] = ov[2]; st[3] = ov[3];
+                        } else if (nb == 2) {
+                            const uint32_t w0 = ov[0], w1 = ov[1];
+                            st[0] = w0 & 0xFFFFu; st[1] = w0 >> 16; st[2] = w1 & 0xFFFFu; st[3] = w1 >> 16;
+                        } else {
+                            const uint32_t w0 = ov[0];
+                            st[0] = w0 & 0xFFu; st[1] = (w0 >> 8) & 0xFFu; st[2] = (w0 >> 16) & 0xFFu; st[3] = w0 >> 24;
+                        }
+                    }
+                    const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
+                    const uint8_t *kbl = kb + lane;                      // this lane's code byte (channels 4*lane..+3)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int e = (int)(int8_t)(e4 >> (8 * c));
+                        const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
+                        const uint32_t zw = (c & 2) ? z4.y : z4.x;
+                        const float zp = bf16_bits_to_f32((c & 1) ? (zw >> 16) : (zw & 0xFFFFu));
+                        const float fs = inv_s * pa_f[c];
+                        // zp row: zp / scale in slot units (exact power-of-two scaling of a bf16)
+                        *reinterpret_cast<__nv_bfloat16 *>(tile + 32 * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(zp * fs);
+                        if (splice) {
+                            float A, Bc;
+                            if (p.use_map) {
+                                const uint32_t msw = (c & 2) ? ms4.y : ms4.x, mcw = (c & 2) ? mc4.y : mc4.x;
+                                const float ms = bf16_bits_to_f32((c & 1) ? (msw >> 16) : (msw & 0xFFFFu));
+                                const float mc = bf16_bits_to_f32((c & 1) ? (mcw >> 16) : (mcw & 0xFFFFu));
+                                A = __fdividef(fs, ms);
+                                Bc = (mc - zp) * fs;
+                            } else {
+                                A = pa_f[c];                              // (lvl*s + zp - zp)/s = lvl
+                                Bc = 0.f;
+                            }
+                            uint32_t bits = bmv[c];
+                            const uint32_t stream = st[c];
+                            const float nf = -pa_f[c];
+                            // delta between the outlier value and the base code it replaces, in code units:
+                            // ((lvl/ms + mc) - (code*s + zp)) / s, rounded to bf16 as the reference rounds
+                            // its delta (the scaling by 1/s and 4^pc is exact)
+                            if (KOUT > 0) {
+                                if (__popc(bits) == KOUT) {
+#pragma unroll
+                                    for (int r = KOUT - 1; r >= 0; --r) {
+                                        const int pz = 31 - __clz(bits);
+                                        bits ^= 1u << pz;
+                                        const uint32_t nib = (stream >> (4 * r)) & 0xFu;
+                                        const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
+                                        const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
+                                        *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
+                                    }
+                                } else {
+                                    or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
+                                }
+                            } else {
+                                int r = __popc(bits) - 1;
+                                while (bits) {
+                                    const int pz = 31 - __clz(bits);
+                                    bits ^= 1u << pz;
+                                    const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
+                                    --r;
+                                    const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
+                                    const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
+                                    *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
+                                }
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+
+                if (lane == 0) mbar_arrive(bar_tfull + 8 * unit);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        }
+        __syncthreads();
+        __syncthreads();
+        return;
+    }
+
+    // =========================== MMA warps (phase B) ===========================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 " OMMX_REGS_MMA ";");
+    const int unit = warp;
+    const int h = unit % H, gsel = unit / H;
+    const uint8_t *tile = s_tiles + unit * DT_BYTES;
+    const uint32_t tile_s = smem_u32(tile);
     // ---- per-thread constants ----
     // MMA row g carries query head (g % 4) when VFOLD (rows 4..7 repeat rows 0..3), else head g.
     const int row_head = VFOLD ? (g & 3) : g;
@@ -327,26 +511,10 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
             QS[r] = pack_bf16x2(lo, hi);
         }
     }
-    // phase-A constants: this lane owns channels 4*lane + c
-    uint32_t pa_col[4];       // byte offset of the channel's column inside an outlier-tile row
-    float pa_f[4];            // 4^pc of the channel's slot
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const int d = 4 * lane + c;
-        const int jj = d >> 5, wi = (d >> 4) & 1, i = d & 7, hi = (d >> 3) & 1;
-        pa_col[c] = 2u * (16 * (4 * wi + (i >> 1)) + 8 * (i & 1) + 2 * jj + hi);
-        pa_f[c] = (float)(1 << (2 * pos_class(i)));
-    }
     // V-fold constants: byte selectors of this row pair's two V scale groups
     const int cgA = g >> 2, cgB = 2 + (g >> 2);
     const uint32_t selA = (uint32_t)(cgA | (cgA << 4) | ((4 + cgA) << 8) | ((4 + cgA) << 12));
     const uint32_t selB = (uint32_t)(cgB | (cgB << 4) | ((4 + cgB) << 8) | ((4 + cgB) << 12));
-    // outlier tile: row 33 = -128 in every column (never rewritten); clear the rest once
-    for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(tile)[i] = 0u;
-    __syncwarp();
-    for (int i = lane; i < 64; i += 32) reinterpret_cast<uint32_t *>(tile + 33 * DT_STRIDE)[i] = 0xC300C300u;
-    __syncwarp();
-
     // ---- online softmax state (row g of the MMA tile) ----
     float m_run = -INFINITY, l_run = 0.f;
     float acc[16][4];
@@ -354,6 +522,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
     for (int i = 0; i < 16; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
     float acc_rs[4] = {0.f, 0.f, 0.f, 0.f};      // VFOLD: sum_t P'[row][t]        (x128 offset)
     float acc_vz[4] = {0.f, 0.f, 0.f, 0.f};      // VFOLD: sum_t P[row][t] * vz[t][cg = column]
+    uint32_t consumed = 0;
 
     for (int it = 0; it < n_iters; ++it) {
         const int s = it % NSTAGES;
@@ -371,106 +540,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
             const uint8_t *vsc = gb + p.o_vs + h * 4;                // + token*H*4
             const uint8_t *vzp = gb + p.o_vz + h * 8;                // + token*H*8
             const uint8_t *ksc = gb + p.o_ks + h * 128;
-            const uint8_t *kzp = gb + p.o_kz + h * 256;
-
-            // ======================= phase A: outlier deltas + zp row =======================
-            {
-                const bool splice = k_out > 0 && !no_outlier;
-                if (splice) {
-                    // clear token rows 0..31 (256 data bytes each)
-#pragma unroll
-                    for (int r2 = 0; r2 < 16; ++r2)
-                        *reinterpret_cast<uint4 *>(tile + (2 * r2 + (lane >> 4)) * DT_STRIDE + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
-                    __syncwarp();
-                }
-                const uint32_t e4 = *reinterpret_cast<const uint32_t *>(ksc + 4 * lane);
-                const uint2 z4 = *reinterpret_cast<const uint2 *>(kzp + 8 * lane);
-                uint2 ms4 = make_uint2(0, 0), mc4 = make_uint2(0, 0);
-                uint4 bm4 = make_uint4(0, 0, 0, 0);
-                uint32_t st[4] = {0, 0, 0, 0};
-                if (splice) {
-                    if (p.use_map) {
-                        ms4 = *reinterpret_cast<const uint2 *>(gb + p.o_ms + h * 256 + 8 * lane);
-                        mc4 = *reinterpret_cast<const uint2 *>(gb + p.o_mc + h * 256 + 8 * lane);
-                    }
-                    bm4 = *reinterpret_cast<const uint4 *>(gb + p.o_bm + h * 512 + 16 * lane);
-                    const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
-                    const uint32_t *ov = reinterpret_cast<const uint32_t *>(gb + p.o_ov + h * 128 * nb + 4 * nb * lane);
-                    if (nb == 3) {
-                        const uint32_t w0 = ov[0], w1 = ov[1], w2 = ov[2];
-                        st[0] = w0 & 0xFFFFFFu;
-                        st[1] = (w0 >> 24) | ((w1 & 0xFFFFu) << 8);
-                        st[2] = (w1 >> 16) | ((w2 & 0xFFu) << 16);
-                        st[3] = w2 >> 8;
-                    } else if (nb == 4) {
-                        st[0] = ov[0]; st[1] = ov[1]; st[2] = ov[2]; st[3] = ov[3];
-                    } else if (nb == 2) {
-                        const uint32_t w0 = ov[0], w1 = ov[1];
-                        st[0] = w0 & 0xFFFFu; st[1] = w0 >> 16; st[2] = w1 & 0xFFFFu; st[3] = w1 >> 16;
-                    } else {
-                        const uint32_t w0 = ov[0];
-                        st[0] = w0 & 0xFFu; st[1] = (w0 >> 8) & 0xFFu; st[2] = (w0 >> 16) & 0xFFu; st[3] = w0 >> 24;
-                    }
-                }
-                const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
-                const uint8_t *kbl = kb + lane;                      // this lane's code byte (channels 4*lane..+3)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int e = (int)(int8_t)(e4 >> (8 * c));
-                    const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
-                    const uint32_t zw = (c & 2) ? z4.y : z4.x;
-                    const float zp = bf16_bits_to_f32((c & 1) ? (zw >> 16) : (zw & 0xFFFFu));
-                    const float fs = inv_s * pa_f[c];
-                    // zp row: zp / scale in slot units (exact power-of-two scaling of a bf16)
-                    *reinterpret_cast<__nv_bfloat16 *>(tile + 32 * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(zp * fs);
-                    if (splice) {
-                        float A, Bc;
-                        if (p.use_map) {
-                            const uint32_t msw = (c & 2) ? ms4.y : ms4.x, mcw = (c & 2) ? mc4.y : mc4.x;
-                            const float ms = bf16_bits_to_f32((c & 1) ? (msw >> 16) : (msw & 0xFFFFu));
-                            const float mc = bf16_bits_to_f32((c & 1) ? (mcw >> 16) : (mcw & 0xFFFFu));
-                            A = __fdividef(fs, ms);
-                            Bc = (mc - zp) * fs;
-                        } else {
-                            A = pa_f[c];                              // (lvl*s + zp - zp)/s = lvl
-                            Bc = 0.f;
-                        }
-                        uint32_t bits = bmv[c];
-                        const uint32_t stream = st[c];
-                        const float nf = -pa_f[c];
-                        // delta between the outlier value and the base code it replaces, in code units:
-                        // ((lvl/ms + mc) - (code*s + zp)) / s, rounded to bf16 as the reference rounds
-                        // its delta (the scaling by 1/s and 4^pc is exact)
-                        if (KOUT > 0) {
-                            if (__popc(bits) == KOUT) {
-#pragma unroll
-                                for (int r = KOUT - 1; r >= 0; --r) {
-                                    const int pz = 31 - __clz(bits);
-                                    bits ^= 1u << pz;
-                                    const uint32_t nib = (stream >> (4 * r)) & 0xFu;
-                                    const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
-                                    const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
-                                    *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
-                                }
-                            } else {
-                                or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
-                            }
-                        } else {
-                            int r = __popc(bits) - 1;
-                            while (bits) {
-                                const int pz = 31 - __clz(bits);
-                                bits ^= 1u << pz;
-                                const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
-                                --r;
-                                const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
-                                const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
-                                *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
-                            }
-                        }
-                    }
-                }
-                __syncwarp();
-            }
 
             // ======================= phase B: QK^T =======================
             uint32_t QQ[16];
@@ -503,7 +572,12 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                     for (int kk = 0; kk < 4; ++kk) mma_bf16(C[nt], QQ[8 + 2 * kk], 0u, QQ[8 + 2 * kk + 1], 0u, R[2 * kk], R[2 * kk + 1]);
                 }
             }
-            // outlier tile (+ zp / -128 rows as n-tile 4)
+            // outlier tile (+ zp / -128 rows as n-tile 4), built by the decode warp of this unit
+            if (!mbar_wait(bar_tfull + 8 * unit, consumed & 1u)) {
+                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+                m_run = -INFINITY; l_run = 0.f;
+                break;
+            }
             {
                 const int mi = lane >> 3, rr = lane & 7;
 #pragma unroll
@@ -521,6 +595,9 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                     }
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * (NSTAGES * unit + (consumed % NSTAGES)));   // the next tile may be built
+            ++consumed;
             // q.zp - 128*sum(q'') sits in columns 0 and 1 of n-tile 4 (lanes with j == 0)
             float qzo = C[4][0] + C[4][1];
             qzo = __shfl_sync(0xFFFFFFFFu, qzo, lane & ~3);
@@ -695,7 +772,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
     __syncthreads();
     float *scratch = reinterpret_cast<float *>(s_stage);             // [NCW][32 lanes][34]
     if (GS > 1 && gsel > 0) {
-        float *my = scratch + ((size_t)warp * 32 + lane) * 34;
+        float *my = scratch + ((size_t)unit * 32 + lane) * 34;
         my[0] = m_run; my[1] = l_tot;
 #pragma unroll
         for (int i = 0; i < 32; ++i) my[2 + i] = outv[i];
@@ -774,14 +851,7 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
     const int nsplit = per > 0 ? min(p.S, (seq + per - 1) / per) : 0;    // splits s with s*per < seq
     const float *base = p.al + (int64_t)b * p.al_sb + (int64_t)hq * p.al_sh;
 
-    // ---- issue the split log-sum-exp loads first, they are the longest dependency ----
-    float mloc = -INFINITY;
-    for (int s = tid; s < nsplit; s += S2_THREADS) {
-        const float l = base[(int64_t)s * p.al_ss + D];
-        s_w[s] = l;
-        mloc = fmaxf(mloc, l);
-    }
-    // ---- bf16 residual rows: logits of this q head ----
+    // ---- bf16 residual rows: logits of this q head (independent of stage 1) ----
     if (tail > 0) {
         if (tid < D) s_q[tid] = __bfloat162float(p.q[(int64_t)b * p.q_sb + (int64_t)hq * p.q_sh + tid]);
         __syncthreads();
@@ -798,6 +868,15 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
                 s_logit[r] = x;
             }
         }
+    }
+    // ---- everything below reads what stage 1 wrote: wait for that grid (no-op without a
+    //      programmatic launch) ----
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float mloc = -INFINITY;
+    for (int s = tid; s < nsplit; s += S2_THREADS) {
+        const float l = base[(int64_t)s * p.al_ss + D];
+        s_w[s] = l;
+        mloc = fmaxf(mloc, l);
     }
     __syncthreads();
     // ---- global max over split lse values and residual logits ----
@@ -931,7 +1010,7 @@ static int validate_decode(const ommx_decode_args *a) {
 
 static size_t stage1_smem(const S1Params &p) {
     return (size_t)NSTAGES * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
-           + 2 * NSTAGES * 8 + 16;
+           + (2 * NSTAGES + (1 + NSTAGES) * NCW) * 8 + 16 + MAX_STAGE_COPIES * sizeof(CopyDesc);
 }
 
 template <int KOUT, bool VFOLD>
@@ -984,7 +1063,9 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     return vfold ? launch_s1<-1, true>(p, grid, smem, st) : launch_s1<-1, false>(p, grid, smem, st);
 }
 
-static int launch_stage2(const ommx_decode_args *a, cudaStream_t st) {
+// `after_stage1`: the previous kernel in the stream is this call's own stage 1, so stage 2 may be
+// launched as its programmatic dependent.
+static int launch_stage2(const ommx_decode_args *a, cudaStream_t st, bool after_stage1 = false) {
     const ommx_kv_planes &pl = a->planes;
     S2Params p;
     p.q = (const __nv_bfloat16 *)a->q; p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h;
@@ -998,9 +1079,17 @@ static int launch_stage2(const ommx_decode_args *a, cudaStream_t st) {
     p.o = a->o; p.o_bf16 = (a->o_dtype == OMMX_DT_BF16); p.o_sb = a->o_stride_b; p.o_sh = a->o_stride_h;
     p.lse = a->lse; p.lse_sb = a->lse_stride_b;
     p.sm_scale = a->sm_scale; p.logit_cap = a->logit_cap;
-    dim3 grid(a->n_q_heads, a->batch);
-    decode_stage2_kernel<<<grid, S2_THREADS, 0, st>>>(p);
-    OMMX_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a->n_q_heads, a->batch);
+    cfg.blockDim = dim3(S2_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;   // overlap this kernel's prologue with stage 1's tail
+    cfg.attrs = attr;
+    cfg.numAttrs = (after_stage1 && a->max_seq_len > 0) ? 1 : 0;
+    OMMX_CUDA_TRY(cudaLaunchKernelEx(&cfg, decode_stage2_kernel, p));
     count_launch();
     return 0;
 }
@@ -1052,7 +1141,7 @@ extern "C" int ommx_b200_decode(const ommx_decode_args *a, void *stream) {
     if (rc) return rc;
     rc = ommx::launch_stage1(a, (cudaStream_t)stream);
     if (rc) return rc;
-    return ommx::launch_stage2(a, (cudaStream_t)stream);
+    return ommx::launch_stage2(a, (cudaStream_t)stream, true);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -1109,7 +1198,7 @@ extern "C" int ommx_b200_decode_static_ws(const ommx_decode_args *a, void *strea
     if (rc) return rc;
     rc = launch_stage1(&b, (cudaStream_t)stream);
     if (rc) return rc;
-    return launch_stage2(&b, (cudaStream_t)stream);
+    return launch_stage2(&b, (cudaStream_t)stream, true);
 }
 
 extern "C" int ommx_b200_merge_states(const float *o_parts, const float *lse_parts, const int32_t *valid_lens,

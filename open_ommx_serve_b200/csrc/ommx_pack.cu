@@ -6,10 +6,9 @@
 // fp32 operation in the same order (no FMA contraction: explicit __f*_rn intrinsics), and the
 // two library calls of the reference (log2, log) are replaced by frozen threshold tables.
 //
-// K kernel: one warp per (32-token group, kv head); lane = token.  The group's [32 x D] tile
-//   is staged in shared memory, then the warp walks the D channels.  Outlier selection is the
-//   reference's stable-sort rule done with warp reductions: the r-th pick is the max (min) key
-//   over unpicked lanes, ties to the lowest lane (redux.sync + ballot).
+// K kernel: one warp per (32-token group, kv head, 16-channel block); lane = token.  Outlier
+//   selection is the reference's stable-sort rule done with warp reductions: the r-th pick is the
+//   max (min) key over unpicked lanes, ties to the lowest lane (redux.sync + ballot).
 // V kernel: one thread per (token, head, 32-channel group).
 #include "ommx_common.cuh"
 
@@ -50,8 +49,7 @@ struct PackKParams {
 };
 
 constexpr int PACK_WARPS = 4;
-constexpr int PACK_MAX_D = 128;
-constexpr int PACK_TILE_STRIDE = PACK_MAX_D + 1;   // floats per staged token row (bank-conflict free)
+constexpr int PACK_BLK = 16;                       // channels per warp: one 32-bit word of 2-bit codes per token
 
 // scale -> (value after optional pow2 snap and storage rounding, exponent)
 __device__ __forceinline__ float snap_scale(float rng, int use_pow2, int scale_kind, int &e) {
@@ -65,23 +63,25 @@ __device__ __forceinline__ float snap_scale(float rng, int use_pow2, int scale_k
     return scale;
 }
 
+// One warp per (32-token group, kv head, block of 16 channels); lane = token.  A lane reads its 16
+// channel values straight from global memory; the 16 two-bit codes of the block are exactly one
+// 32-bit word of the token's row, so warps never share an output word.
 template <typename T>
 __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_kernel(PackKParams p) {
-    extern __shared__ float s_tile[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int unit = blockIdx.x * PACK_WARPS + warp;           // (group, head)
-    if (unit >= p.num_groups * p.H) return;
-    const int g = unit / p.H, h = unit - g * p.H;
+    const int nblk = p.D / PACK_BLK;
+    const int unit = blockIdx.x * PACK_WARPS + warp;           // (group, head, channel block)
+    if (unit >= p.num_groups * p.H * nblk) return;
+    const int blk = unit % nblk;
+    const int gh = unit / nblk;
+    const int g = gh / p.H, h = gh - g * p.H;
     const int D = p.D;
-    float *tile = s_tile + warp * 32 * PACK_TILE_STRIDE;
 
-    // stage the [32 tokens x D] tile, coalesced along channels
-    const T *src = reinterpret_cast<const T *>(p.k);
-    for (int r = 0; r < 32; ++r) {
-        const T *row = src + (int64_t)(g * 32 + r) * p.stride_token + (int64_t)h * p.stride_head;
-        for (int c = lane; c < D; c += 32) tile[r * PACK_TILE_STRIDE + c] = load_as_f32(row + c);
-    }
-    __syncwarp();
+    const T *row = reinterpret_cast<const T *>(p.k) + (int64_t)(g * 32 + lane) * p.stride_token
+                 + (int64_t)h * p.stride_head + blk * PACK_BLK;
+    float xv[PACK_BLK];
+#pragma unroll
+    for (int c = 0; c < PACK_BLK; ++c) xv[c] = load_as_f32(row + c);
 
     // destination addressing
     const int ps = p.page_size;
@@ -100,118 +100,102 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_kernel(PackKParams p) 
     const int nb = (k + 1) / 2;
     const uint32_t lt_mask = (1u << lane) - 1u;
     const bool store_f32 = (p.scale_kind == OMMX_SCALE_F32);
-    const int64_t gbase = ((int64_t)slot * p.H + h) * D;       // element offset in [G,H,D] planes
+    const int64_t gbase = ((int64_t)slot * p.H + h) * D + blk * PACK_BLK;   // element offset in [G,H,D] planes
 
-    uint32_t words[PACK_MAX_D / 16];
-#pragma unroll
-    for (int w = 0; w < PACK_MAX_D / 16; ++w) words[w] = 0;
+    uint32_t word = 0;
     bool bad = false;
-
-    // per-channel parameters of the current 32-channel block, parked on lane (d & 31)
+    // per-channel parameters, parked on lane cc (lanes 0..15)
     int my_e = 0;
     float my_scale = 0.f, my_zp = 0.f, my_ms = 0.f, my_mc = 0.f;
     uint32_t my_bmp = 0;
     unsigned long long my_val = 0ull;
 
 #pragma unroll
-    for (int w = 0; w < PACK_MAX_D / 16; ++w) {
-        if (w * 16 >= D) break;
-#pragma unroll 4
-        for (int cc = 0; cc < 16; ++cc) {
-            const int d = w * 16 + cc;
-            const float x = tile[lane * PACK_TILE_STRIDE + d];
-            if (!isfinite(x)) bad = true;
-            const uint32_t key = p.select_signed ? f32_key(x) : (__float_as_uint(fabsf(x)) + 1u);
-            // ---- outlier selection -------------------------------------------------------
-            bool sel = false;
-            for (int r = 0; r < kt; ++r) {                      // largest first, ties -> low lane
-                uint32_t cand = sel ? 0u : key;
-                uint32_t m = __reduce_max_sync(0xFFFFFFFFu, cand);
-                uint32_t hit = __ballot_sync(0xFFFFFFFFu, !sel && cand == m);
-                if (hit && lane == (__ffs(hit) - 1)) sel = true;
+    for (int cc = 0; cc < PACK_BLK; ++cc) {
+        const float x = xv[cc];
+        if (!isfinite(x)) bad = true;
+        const uint32_t key = p.select_signed ? f32_key(x) : (__float_as_uint(fabsf(x)) + 1u);
+        // ---- outlier selection: r-th pick = extreme key over unpicked lanes, ties -> lowest lane ----
+        bool sel = false;
+        for (int r = 0; r < kt; ++r) {
+            uint32_t cand = sel ? 0u : key;
+            uint32_t m = __reduce_max_sync(0xFFFFFFFFu, cand);
+            uint32_t hit = __ballot_sync(0xFFFFFFFFu, !sel && cand == m);
+            if (hit && lane == (__ffs(hit) - 1)) sel = true;
+        }
+        for (int r = 0; r < kb; ++r) {
+            uint32_t cand = sel ? 0xFFFFFFFFu : key;
+            uint32_t m = __reduce_min_sync(0xFFFFFFFFu, cand);
+            uint32_t hit = __ballot_sync(0xFFFFFFFFu, !sel && cand == m);
+            if (hit && lane == (__ffs(hit) - 1)) sel = true;
+        }
+        const uint32_t omask = __ballot_sync(0xFFFFFFFFu, sel);
+        // ---- base affine over the non-outlier lanes ----
+        const uint32_t vkey = f32_key(x);
+        uint32_t kmin = __reduce_min_sync(0xFFFFFFFFu, sel ? 0xFFFFFFFFu : vkey);
+        uint32_t kmax = __reduce_max_sync(0xFFFFFFFFu, sel ? 0u : vkey);
+        float mn = (omask == 0xFFFFFFFFu) ? 0.f : key_f32(kmin);
+        float mx = (omask == 0xFFFFFFFFu) ? 0.f : key_f32(kmax);
+        int e;
+        const float scale = snap_scale(__fsub_rn(mx, mn), p.use_pow2, p.scale_kind, e);
+        const float zp = store_f32 ? mn : bf16_round_f32(mn);
+        float qv = rintf(__fdiv_rn(__fsub_rn(x, zp), scale));
+        qv = fminf(fmaxf(qv, 0.f), 3.f);
+        word |= (uint32_t)(int)qv << (2 * cc);
+        // ---- outlier values ----
+        float ms = 0.f, mc = 0.f;
+        unsigned long long val = 0ull;
+        if (k > 0) {
+            float mapped;
+            if (p.outlier_map) {
+                uint32_t okmin = __reduce_min_sync(0xFFFFFFFFu, sel ? vkey : 0xFFFFFFFFu);
+                uint32_t okmax = __reduce_max_sync(0xFFFFFFFFu, sel ? vkey : 0u);
+                float omn = key_f32(okmin), omx = key_f32(okmax);
+                mc = __fmul_rn(__fadd_rn(omx, omn), 0.5f);
+                // the reference evaluates 12.0 / range as reciprocal(range) * 12
+                ms = __fmul_rn(__frcp_rn(fmaxf(__fsub_rn(omx, omn), 1e-8f)), 12.0f);
+                if (!store_f32) { mc = bf16_round_f32(mc); ms = bf16_round_f32(ms); }
+                mapped = __fmul_rn(__fsub_rn(x, mc), ms);
+            } else {
+                mapped = __fdiv_rn(__fsub_rn(x, zp), scale);
             }
-            for (int r = 0; r < kb; ++r) {                      // then smallest of the rest
-                uint32_t cand = sel ? 0xFFFFFFFFu : key;
-                uint32_t m = __reduce_min_sync(0xFFFFFFFFu, cand);
-                uint32_t hit = __ballot_sync(0xFFFFFFFFu, !sel && cand == m);
-                if (hit && lane == (__ffs(hit) - 1)) sel = true;
-            }
-            const uint32_t omask = __ballot_sync(0xFFFFFFFFu, sel);
-            // ---- base affine over the non-outlier lanes ---------------------------------------
-            const uint32_t vkey = f32_key(x);
-            uint32_t kmin = __reduce_min_sync(0xFFFFFFFFu, sel ? 0xFFFFFFFFu : vkey);
-            uint32_t kmax = __reduce_max_sync(0xFFFFFFFFu, sel ? 0u : vkey);
-            float mn = (omask == 0xFFFFFFFFu) ? 0.f : key_f32(kmin);
-            float mx = (omask == 0xFFFFFFFFu) ? 0.f : key_f32(kmax);
-            int e;
-            const float scale = snap_scale(__fsub_rn(mx, mn), p.use_pow2, p.scale_kind, e);
-            const float zp = store_f32 ? mn : bf16_round_f32(mn);
-            float qv = rintf(__fdiv_rn(__fsub_rn(x, zp), scale));
-            qv = fminf(fmaxf(qv, 0.f), 3.f);
-            const uint32_t code = (uint32_t)(int)qv;
-            words[w] |= code << (2 * cc);
-            // ---- outlier values ------------------------------------------------------------------
-            float ms = 0.f, mc = 0.f;
-            unsigned long long val = 0ull;
-            if (k > 0) {
-                float mapped;
-                if (p.outlier_map) {
-                    uint32_t okmin = __reduce_min_sync(0xFFFFFFFFu, sel ? vkey : 0xFFFFFFFFu);
-                    uint32_t okmax = __reduce_max_sync(0xFFFFFFFFu, sel ? vkey : 0u);
-                    float omn = key_f32(okmin), omx = key_f32(okmax);
-                    mc = __fmul_rn(__fadd_rn(omx, omn), 0.5f);
-                    // the reference evaluates 12.0 / range as reciprocal(range) * 12
-                    ms = __fmul_rn(__frcp_rn(fmaxf(__fsub_rn(omx, omn), 1e-8f)), 12.0f);
-                    if (!store_f32) { mc = bf16_round_f32(mc); ms = bf16_round_f32(ms); }
-                    mapped = __fmul_rn(__fsub_rn(x, mc), ms);
+            uint32_t fp4 = (uint32_t)fp4_encode_tbl(mapped, c_fp4_thresh);
+            int rank = __popc(omask & lt_mask);
+            unsigned long long contrib = (sel && rank < 16) ? ((unsigned long long)fp4 << (4 * rank)) : 0ull;
+            uint32_t lo = __reduce_or_sync(0xFFFFFFFFu, (uint32_t)contrib);
+            uint32_t hi = (k > 8) ? __reduce_or_sync(0xFFFFFFFFu, (uint32_t)(contrib >> 32)) : 0u;
+            val = ((unsigned long long)hi << 32) | lo;
+        }
+        if (lane == cc) {
+            my_e = e; my_scale = scale; my_zp = zp; my_ms = ms; my_mc = mc; my_bmp = omask; my_val = val;
+        }
+    }
+    // ---- lanes 0..15 write the block's 16 consecutive channel entries ----
+    if (slot_ok && lane < PACK_BLK) {
+        const int64_t off = gbase + lane;
+        if (p.scale_kind == OMMX_SCALE_INT8_EXP) reinterpret_cast<int8_t *>(p.k_scale)[off] = (int8_t)my_e;
+        else if (p.scale_kind == OMMX_SCALE_BF16) reinterpret_cast<uint16_t *>(p.k_scale)[off] = (uint16_t)f32_to_bf16_bits(my_scale);
+        else reinterpret_cast<float *>(p.k_scale)[off] = my_scale;
+        if (store_f32) reinterpret_cast<float *>(p.k_zp)[off] = my_zp;
+        else reinterpret_cast<uint16_t *>(p.k_zp)[off] = (uint16_t)f32_to_bf16_bits(my_zp);
+        if (k > 0) {
+            if (p.outlier_map) {
+                if (store_f32) {
+                    reinterpret_cast<float *>(p.k_mapscale)[off] = my_ms;
+                    reinterpret_cast<float *>(p.k_mapcenter)[off] = my_mc;
                 } else {
-                    mapped = __fdiv_rn(__fsub_rn(x, zp), scale);
-                }
-                uint32_t fp4 = (uint32_t)fp4_encode_tbl(mapped, c_fp4_thresh);
-                int rank = __popc(omask & lt_mask);
-                unsigned long long contrib = (sel && rank < 16) ? ((unsigned long long)fp4 << (4 * rank)) : 0ull;
-                uint32_t lo = __reduce_or_sync(0xFFFFFFFFu, (uint32_t)contrib);
-                uint32_t hi = (k > 8) ? __reduce_or_sync(0xFFFFFFFFu, (uint32_t)(contrib >> 32)) : 0u;
-                val = ((unsigned long long)hi << 32) | lo;
-            }
-            if (lane == (d & 31)) {
-                my_e = e; my_scale = scale; my_zp = zp; my_ms = ms; my_mc = mc; my_bmp = omask; my_val = val;
-            }
-            // ---- flush a finished block of 32 channels: lane l owns channel (d & ~31) + l ----
-            if ((d & 31) == 31 && slot_ok) {
-                const int64_t off = gbase + (d & ~31) + lane;
-                if (p.scale_kind == OMMX_SCALE_INT8_EXP) {
-                    reinterpret_cast<int8_t *>(p.k_scale)[off] = (int8_t)my_e;
-                } else if (p.scale_kind == OMMX_SCALE_BF16) {
-                    reinterpret_cast<uint16_t *>(p.k_scale)[off] = (uint16_t)f32_to_bf16_bits(my_scale);
-                } else {
-                    reinterpret_cast<float *>(p.k_scale)[off] = my_scale;
-                }
-                if (store_f32) reinterpret_cast<float *>(p.k_zp)[off] = my_zp;
-                else reinterpret_cast<uint16_t *>(p.k_zp)[off] = (uint16_t)f32_to_bf16_bits(my_zp);
-                if (k > 0) {
-                    if (p.outlier_map) {
-                        if (store_f32) {
-                            reinterpret_cast<float *>(p.k_mapscale)[off] = my_ms;
-                            reinterpret_cast<float *>(p.k_mapcenter)[off] = my_mc;
-                        } else {
-                            reinterpret_cast<uint16_t *>(p.k_mapscale)[off] = (uint16_t)f32_to_bf16_bits(my_ms);
-                            reinterpret_cast<uint16_t *>(p.k_mapcenter)[off] = (uint16_t)f32_to_bf16_bits(my_mc);
-                        }
-                    }
-                    reinterpret_cast<uint32_t *>(p.k_obmp)[off] = my_bmp;
-                    for (int i = 0; i < nb; ++i) p.k_oval[off * nb + i] = (uint8_t)(my_val >> (8 * i));
+                    reinterpret_cast<uint16_t *>(p.k_mapscale)[off] = (uint16_t)f32_to_bf16_bits(my_ms);
+                    reinterpret_cast<uint16_t *>(p.k_mapcenter)[off] = (uint16_t)f32_to_bf16_bits(my_mc);
                 }
             }
+            reinterpret_cast<uint32_t *>(p.k_obmp)[off] = my_bmp;
+            for (int i = 0; i < nb; ++i) p.k_oval[off * nb + i] = (uint8_t)(my_val >> (8 * i));
         }
     }
     if (bad) or_status(p.status, OMMX_ST_NONFINITE);
     if (page_ok) {
         uint8_t *dst = p.k_base + (((int64_t)page * ps + (tok % ps)) * p.H + h) * (D / 4);
-        uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
-#pragma unroll
-        for (int w = 0; w < PACK_MAX_D / 16; ++w)
-            if (w * 16 < D) d32[w] = words[w];
+        reinterpret_cast<uint32_t *>(dst)[blk] = word;
     }
 }
 
@@ -286,15 +270,9 @@ static int launch_pack(const ommx_pack_args *a, cudaStream_t st) {
     kp.k_base = (uint8_t *)pl.k_base; kp.k_scale = pl.k_scale; kp.k_zp = pl.k_zp;
     kp.k_mapscale = pl.k_mapscale; kp.k_mapcenter = pl.k_mapcenter;
     kp.k_obmp = (uint8_t *)pl.k_obmp; kp.k_oval = (uint8_t *)pl.k_oval; kp.status = a->status;
-    const int units = kp.num_groups * kp.H;
-    const size_t smem = (size_t)PACK_WARPS * 32 * PACK_TILE_STRIDE * sizeof(float);
-    static bool attr_done = false;   // per template instance
-    if (!attr_done) {
-        OMMX_CUDA_TRY(cudaFuncSetAttribute(pack_k_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_done = true;
-    }
+    const int units = kp.num_groups * kp.H * (kp.D / PACK_BLK);
     if (units > 0) {
-        pack_k_kernel<T><<<(units + PACK_WARPS - 1) / PACK_WARPS, PACK_WARPS * 32, smem, st>>>(kp);
+        pack_k_kernel<T><<<(units + PACK_WARPS - 1) / PACK_WARPS, PACK_WARPS * 32, 0, st>>>(kp);
         OMMX_CUDA_TRY(cudaGetLastError());
         count_launch();
     }
@@ -325,8 +303,8 @@ extern "C" int ommx_b200_pack_kv(const ommx_pack_args *a, void *stream) {
         return fail(OMMX_E_ARG, "pack: page_size=%d must divide 32 or be a multiple of it", pl.page_size);
     if (a->num_tokens % pl.page_size != 0)
         return fail(OMMX_E_ARG, "pack: num_tokens=%d must be a multiple of page_size=%d", a->num_tokens, pl.page_size);
-    if (pl.head_dim % 32 != 0 || pl.head_dim <= 0 || pl.head_dim > PACK_MAX_D)
-        return fail(OMMX_E_UNSUPPORTED, "pack: head_dim=%d must be a multiple of 32, at most %d", pl.head_dim, PACK_MAX_D);
+    if (pl.head_dim % 32 != 0 || pl.head_dim <= 0)
+        return fail(OMMX_E_UNSUPPORTED, "pack: head_dim=%d must be a positive multiple of 32", pl.head_dim);
     if (pl.n_kv_heads <= 0) return fail(OMMX_E_ARG, "pack: n_kv_heads=%d", pl.n_kv_heads);
     if (pl.outliers_per_vector < 0 || pl.outliers_per_vector > 16)
         return fail(OMMX_E_UNSUPPORTED, "pack: outliers_per_vector=%d outside [0,16]", pl.outliers_per_vector);
