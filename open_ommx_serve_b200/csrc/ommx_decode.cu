@@ -26,6 +26,8 @@
 // dequantized to bf16.  One point differs at the bf16-rounding level: q.zp uses the bf16
 // q*sm_scale instead of fp32 q.
 #include "ommx_common.cuh"
+#include <cuda.h>                       // CUtensorMap (types only; the encoder is looked up at run time)
+#include <mutex>
 
 namespace ommx {
 
@@ -65,15 +67,20 @@ struct S1Params {
     // shared-memory layout of one group block (bytes)
     int32_t GS, gb_bytes, stage_bytes;
     int32_t o_vm, o_vs, o_vz, o_ks, o_kz, o_ms, o_mc, o_bm, o_ov;
+    // tensor maps of the two code planes as [bytes/128][128] uint8 with 128-byte swizzle
+    uint32_t swz;                        // 0x70 when the maps are in use, else 0
+    int32_t rows_per_page;               // 128-byte lines per page
+    alignas(64) CUtensorMap tmap_k;
+    alignas(64) CUtensorMap tmap_v;
 };
 
 // One bulk copy of a stage: source plane, bytes, destination inside the stage, and which table entry
 // (page id or group slot) selects the source block.
 struct __align__(16) CopyDesc {
-    const uint8_t *src;
+    const uint8_t *src;                  // plane base, or nullptr + kind for a tensor-map copy
     uint32_t unit, dst;
-    int32_t tbase, tmul, gi, tok0;
-};
+    int32_t tbase, tmul, gi, tok0;       // gi: group in stage (bits 0..7) | kind << 8
+};                                       // kind 0 bulk copy, 1 k_base through tmap_k, 2 v_main through tmap_v
 constexpr int MAX_STAGE_COPIES = 8 * (4 * 4 + 6);                    // 8 groups per stage, 8-token pages
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -130,6 +137,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// The 2-bit code planes are staged with the TMA's 128-byte swizzle (16-byte chunk index XOR line
+// index mod 8) when a page is a whole number of 1 KB swizzle atoms: a head's 32-byte code row then
+// lands in a different bank window on each token row instead of the same one.  `o` is the linear byte
+// offset inside a 1 KB aligned region; swz is 0x70 (swizzled) or 0 (plain bulk copies).
+__device__ __forceinline__ uint32_t swz128(uint32_t o, uint32_t swz) { return o ^ ((o >> 3) & swz); }
+
+__device__ __forceinline__ void tma_2d_g2s(uint32_t dst, const CUtensorMap *map, int32_t x, int32_t y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
 // position class of channel-in-word index i (0..7): the 2-bit field sits at bit 2*pc of its half
 // when the LOP3 extracts it, so the extracted bf16 is 128 + code * 4^pc.
 __device__ __forceinline__ int pos_class(int i) { return i < 3 ? i : (i < 6 ? i - 3 : i - 6); }
@@ -168,8 +186,10 @@ constexpr int ABL_NO_OUTLIER = 1, ABL_NO_V = 2, ABL_NO_K = 4, ABL_NO_COMPUTE = 8
 //        MMA as raw 128 + code*4^pc values: no per-element V arithmetic at all.  The offset comes
 //        back out through a row-sum column, the zero-points through a small bias MMA.
 template <int KOUT, bool VFOLD>
-__global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Params p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+__global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __grid_constant__ S1Params p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // swizzle atoms are 1 KB: align the ring by hand (the launch adds 1 KB of slack)
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int split = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -251,6 +271,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                 d.dst = gbo + (plane == 0 ? 0u : (plane == 1 ? (uint32_t)p.o_vm : (plane == 2 ? (uint32_t)p.o_vs : (uint32_t)p.o_vz)))
                       + (uint32_t)pg * page_b * w;
                 d.tbase = pg; d.tmul = p.ppg; d.tok0 = pg * p.ps;
+                if (p.swz != 0 && plane < 2) d.gi |= (plane + 1) << 8;
             } else {
                 const int gp = ci - 4 * p.ppg;
                 const bool on = gp < 2 || (k_out > 0 && (gp >= 4 || p.use_map));
@@ -296,7 +317,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                 uint32_t mine = 0;
                 for (int c = lane; c < ncopies; c += 32) {
                     const CopyDesc d = s_desc[c];
-                    const int lg = lg0 + d.gi;
+                    const int lg = lg0 + (d.gi & 0xFF);
                     if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) mine += d.unit;
                 }
                 total = __reduce_add_sync(0xFFFFFFFFu, mine);
@@ -306,10 +327,12 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
             const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
             for (int c = lane; c < ncopies; c += 32) {
                 const CopyDesc d = s_desc[c];
-                const int lg = lg0 + d.gi;
+                const int lg = lg0 + (d.gi & 0xFF);
+                const int kind = d.gi >> 8;
                 if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) {
                     const int64_t idx = s_tab[d.tbase + lg * d.tmul];
-                    bulk_g2s(sbase + d.dst, d.src + idx * d.unit, d.unit, bar_full + 8 * s);
+                    if (kind == 0) bulk_g2s(sbase + d.dst, d.src + idx * d.unit, d.unit, bar_full + 8 * s);
+                    else tma_2d_g2s(sbase + d.dst, kind == 1 ? &p.tmap_k : &p.tmap_v, 0, (int32_t)idx * p.rows_per_page, bar_full + 8 * s);
                 }
             }
         }
@@ -368,7 +391,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                 // phase k / NSTAGES): the newest event a waiter can be missing is then always the one it
                 // waits for, never an older phase of the same parity.
                 uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
-                const uint8_t *kb = gb + h * 32;                     // + token*TS
                 const uint8_t *ksc = gb + p.o_ks + h * 128;
                 const uint8_t *kzp = gb + p.o_kz + h * 256;
                 if (it > 0 && !mbar_wait(bar_tempty + 8 * (NSTAGES * unit + ((it - 1) % NSTAGES)),
@@ -415,7 +437,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                         }
                     }
                     const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
-                    const uint8_t *kbl = kb + lane;                      // this lane's code byte (channels 4*lane..+3)
+                    const uint8_t *kreg = gb;                            // k_base region of the group (1 KB aligned)
+                    const uint32_t kl_off = (uint32_t)(h * 32 + lane);     // this lane's code byte (channels 4*lane..+3)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int e = (int)(int8_t)(e4 >> (8 * c));
@@ -450,7 +473,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                                         const int pz = 31 - __clz(bits);
                                         bits ^= 1u << pz;
                                         const uint32_t nib = (stream >> (4 * r)) & 0xFu;
-                                        const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
+                                        const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> (2 * c)) & 3u);
                                         const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
                                         *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
                                     }
@@ -464,7 +487,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
                                     bits ^= 1u << pz;
                                     const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
                                     --r;
-                                    const float cf = (float)((kbl[pz * TS] >> (2 * c)) & 3u);
+                                    const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> (2 * c)) & 3u);
                                     const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
                                     *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
                                 }
@@ -535,8 +558,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
         const int lg = it * GS + gsel;                               // local group of this warp
         if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
             uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
-            const uint8_t *kb = gb + h * 32;                         // + token*TS
-            const uint8_t *vm = gb + p.o_vm + h * 32;
+            const uint8_t *vreg = gb + p.o_vm;                      // v_main region of the group (1 KB aligned)
             const uint8_t *vsc = gb + p.o_vs + h * 4;                // + token*H*4
             const uint8_t *vzp = gb + p.o_vz + h * 8;                // + token*H*8
             const uint8_t *ksc = gb + p.o_ks + h * 128;
@@ -562,7 +584,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
             if (!(p.abl & ABL_NO_K)) {
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
-                    const uint2 kw = *reinterpret_cast<const uint2 *>(kb + (8 * nt + g) * TS + 8 * j);
+                    const uint2 kw = *reinterpret_cast<const uint2 *>(gb + swz128((uint32_t)((8 * nt + g) * TS + h * 32 + 8 * j), p.swz));
                     uint32_t R[8];
                     codes_to_bf16x2(kw.x, R);
 #pragma unroll
@@ -669,10 +691,10 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
 #pragma unroll
                     for (int kt = 0; kt < 2; ++kt) {
                         const int ta = 16 * kt + 2 * j;
-                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vm + ta * TS + 4 * g);
-                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vm + (ta + 1) * TS + 4 * g);
-                        const uint32_t wc = *reinterpret_cast<const uint32_t *>(vm + (ta + 8) * TS + 4 * g);
-                        const uint32_t wd = *reinterpret_cast<const uint32_t *>(vm + (ta + 9) * TS + 4 * g);
+                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)(ta * TS + h * 32 + 4 * g), p.swz));
+                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)((ta + 1) * TS + h * 32 + 4 * g), p.swz));
+                        const uint32_t wc = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)((ta + 8) * TS + h * 32 + 4 * g), p.swz));
+                        const uint32_t wd = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)((ta + 9) * TS + h * 32 + 4 * g), p.swz));
                         uint32_t R0[8], R1[8];
                         codes_to_bf16x2(__byte_perm(wa, wb, 0x5410), R0);       // channels 0..7 of (ta, tb)
                         codes_to_bf16x2(__byte_perm(wc, wd, 0x5410), R1);
@@ -701,8 +723,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const S1Pa
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
                             const int ta = 16 * kt + 8 * half + 2 * j, tb = ta + 1;
-                            const uint32_t wa = *reinterpret_cast<const uint32_t *>(vm + ta * TS + 4 * g);
-                            const uint32_t wb = *reinterpret_cast<const uint32_t *>(vm + tb * TS + 4 * g);
+                            const uint32_t wa = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)(ta * TS + h * 32 + 4 * g), p.swz));
+                            const uint32_t wb = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)(tb * TS + h * 32 + 4 * g), p.swz));
                             const uint32_t ea = vsc[ta * H * 4 + (g >> 1)], eb2 = vsc[tb * H * 4 + (g >> 1)];
                             const uint32_t za = *reinterpret_cast<const uint16_t *>(vzp + ta * H * 8 + 2 * (g >> 1));
                             const uint32_t zb = *reinterpret_cast<const uint16_t *>(vzp + tb * H * 8 + 2 * (g >> 1));
@@ -1008,8 +1030,59 @@ static int validate_decode(const ommx_decode_args *a) {
     return 0;
 }
 
+// ---- tensor maps of the code planes (driver entry point looked up at run time, no link dependency) ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static std::atomic<int> state{0};                 // 0 unknown, 1 found, 2 absent
+    static EncodeTiledFn fn = nullptr;
+    int st = state.load(std::memory_order_acquire);
+    if (st == 0) {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        const bool ok = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+                        q == cudaDriverEntryPointSuccess && f != nullptr;
+        if (ok) fn = reinterpret_cast<EncodeTiledFn>(f);
+        (void)cudaGetLastError();
+        state.store(ok ? 1 : 2, std::memory_order_release);
+        st = ok ? 1 : 2;
+    }
+    return st == 1 ? fn : nullptr;
+}
+
+// Plane viewed as [bytes/128][128] uint8, box = one page, 128-byte swizzle.  Returns false when the
+// map cannot be built (the caller then stages the plane with plain bulk copies).
+// Encoded maps are kept in a small table keyed by (base, bytes, box rows): a serving loop calls with the
+// same planes every step and the driver call costs about a microsecond.
+static bool make_code_map(CUtensorMap *m, const void *base, int64_t total_bytes, int rows_per_page) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr || total_bytes < 128 || rows_per_page < 8 || rows_per_page > 256) return false;
+    struct Entry { const void *base; int64_t bytes; int rows; CUtensorMap map; };
+    constexpr int N = 256;
+    static Entry table[N];
+    static std::mutex mu;
+    const size_t slot = (reinterpret_cast<uintptr_t>(base) >> 8) % N;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        const Entry &e = table[slot];
+        if (e.base == base && e.bytes == total_bytes && e.rows == rows_per_page) { *m = e.map; return true; }
+    }
+    cuuint64_t gdim[2] = {128, (cuuint64_t)(total_bytes / 128)};
+    cuuint64_t gstride[1] = {128};
+    cuuint32_t box[2] = {128, (cuuint32_t)rows_per_page};
+    cuuint32_t estr[2] = {1, 1};
+    if (fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), gdim, gstride, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::lock_guard<std::mutex> g(mu);
+    table[slot].base = base; table[slot].bytes = total_bytes; table[slot].rows = rows_per_page; table[slot].map = *m;
+    return true;
+}
+
 static size_t stage1_smem(const S1Params &p) {
-    return (size_t)NSTAGES * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
+    return 1024 + (size_t)NSTAGES * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
            + (2 * NSTAGES + (1 + NSTAGES) * NCW) * 8 + 16 + MAX_STAGE_COPIES * sizeof(CopyDesc);
 }
 
@@ -1052,7 +1125,19 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.o_kz = p.o_ks + H * 128; p.o_ms = p.o_kz + H * 256; p.o_mc = p.o_ms + H * 256; p.o_bm = p.o_mc + H * 256;
     p.o_ov = p.o_bm + H * 512;
     p.gb_bytes = p.o_ov + H * 128 * (p.nb > 0 ? p.nb : 0);
-    p.gb_bytes = (p.gb_bytes + 127) / 128 * 128;
+    // swizzled tensor-map staging of the two code planes when a page is whole 1 KB swizzle atoms and
+    // the 1 KB rounding of the group block still fits shared memory (4 or 8 local kv heads)
+    const int64_t page_bytes = (int64_t)p.ps * H * 32;
+    p.swz = 0;
+    p.rows_per_page = (int32_t)(page_bytes / 128);
+    memset(&p.tmap_k, 0, sizeof(CUtensorMap));
+    memset(&p.tmap_v, 0, sizeof(CUtensorMap));
+    if (H >= 4 && page_bytes % 1024 == 0 &&
+        make_code_map(&p.tmap_k, pl.k_base, (int64_t)pl.num_pages * page_bytes, p.rows_per_page) &&
+        make_code_map(&p.tmap_v, pl.v_main, (int64_t)pl.num_pages * page_bytes, p.rows_per_page))
+        p.swz = 0x70u;
+    const int round_to = p.swz ? 1024 : 128;
+    p.gb_bytes = (p.gb_bytes + round_to - 1) / round_to * round_to;
     p.stage_bytes = p.GS * p.gb_bytes;
     p.abl = a->abl_flags;
     const size_t smem = stage1_smem(p);
