@@ -83,6 +83,18 @@ struct __align__(16) CopyDesc {
 };                                       // kind 0 bulk copy, 1 k_base through tmap_k, 2 v_main through tmap_v
 constexpr int MAX_STAGE_COPIES = 8 * (4 * 4 + 6);                    // 8 groups per stage, 8-token pages
 
+// Development builds (-DOMMX_TRACE) stamp the SM clock at fixed points of one CTA's warps into a
+// device array that ommx_b200_debug_read_trace copies out; service builds compile the probes away.
+#ifdef OMMX_TRACE
+__device__ long long g_trace[32 * 256];
+#define OMMX_TR(slot)                                                                              \
+    do {                                                                                           \
+        if (blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (slot) < 256) g_trace[warp * 256 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define OMMX_TR(slot) do { } while (0)
+#endif
+
 // ---- PTX wrappers --------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -172,6 +184,25 @@ __device__ __forceinline__ void codes_to_bf16x2(uint32_t w, uint32_t (&r)[8]) {
     r[7] = lop3_and_or(t, 0x000C000Cu, M);
 }
 
+// The same extraction in two halves (registers 0..3, then 4..7), for loops that interleave several
+// code words so that back-to-back MMAs never share an accumulator.
+__device__ __forceinline__ void codes_to_bf16x2_lo(uint32_t w, uint32_t (&r)[4]) {
+    const uint32_t M = 0x43004300u;
+    r[0] = lop3_and_or(w, 0x00030003u, M);
+    r[1] = lop3_and_or(w, 0x000C000Cu, M);
+    r[2] = lop3_and_or(w, 0x00300030u, M);
+    r[3] = lop3_and_or(w >> 6, 0x00030003u, M);
+}
+__device__ __forceinline__ void codes_to_bf16x2_hi(uint32_t w, uint32_t (&r)[4]) {
+    const uint32_t M = 0x43004300u;
+    uint32_t t = w >> 6;
+    r[0] = lop3_and_or(t, 0x000C000Cu, M);
+    r[1] = lop3_and_or(t, 0x00300030u, M);
+    t = w >> 12;
+    r[2] = lop3_and_or(t, 0x00030003u, M);
+    r[3] = lop3_and_or(t, 0x000C000Cu, M);
+}
+
 // =================================================================================================
 // Stage 1
 // =================================================================================================
@@ -192,6 +223,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int split = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    OMMX_TR(250);
 
     // ---- split range (same rounding as the reference, paged_decode.py:1428-1432) ----
     const int seq = p.b_seq_len[b];
@@ -221,7 +253,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     const uint32_t bar_full = smem_u32(s_bar), bar_empty = smem_u32(s_bar + NSTAGES);
     const uint32_t bar_tfull = smem_u32(s_bar + 2 * NSTAGES), bar_tempty = smem_u32(s_bar + 2 * NSTAGES + NCW);
 
-    // ---- prologue: LUT, barriers (the producer warp alone loads the page / slot tables) ----
+    // ---- prologue: LUT, barriers, copy descriptors and the split's page / slot tables, spread over the
+    //      whole CTA so that the producer can issue the first stage right after the barrier ----
     if (threadIdx.x < 16) {
         const int c = threadIdx.x;
         const int mi = ((c >> 1) & 3) * 2 + (c & 1);                    // exp*2 + mant
@@ -240,24 +273,15 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __syncthreads();
-    // Stage 2 is launched as a programmatic dependent: it may start its own prologue (residual-row
-    // logits, which do not depend on this kernel) as soon as SM resources free up, and waits for this
-    // grid to finish before it reads the split partials.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-    // ---- roles; each branch starts by resizing its warpgroups' register budget and never rejoins ----
-    if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
-    if (warp == PRODUCER_WARP) {
-        // =========================== producer warp ===========================
-        // Copy roles (group-in-stage, plane) are tabulated once in shared memory; the loop body is one
-        // descriptor load, one table lookup, one multiply-add and one bulk copy per role, with no
-        // divergent paths, because this single warp's issue latency bounds how fast stages refill.
-        const int cpg = 4 * p.ppg + 6;                                  // copies per group
-        const int ncopies = GS * cpg;
+    const int cpg = 4 * p.ppg + 6;                                      // copies per group
+    const int ncopies = GS * cpg;
+    {
+        // Copy roles (group-in-stage, plane) are tabulated once; the producer's loop body is then one
+        // descriptor load, one table lookup, one multiply-add and one copy per role, with no divergent
+        // paths, because that single warp's issue latency bounds how fast stages refill.
         const uint32_t page_b = (uint32_t)p.ps * H;                     // (token, head) rows per page
-        uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
-        for (int c = lane; c < ncopies; c += 32) {
+        const int c = (int)threadIdx.x - 64;                            // threads 64.. build one descriptor each
+        if (c >= 0 && c < ncopies) {
             CopyDesc d;
             d.src = nullptr; d.unit = 0; d.dst = 0; d.tbase = 0; d.tmul = 0; d.gi = 0; d.tok0 = 0;
             const int gi = c / cpg, ci = c - gi * cpg;
@@ -284,33 +308,46 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 }
             }
             s_desc[c] = d;
-            full_total += d.unit;
         }
+        // page ids first (s_tab[0..)), group slots behind them
+        const int g0 = p.seg_group_base + t0 / 32;                      // first logical group
+        const int npages = (ntok + p.ps - 1) / p.ps;
+        const int64_t pg0 = ((int64_t)g0 * 32) / p.ps;
+        for (int i = threadIdx.x; i < npages; i += S1_THREADS) {
+            int64_t pg = load_index(p.r2t, p.tbl64, (int64_t)b * p.r2t_sb + pg0 + i);
+            if (pg < 0 || pg >= p.num_pages) { or_status(p.status, OMMX_ST_BAD_PAGE); pg = 0; }
+            s_tab[i] = (int)pg;
+        }
+        for (int i = S1_THREADS - 1 - (int)threadIdx.x; i < ngroups; i += S1_THREADS) {
+            int64_t sl = load_index(p.r2g, p.tbl64, (int64_t)b * p.r2g_sb + g0 + i);
+            if (sl < 0 || sl >= p.num_slots) { or_status(p.status, OMMX_ST_BAD_GROUP); sl = 0; }
+            s_tab[MAX_SPLIT_PAGES + i] = (int)sl;
+        }
+    }
+    __syncthreads();
+    OMMX_TR(251);
+    // Stage 2 is launched as a programmatic dependent: it may start its own prologue (residual-row
+    // logits, which do not depend on this kernel) as soon as SM resources free up, and waits for this
+    // grid to finish before it reads the split partials.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // ---- roles; each branch starts by resizing its warpgroups' register budget and never rejoins ----
+    if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
+    if (warp == PRODUCER_WARP) {
+        // =========================== producer warp ===========================
+        uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
+        for (int c = lane; c < ncopies; c += 32) full_total += s_desc[c].unit;
         full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
-        {   // page ids first (s_tab[0..)), group slots behind them
-            const int g0 = p.seg_group_base + t0 / 32;                  // first logical group
-            const int npages = (ntok + p.ps - 1) / p.ps;
-            const int64_t pg0 = ((int64_t)g0 * 32) / p.ps;
-            for (int i = lane; i < npages; i += 32) {
-                int64_t pg = load_index(p.r2t, p.tbl64, (int64_t)b * p.r2t_sb + pg0 + i);
-                if (pg < 0 || pg >= p.num_pages) { or_status(p.status, OMMX_ST_BAD_PAGE); pg = 0; }
-                s_tab[i] = (int)pg;
-            }
-            for (int i = lane; i < ngroups; i += 32) {
-                int64_t sl = load_index(p.r2g, p.tbl64, (int64_t)b * p.r2g_sb + g0 + i);
-                if (sl < 0 || sl >= p.num_slots) { or_status(p.status, OMMX_ST_BAD_GROUP); sl = 0; }
-                s_tab[MAX_SPLIT_PAGES + i] = (int)sl;
-            }
-            __syncwarp();
-        }
         const int whole_groups = ntok / 32;
         for (int it = 0; it < n_iters; ++it) {
             const int s = it % NSTAGES;
             const uint32_t ph = (it / NSTAGES) & 1;
+            OMMX_TR(4 * it);
             if (!mbar_wait(bar_empty + 8 * s, ph ^ 1)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
             }
+            OMMX_TR(4 * it + 1);
             const int lg0 = it * GS;
             uint32_t total = full_total;
             if (lg0 + GS > whole_groups) {                              // last stage: fewer groups or a partial group
@@ -335,6 +372,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     else tma_2d_g2s(sbase + d.dst, kind == 1 ? &p.tmap_k : &p.tmap_v, 0, (int32_t)idx * p.rows_per_page, bar_full + 8 * s);
                 }
             }
+            OMMX_TR(4 * it + 2);
         }
         // fall through to the two CTA-wide barriers of the epilogue
         __syncthreads();
@@ -375,6 +413,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         }
         for (int n = dw; n < n_iters * NCW; n += NDW) {
             const int it = n / NCW, unit = n % NCW;
+            const int trk = 8 * ((n - dw) / NDW);
+            OMMX_TR(trk);
             const int h = unit % H, gsel = unit / H;
             uint8_t *tile = s_tiles + unit * DT_BYTES;
             const int s = it % NSTAGES;
@@ -383,6 +423,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
             }
+            OMMX_TR(trk + 1);
             const int lg = it * GS + gsel;                           // local group of this unit
             if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
                 // Tile `it` of a unit may be written once the MMA warp has read tile it-1.  Decode warps
@@ -398,6 +439,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                     break;
                 }
+                OMMX_TR(trk + 2);
             {
                     const bool splice = k_out > 0 && !no_outlier;
                     if (splice) {
@@ -436,6 +478,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                             st[0] = w0 & 0xFFu; st[1] = (w0 >> 8) & 0xFFu; st[2] = (w0 >> 16) & 0xFFu; st[3] = w0 >> 24;
                         }
                     }
+                    OMMX_TR(trk + 3);
                     const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
                     const uint8_t *kreg = gb;                            // k_base region of the group (1 KB aligned)
                     const uint32_t kl_off = (uint32_t)(h * 32 + lane);     // this lane's code byte (channels 4*lane..+3)
@@ -496,6 +539,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     }
                     __syncwarp();
                 }
+                OMMX_TR(trk + 4);
 
                 if (lane == 0) mbar_arrive(bar_tfull + 8 * unit);
             }
@@ -521,15 +565,30 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     uint32_t QS[16];
     {
         const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (row_ok ? row_head : 0)) * p.q_sh;
+        // this lane's 32 channels are contiguous: four 16-byte loads when the row allows it
+        uint32_t qw[16];
+        if ((reinterpret_cast<uintptr_t>(qrow) & 15u) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 t = reinterpret_cast<const uint4 *>(qrow + 32 * j)[v];
+                qw[4 * v] = t.x; qw[4 * v + 1] = t.y; qw[4 * v + 2] = t.z; qw[4 * v + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int v = 0; v < 16; ++v) {
+                const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qrow + 32 * j);
+                qw[v] = (uint32_t)q16[2 * v] | ((uint32_t)q16[2 * v + 1] << 16);
+            }
+        }
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
             const int wi = r >> 3, i = r & 7;
-            const int ch = 32 * j + 16 * wi + i;
+            const int e0 = 16 * wi + i, e1 = e0 + 8;                  // channel 32j + e0 / + e1
             const float f = 0.5f / (float)(1 << (2 * pos_class(i)));
             float lo = 0.f, hi = 0.f;
             if (row_ok) {
-                lo = bf16_round_f32(__bfloat162float(qrow[ch]) * p.sm_scale) * f;
-                hi = bf16_round_f32(__bfloat162float(qrow[ch + 8]) * p.sm_scale) * f;
+                lo = bf16_round_f32(bf16_bits_to_f32((qw[e0 >> 1] >> (16 * (e0 & 1))) & 0xFFFFu) * p.sm_scale) * f;
+                hi = bf16_round_f32(bf16_bits_to_f32((qw[e1 >> 1] >> (16 * (e1 & 1))) & 0xFFFFu) * p.sm_scale) * f;
             }
             QS[r] = pack_bf16x2(lo, hi);
         }
@@ -547,14 +606,17 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     float acc_vz[4] = {0.f, 0.f, 0.f, 0.f};      // VFOLD: sum_t P[row][t] * vz[t][cg = column]
     uint32_t consumed = 0;
 
+    OMMX_TR(252);
     for (int it = 0; it < n_iters; ++it) {
         const int s = it % NSTAGES;
         const uint32_t ph = (it / NSTAGES) & 1;
+        OMMX_TR(8 * it);
         if (!mbar_wait(bar_full + 8 * s, ph)) {
             if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
             m_run = -INFINITY; l_run = 0.f;
             break;
         }
+        OMMX_TR(8 * it + 1);
         const int lg = it * GS + gsel;                               // local group of this warp
         if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
             uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
@@ -594,12 +656,14 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     for (int kk = 0; kk < 4; ++kk) mma_bf16(C[nt], QQ[8 + 2 * kk], 0u, QQ[8 + 2 * kk + 1], 0u, R[2 * kk], R[2 * kk + 1]);
                 }
             }
+            OMMX_TR(8 * it + 2);
             // outlier tile (+ zp / -128 rows as n-tile 4), built by the decode warp of this unit
             if (!mbar_wait(bar_tfull + 8 * unit, consumed & 1u)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 m_run = -INFINITY; l_run = 0.f;
                 break;
             }
+            OMMX_TR(8 * it + 3);
             {
                 const int mi = lane >> 3, rr = lane & 7;
 #pragma unroll
@@ -620,6 +684,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * (NSTAGES * unit + (consumed % NSTAGES)));   // the next tile may be built
             ++consumed;
+            OMMX_TR(8 * it + 4);
             // q.zp - 128*sum(q'') sits in columns 0 and 1 of n-tile 4 (lanes with j == 0)
             float qzo = C[4][0] + C[4][1];
             qzo = __shfl_sync(0xFFFFFFFFu, qzo, lane & ~3);
@@ -672,6 +737,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 }
             }
 
+            OMMX_TR(8 * it + 5);
             // ======================= P.V =======================
             // lane (g, j) supplies channel column g of every n-tile: channels 16*g + i, scale group g/2
             if (!(p.abl & ABL_NO_V)) {
@@ -757,7 +823,9 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         // release the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        OMMX_TR(8 * it + 6);
     }
+    OMMX_TR(253);
 
     // ---- epilogue: finalize this lane's 32 output channels, merge warps that share a head ----
     // Every lane ends up with outv[0..15] = channels 32j + i and outv[16..31] = channels 32j + 16 + i of
@@ -824,6 +892,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             if (lse_writer) dst[HD] = l_tot > 0.f ? m_run + logf(l_tot) : -INFINITY;
         }
     }
+    OMMX_TR(254);
 }
 
 // =================================================================================================
@@ -1297,3 +1366,10 @@ extern "C" int ommx_b200_merge_states(const float *o_parts, const float *lse_par
     count_launch();
     return 0;
 }
+
+#ifdef OMMX_TRACE
+// Development builds only: copy the probe array (32 warps x 256 slots of SM clock values) to the host.
+extern "C" int ommx_b200_debug_read_trace(long long *host_out) {
+    return cudaMemcpyFromSymbol(host_out, ommx::g_trace, sizeof(long long) * 32 * 256) == cudaSuccess ? 0 : OMMX_E_CUDA;
+}
+#endif
