@@ -34,6 +34,7 @@ extern "C" {
 #define OMMX_ST_NONFINITE    4     /* packer saw NaN/Inf in K or V */
 #define OMMX_ST_TIMEOUT      8     /* a bounded wait inside a kernel ran out */
 #define OMMX_ST_BAD_LENGTH  16     /* b_seq_len needs more groups per split than a CTA can index */
+#define OMMX_ST_SCALE_RANGE 32     /* a K or V scale exponent above 11 was clamped in decode (scale step > 2048) */
 
 /* element types of q / o / k,v inputs */
 #define OMMX_DT_F32   0

@@ -13,10 +13,11 @@ LIB_PATH = os.path.join(PKG, "libommx_b200.so")
 
 OMMX_DT_F32, OMMX_DT_BF16, OMMX_DT_F16 = 0, 1, 2
 OMMX_SCALE_INT8_EXP, OMMX_SCALE_BF16, OMMX_SCALE_F32 = 0, 1, 2
-ST_BAD_PAGE, ST_BAD_GROUP, ST_NONFINITE, ST_TIMEOUT, ST_BAD_LENGTH = 1, 2, 4, 8, 16
+ST_BAD_PAGE, ST_BAD_GROUP, ST_NONFINITE, ST_TIMEOUT, ST_BAD_LENGTH, ST_SCALE_RANGE = 1, 2, 4, 8, 16, 32
 STATUS_NAMES = {ST_BAD_PAGE: "page id out of range", ST_BAD_GROUP: "group slot out of range",
                 ST_NONFINITE: "non-finite K/V value", ST_TIMEOUT: "a bounded device wait ran out",
-                ST_BAD_LENGTH: "a split holds more groups than one CTA can index"}
+                ST_BAD_LENGTH: "a split holds more groups than one CTA can index",
+                ST_SCALE_RANGE: "a scale exponent above 11 was clamped"}
 
 
 class KVPlanes(C.Structure):

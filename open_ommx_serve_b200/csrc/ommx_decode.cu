@@ -32,20 +32,27 @@
 namespace ommx {
 
 constexpr int HD = 128;                 // head_dim this build serves
-constexpr int NCW = 8;                  // (group, head) units in flight per CTA: 8 MMA warps + 8 decode warps
-constexpr int NDW = 11;                 // decode warps (stateless tile builders, items dealt round-robin)
-constexpr int PRODUCER_WARP = NCW + NDW;  // warp 19 streams the planes
+constexpr int NCW = 8;                  // (group, head) units in flight per CTA, one MMA warp each
+constexpr int NDW = 15;                 // decode warps (stateless sidecar builders, items dealt round-robin)
+constexpr int PRODUCER_WARP = NCW + NDW;  // warp 23 streams the planes
 constexpr int S1_THREADS = (NCW + NDW + 1) * 32;
 // Register budget per role (setmaxnreg, warpgroup granularity).  Only what the CTA was launched with
-// can be moved around: 640 threads x 96 = 61440 >= 256*152 (MMA) + 384*56 (decode + producer) = 60416.
-#define OMMX_REGS_MMA "152"
+// can be moved around: 768 threads x 80 = 61440 = 256*128 (MMA) + 512*56 (decode + producer).  The
+// launch refuses to run if the compiled kernel holds fewer registers than the roles ask for, because
+// setmaxnreg.inc would then wait forever.
+#define OMMX_REGS_MMA "128"
 #define OMMX_REGS_DECODE "56"
-constexpr int NSTAGES = 4;
-constexpr int DT_STRIDE = 272;          // bytes per outlier-tile row (256 data + 16 pad)
-constexpr int DT_ROWS = 34;             // 32 tokens + zp row + (-128) row
+constexpr int REGS_MMA = 128, REGS_DECODE = 56;
+constexpr int MAX_STAGES = 4;           // ring depth (3 when the planes of a stage are large)
+constexpr int DT_STRIDE = 272;          // bytes per sidecar-tile row (256 data + 16 pad)
+constexpr int ROW_ZP = 32;              // K zero-points, fp16, channel order
+constexpr int ROW_KF = 33;              // K scale factors 2^(e+4), fp16, in code-fragment order
+constexpr int ROW_VF = 34;              // V scale factors, fp16, fragment order (rows 34, 35: two copies)
+constexpr int ROW_ZT = 36;              // V zero-points [scale group][token], fp16 (rows 36, 37: two copies)
+constexpr int DT_ROWS = 38;             // rows 0..31: outlier deltas [token][channel], fp16
 constexpr int DT_BYTES = DT_ROWS * DT_STRIDE;
 constexpr int MAX_SPLIT_GROUPS = 512;   // groups one CTA can index (16K tokens per split)
-constexpr int MAX_SPLIT_PAGES = 2048;
+constexpr int MAX_SPLIT_PAGES = 1024;
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // about a second of SM clock: the wait has failed
 
 struct S1Params {
@@ -65,7 +72,7 @@ struct S1Params {
     int32_t *status;
     int32_t abl;
     // shared-memory layout of one group block (bytes)
-    int32_t GS, gb_bytes, stage_bytes;
+    int32_t GS, gb_bytes, stage_bytes, nstages;
     int32_t o_vm, o_vs, o_vz, o_ks, o_kz, o_ms, o_mc, o_bm, o_ov;
     // tensor maps of the two code planes as [bytes/128][128] uint8 with 128-byte swizzle
     uint32_t swz;                        // 0x70 when the maps are in use, else 0
@@ -143,6 +150,31 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t &r0, uint32_t &r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+// transpose an 8x8 matrix of 16-bit elements held one row pair per lane (the accumulator layout)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t hmul2_f16(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -160,47 +192,8 @@ __device__ __forceinline__ void tma_2d_g2s(uint32_t dst, const CUtensorMap *map,
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
-// position class of channel-in-word index i (0..7): the 2-bit field sits at bit 2*pc of its half
-// when the LOP3 extracts it, so the extracted bf16 is 128 + code * 4^pc.
-__device__ __forceinline__ int pos_class(int i) { return i < 3 ? i : (i < 6 ? i - 3 : i - 6); }
-
 __device__ __forceinline__ int64_t load_index(const void *tbl, int is64, int64_t i) {
     return is64 ? reinterpret_cast<const int64_t *>(tbl)[i] : (int64_t) reinterpret_cast<const int32_t *>(tbl)[i];
-}
-
-// Extract the 8 bf16x2 registers of one 32-bit code word: register i holds (code i, code i+8)
-// as bf16 values 128 + code * 4^pos_class(i).
-__device__ __forceinline__ void codes_to_bf16x2(uint32_t w, uint32_t (&r)[8]) {
-    const uint32_t M = 0x43004300u;
-    r[0] = lop3_and_or(w, 0x00030003u, M);
-    r[1] = lop3_and_or(w, 0x000C000Cu, M);
-    r[2] = lop3_and_or(w, 0x00300030u, M);
-    uint32_t t = w >> 6;
-    r[3] = lop3_and_or(t, 0x00030003u, M);
-    r[4] = lop3_and_or(t, 0x000C000Cu, M);
-    r[5] = lop3_and_or(t, 0x00300030u, M);
-    t = w >> 12;
-    r[6] = lop3_and_or(t, 0x00030003u, M);
-    r[7] = lop3_and_or(t, 0x000C000Cu, M);
-}
-
-// The same extraction in two halves (registers 0..3, then 4..7), for loops that interleave several
-// code words so that back-to-back MMAs never share an accumulator.
-__device__ __forceinline__ void codes_to_bf16x2_lo(uint32_t w, uint32_t (&r)[4]) {
-    const uint32_t M = 0x43004300u;
-    r[0] = lop3_and_or(w, 0x00030003u, M);
-    r[1] = lop3_and_or(w, 0x000C000Cu, M);
-    r[2] = lop3_and_or(w, 0x00300030u, M);
-    r[3] = lop3_and_or(w >> 6, 0x00030003u, M);
-}
-__device__ __forceinline__ void codes_to_bf16x2_hi(uint32_t w, uint32_t (&r)[4]) {
-    const uint32_t M = 0x43004300u;
-    uint32_t t = w >> 6;
-    r[0] = lop3_and_or(t, 0x000C000Cu, M);
-    r[1] = lop3_and_or(t, 0x00300030u, M);
-    t = w >> 12;
-    r[2] = lop3_and_or(t, 0x00030003u, M);
-    r[3] = lop3_and_or(t, 0x000C000Cu, M);
 }
 
 // =================================================================================================
@@ -211,12 +204,49 @@ __device__ __forceinline__ void codes_to_bf16x2_hi(uint32_t w, uint32_t (&r)[4])
 // and P.V, 4 = skip the K code dequant and its MMAs.
 constexpr int ABL_NO_OUTLIER = 1, ABL_NO_V = 2, ABL_NO_K = 4, ABL_NO_COMPUTE = 8;   // 8: stream the planes only
 
+// fp16 bits of 2^(e + FBIAS).  Exponents below -18 give 0 (such a scale step is under 2^-18 and the
+// term it multiplies is dropped); exponents above 11 are clamped and reported.
+constexpr int FBIAS = 4;
+__device__ __forceinline__ uint32_t pow2_f16_bits(int e, bool &clamped) {
+    int u = e + 15 + FBIAS;
+    clamped = u > 30;
+    u = min(u, 30);
+    return u < 1 ? 0u : (uint32_t)u << 10;
+}
+// the reference rounds an outlier's delta to bf16; keep that rounding point, then store it as fp16
+// (exact: 8 significant bits fit in 11)
+__device__ __forceinline__ uint32_t f16_bits_of_bf16_rounded(float x) {
+    uint16_t r;
+    const float xb = bf16_round_f32(x);
+    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(r) : "f"(xb));
+    return (uint32_t)r;
+}
+__device__ __forceinline__ uint32_t f16_bits_sat(float x) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(r) : "f"(x));
+    return (uint32_t)r;
+}
+// field i (0..7) of the lower and upper 8 codes of a 32-bit code word, as two fp16 subnormals
+// code * 4^slot * 2^-24 with slot = i (i < 5) or i - 5: no arithmetic beyond the AND
+__device__ __forceinline__ uint32_t code_pair(uint32_t w, int i) {
+    return i < 5 ? (w & (0x00030003u << (2 * i))) : ((w >> 10) & (0x00030003u << (2 * (i - 5))));
+}
+__device__ __forceinline__ int code_slot(int i) { return i < 5 ? i : i - 5; }
+
 // KOUT: outliers per K vector known at compile time (static, unrolled splice) or -1 (runtime).
-// VFOLD: GQA groups of at most 4 query heads.  The 16 MMA rows are (query head, V scale group)
-//        pairs, the per-(token, group) power-of-two V scale is folded into P, and V enters the
-//        MMA as raw 128 + code*4^pc values: no per-element V arithmetic at all.  The offset comes
-//        back out through a row-sum column, the zero-points through a small bias MMA.
-template <int KOUT, bool VFOLD>
+//
+// Every MMA is m16n8k16 fp16 with the 2-bit codes as the A operand: a code field masked in place is an
+// fp16 subnormal, code * 4^slot * 2^-24, exact and without an offset.  N = 8 columns are the query heads
+// of the kv head (GQA <= 8).
+//   logits   S^T[token][head]  = codes[token][ch] . (q * 2^e_k)[ch][head]      (2 m-tiles x 8 k-steps)
+//                              + delta[token][ch] . q[ch][head]                (sidecar tile, same shape)
+//                              + zp[ch] . q[ch][head]                          (one row, broadcast)
+//   output   O^T[ch][head]     = codes^T[ch][token] . (P * 2^e_v)[token][head] (8 m-tiles x 2 k-steps, the
+//                                16 rows of an m-tile lie in one V scale group)
+//                              + vz^T[group][token] . P[token][head]
+// The power-of-two factors, zero-points and deltas of a unit are laid out for these fragments by the
+// decode warps (the sidecar tile), so the MMA warps multiply and accumulate and do little else.
+template <int KOUT>
 __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __grid_constant__ S1Params p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzle atoms are 1 KB: align the ring by hand (the launch adds 1 KB of slack)
@@ -234,24 +264,24 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     if (t1 <= t0) return;
     const int ntok = t1 - t0;
     int ngroups = (ntok + 31) / 32;
-    if (ngroups > MAX_SPLIT_GROUPS) {                 // host sizing should prevent this
+    if (ngroups > MAX_SPLIT_GROUPS || ngroups * p.ppg > MAX_SPLIT_PAGES) {   // host sizing should prevent this
         if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_LENGTH);
         return;
     }
-    const int H = p.H, GS = p.GS;
+    const int H = p.H, GS = p.GS, NS = p.nstages;
     const int n_iters = (ngroups + GS - 1) / GS;
     const int k_out = KOUT >= 0 ? KOUT : p.k_out;
 
     // ---- shared memory carve-up ----
-    uint8_t *s_stage = smem;                                            // NSTAGES * stage_bytes
-    uint8_t *s_tiles = s_stage + NSTAGES * p.stage_bytes;               // NCW * DT_BYTES
+    uint8_t *s_stage = smem;                                            // nstages * stage_bytes
+    uint8_t *s_tiles = s_stage + NS * p.stage_bytes;                    // NCW * DT_BYTES
     int32_t *s_tab = reinterpret_cast<int32_t *>(s_tiles + NCW * DT_BYTES);   // page ids, then group slots
     float *s_lut = reinterpret_cast<float *>(s_tab + MAX_SPLIT_PAGES + MAX_SPLIT_GROUPS);
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[NSTAGES], empty[NSTAGES], tile_full[NCW], tile_empty[NCW][NSTAGES]
-    int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * NSTAGES + (1 + NSTAGES) * NCW);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[], empty[], tile_full[NCW], tile_empty[NCW][]
+    int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * MAX_STAGES + (1 + MAX_STAGES) * NCW);
     CopyDesc *s_desc = reinterpret_cast<CopyDesc *>(s_abort + 4);
-    const uint32_t bar_full = smem_u32(s_bar), bar_empty = smem_u32(s_bar + NSTAGES);
-    const uint32_t bar_tfull = smem_u32(s_bar + 2 * NSTAGES), bar_tempty = smem_u32(s_bar + 2 * NSTAGES + NCW);
+    const uint32_t bar_full = smem_u32(s_bar), bar_empty = smem_u32(s_bar + MAX_STAGES);
+    const uint32_t bar_tfull = smem_u32(s_bar + 2 * MAX_STAGES), bar_tempty = smem_u32(s_bar + 2 * MAX_STAGES + NCW);
 
     // ---- prologue: LUT, barriers, copy descriptors and the split's page / slot tables, spread over the
     //      whole CTA so that the producer can issue the first stage right after the barrier ----
@@ -262,13 +292,13 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         s_lut[c] = (c & 8) ? -mag : mag;
     }
     if (threadIdx.x == 32) {
-        for (int s = 0; s < NSTAGES; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 2 * NCW);
+            mbar_init(bar_empty + 8 * s, 3 * NCW);                  // 8 MMA warps + 16 tile halves
         }
         for (int u = 0; u < NCW; ++u) {
-            mbar_init(bar_tfull + 8 * u, 1);
-            for (int k2 = 0; k2 < NSTAGES; ++k2) mbar_init(bar_tempty + 8 * (NSTAGES * u + k2), 1);
+            mbar_init(bar_tfull + 8 * u, 2);                        // the two halves of a tile
+            for (int k2 = 0; k2 < MAX_STAGES; ++k2) mbar_init(bar_tempty + 8 * (MAX_STAGES * u + k2), 1);
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -340,8 +370,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
         const int whole_groups = ntok / 32;
         for (int it = 0; it < n_iters; ++it) {
-            const int s = it % NSTAGES;
-            const uint32_t ph = (it / NSTAGES) & 1;
+            const int s = it % NS;
+            const uint32_t ph = (it / NS) & 1;
             OMMX_TR(4 * it);
             if (!mbar_wait(bar_empty + 8 * s, ph ^ 1)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
@@ -389,36 +419,26 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     const bool no_outlier = (p.abl & ABL_NO_OUTLIER) != 0;
 
     if (warp >= NCW) {
-        // =========================== decode warps (phase A) ===========================
-        // Build a unit's outlier-delta tile one group ahead of its MMA warp: wait until the MMA warp
-        // has read the previous tile of that unit, write the new one, publish it.
+        // =========================== decode warps ===========================
+        // Build the sidecar tile of a unit between two uses by its MMA warp.  A tile is built in two
+        // halves by two warps at once, because the MMA warp of the unit waits for it: half hf takes K
+        // channels 64hf..64hf+63 (lane l: channels 64hf + 2l, +1 - delta columns, zero-points, scale
+        // factors) and V tokens 16hf..16hf+15 (lane l: token 16hf + l%16, scale groups 2(l/16), +1).
         const int dw = warp - NCW;
-        // this lane owns channels 4*lane + c
-        uint32_t pa_col[4];       // byte offset of the channel's column inside an outlier-tile row
-        float pa_f[4];            // 4^pc of the channel's slot
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int d = 4 * lane + c;
-            const int jj = d >> 5, wi = (d >> 4) & 1, i = d & 7, hi = (d >> 3) & 1;
-            pa_col[c] = 2u * (16 * (4 * wi + (i >> 1)) + 8 * (i & 1) + 2 * jj + hi);
-            pa_f[c] = (float)(1 << (2 * pos_class(i)));
-        }
-        if (dw < NCW) {           // item (0, dw) is this warp's: it is the first to touch tile dw
+        if (dw < NCW) {           // the first to touch tile dw clears it once (unused rows stay zero)
             uint8_t *t0p = s_tiles + dw * DT_BYTES;
-            // row 33 = -128 in every column (never rewritten); clear the rest once
             for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(t0p)[i] = 0u;
-            __syncwarp();
-            for (int i = lane; i < 64; i += 32) reinterpret_cast<uint32_t *>(t0p + 33 * DT_STRIDE)[i] = 0xC300C300u;
-            __syncwarp();
         }
-        for (int n = dw; n < n_iters * NCW; n += NDW) {
-            const int it = n / NCW, unit = n % NCW;
+        // every tile is cleared before any half of it is written (only decode warps take part)
+        asm volatile("bar.sync 1, %0;" ::"n"(NDW * 32) : "memory");
+        for (int n = dw; n < n_iters * NCW * 2; n += NDW) {
+            const int it = n / (2 * NCW), unit = (n >> 1) % NCW, hf = n & 1;
             const int trk = 8 * ((n - dw) / NDW);
             OMMX_TR(trk);
             const int h = unit % H, gsel = unit / H;
             uint8_t *tile = s_tiles + unit * DT_BYTES;
-            const int s = it % NSTAGES;
-            const uint32_t ph = (it / NSTAGES) & 1;
+            const int s = it % NS;
+            const uint32_t ph = (it / NS) & 1;
             if (!mbar_wait(bar_full + 8 * s, ph)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
@@ -427,120 +447,139 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             const int lg = it * GS + gsel;                           // local group of this unit
             if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
                 // Tile `it` of a unit may be written once the MMA warp has read tile it-1.  Decode warps
-                // run up to NSTAGES groups ahead and the tiles of one unit are built by different warps,
-                // so "tile k was read" events rotate over NSTAGES barriers per unit (barrier k % NSTAGES,
-                // phase k / NSTAGES): the newest event a waiter can be missing is then always the one it
-                // waits for, never an older phase of the same parity.
+                // run up to NS groups ahead and the tiles of one unit are built by different warps, so
+                // "tile k was read" events rotate over NS barriers per unit (barrier k % NS, phase
+                // k / NS): the newest event a waiter can be missing is then always the one it waits
+                // for, never an older phase of the same parity.
                 uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
-                const uint8_t *ksc = gb + p.o_ks + h * 128;
-                const uint8_t *kzp = gb + p.o_kz + h * 256;
-                if (it > 0 && !mbar_wait(bar_tempty + 8 * (NSTAGES * unit + ((it - 1) % NSTAGES)),
-                                         (uint32_t)((it - 1) / NSTAGES) & 1u)) {
+                const int d0 = 64 * hf + 2 * lane;                   // first of this lane's two channels
+                if (it > 0 && !mbar_wait(bar_tempty + 8 * (MAX_STAGES * unit + ((it - 1) % NS)),
+                                         (uint32_t)((it - 1) / NS) & 1u)) {
                     if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                     break;
                 }
                 OMMX_TR(trk + 2);
-            {
-                    const bool splice = k_out > 0 && !no_outlier;
-                    if (splice) {
-                        // clear token rows 0..31 (256 data bytes each)
+                bool clamped_any = false;
+                const bool splice = k_out > 0 && !no_outlier;
+                if (splice) {
+                    // clear this half's columns of token rows 0..31 (128 bytes per row)
 #pragma unroll
-                        for (int r2 = 0; r2 < 16; ++r2)
-                            *reinterpret_cast<uint4 *>(tile + (2 * r2 + (lane >> 4)) * DT_STRIDE + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
-                        __syncwarp();
-                    }
-                    const uint32_t e4 = *reinterpret_cast<const uint32_t *>(ksc + 4 * lane);
-                    const uint2 z4 = *reinterpret_cast<const uint2 *>(kzp + 8 * lane);
-                    uint2 ms4 = make_uint2(0, 0), mc4 = make_uint2(0, 0);
-                    uint4 bm4 = make_uint4(0, 0, 0, 0);
-                    uint32_t st[4] = {0, 0, 0, 0};
-                    if (splice) {
-                        if (p.use_map) {
-                            ms4 = *reinterpret_cast<const uint2 *>(gb + p.o_ms + h * 256 + 8 * lane);
-                            mc4 = *reinterpret_cast<const uint2 *>(gb + p.o_mc + h * 256 + 8 * lane);
-                        }
-                        bm4 = *reinterpret_cast<const uint4 *>(gb + p.o_bm + h * 512 + 16 * lane);
-                        const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
-                        const uint32_t *ov = reinterpret_cast<const uint32_t *>(gb + p.o_ov + h * 128 * nb + 4 * nb * lane);
-                        if (nb == 3) {
-                            const uint32_t w0 = ov[0], w1 = ov[1], w2 = ov[2];
-                            st[0] = w0 & 0xFFFFFFu;
-                            st[1] = (w0 >> 24) | ((w1 & 0xFFFFu) << 8);
-                            st[2] = (w1 >> 16) | ((w2 & 0xFFu) << 16);
-                            st[3] = w2 >> 8;
-                        } else if (nb == 4) {
-                            st[0] = ov[0]; st[1] = ov[1]; st[2] = ov[2]; st[3] = ov[3];
-                        } else if (nb == 2) {
-                            const uint32_t w0 = ov[0], w1 = ov[1];
-                            st[0] = w0 & 0xFFFFu; st[1] = w0 >> 16; st[2] = w1 & 0xFFFFu; st[3] = w1 >> 16;
-                        } else {
-                            const uint32_t w0 = ov[0];
-                            st[0] = w0 & 0xFFu; st[1] = (w0 >> 8) & 0xFFu; st[2] = (w0 >> 16) & 0xFFu; st[3] = w0 >> 24;
-                        }
-                    }
-                    OMMX_TR(trk + 3);
-                    const uint32_t bmv[4] = {bm4.x, bm4.y, bm4.z, bm4.w};
-                    const uint8_t *kreg = gb;                            // k_base region of the group (1 KB aligned)
-                    const uint32_t kl_off = (uint32_t)(h * 32 + lane);     // this lane's code byte (channels 4*lane..+3)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int e = (int)(int8_t)(e4 >> (8 * c));
-                        const float inv_s = __uint_as_float((uint32_t)(127 - e) << 23);
-                        const uint32_t zw = (c & 2) ? z4.y : z4.x;
-                        const float zp = bf16_bits_to_f32((c & 1) ? (zw >> 16) : (zw & 0xFFFFu));
-                        const float fs = inv_s * pa_f[c];
-                        // zp row: zp / scale in slot units (exact power-of-two scaling of a bf16)
-                        *reinterpret_cast<__nv_bfloat16 *>(tile + 32 * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(zp * fs);
-                        if (splice) {
-                            float A, Bc;
-                            if (p.use_map) {
-                                const uint32_t msw = (c & 2) ? ms4.y : ms4.x, mcw = (c & 2) ? mc4.y : mc4.x;
-                                const float ms = bf16_bits_to_f32((c & 1) ? (msw >> 16) : (msw & 0xFFFFu));
-                                const float mc = bf16_bits_to_f32((c & 1) ? (mcw >> 16) : (mcw & 0xFFFFu));
-                                A = __fdividef(fs, ms);
-                                Bc = (mc - zp) * fs;
-                            } else {
-                                A = pa_f[c];                              // (lvl*s + zp - zp)/s = lvl
-                                Bc = 0.f;
-                            }
-                            uint32_t bits = bmv[c];
-                            const uint32_t stream = st[c];
-                            const float nf = -pa_f[c];
-                            // delta between the outlier value and the base code it replaces, in code units:
-                            // ((lvl/ms + mc) - (code*s + zp)) / s, rounded to bf16 as the reference rounds
-                            // its delta (the scaling by 1/s and 4^pc is exact)
-                            if (KOUT > 0) {
-                                if (__popc(bits) == KOUT) {
-#pragma unroll
-                                    for (int r = KOUT - 1; r >= 0; --r) {
-                                        const int pz = 31 - __clz(bits);
-                                        bits ^= 1u << pz;
-                                        const uint32_t nib = (stream >> (4 * r)) & 0xFu;
-                                        const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> (2 * c)) & 3u);
-                                        const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
-                                        *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
-                                    }
-                                } else {
-                                    or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
-                                }
-                            } else {
-                                int r = __popc(bits) - 1;
-                                while (bits) {
-                                    const int pz = 31 - __clz(bits);
-                                    bits ^= 1u << pz;
-                                    const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
-                                    --r;
-                                    const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> (2 * c)) & 3u);
-                                    const float X = fmaf(cf, nf, fmaf(s_lut[nib], A, Bc));
-                                    *reinterpret_cast<__nv_bfloat16 *>(tile + pz * DT_STRIDE + pa_col[c]) = __float2bfloat16_rn(X);
-                                }
-                            }
-                        }
-                    }
+                    for (int k2 = 0; k2 < 8; ++k2)
+                        *reinterpret_cast<uint4 *>(tile + (4 * k2 + (lane >> 3)) * DT_STRIDE + 128 * hf + 16 * (lane & 7)) = make_uint4(0, 0, 0, 0);
                     __syncwarp();
                 }
+                const uint32_t e2 = *reinterpret_cast<const uint16_t *>(gb + p.o_ks + h * 128 + d0);
+                const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
+                uint32_t ms2 = 0, mc2 = 0;
+                uint2 bm2 = make_uint2(0, 0);
+                uint32_t st[2] = {0, 0};
+                if (splice) {
+                    if (p.use_map) {
+                        ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
+                        mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
+                    }
+                    bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
+                    const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
+                    const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nb;          // 2*nb bytes, 2-byte aligned
+                    if (nb == 3) {
+                        const uint32_t w0 = reinterpret_cast<const uint16_t *>(ov)[0], w1 = reinterpret_cast<const uint16_t *>(ov)[1],
+                                       w2 = reinterpret_cast<const uint16_t *>(ov)[2];
+                        st[0] = w0 | ((w1 & 0xFFu) << 16);
+                        st[1] = (w1 >> 8) | (w2 << 8);
+                    } else if (nb == 4) {
+                        const uint2 w = *reinterpret_cast<const uint2 *>(ov);
+                        st[0] = w.x; st[1] = w.y;
+                    } else if (nb == 2) {
+                        const uint32_t w = *reinterpret_cast<const uint32_t *>(ov);
+                        st[0] = w & 0xFFFFu; st[1] = w >> 16;
+                    } else {
+                        const uint32_t w = *reinterpret_cast<const uint16_t *>(ov);
+                        st[0] = w & 0xFFu; st[1] = w >> 8;
+                    }
+                }
+                OMMX_TR(trk + 3);
+                const uint32_t bmv[2] = {bm2.x, bm2.y};
+                const uint8_t *kreg = gb;                            // k_base region of the group (1 KB aligned)
+                const uint32_t kl_off = (uint32_t)(h * 32 + (d0 >> 2));   // the code byte holding this lane's channels
+                // this lane's entry in the fragment-ordered K factor row
+                const uint32_t kf_off = ROW_KF * DT_STRIDE + 64u * (2 * hf + (lane >> 4)) + 32u * ((lane >> 3) & 1) + 8u * (lane & 3) + 2u * ((lane >> 2) & 1);
+                uint32_t zph[2];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int e = max((int)(int8_t)(e2 >> (8 * c)), -126);
+                    const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
+                    const float zp = bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu));
+                    zph[c] = f16_bits_sat(zp);
+                    bool cl;
+                    const uint32_t fb = pow2_f16_bits(e, cl);
+                    clamped_any |= cl;
+                    *reinterpret_cast<uint16_t *>(tile + kf_off + 4 * c) = (uint16_t)fb;
+                    if (splice) {
+                        // delta between the outlier value and the base value it replaces, rounded once
+                        float A = sc, Bc = 0.f;                     // shared map: lvl*s + zp - (code*s + zp)
+                        if (p.use_map) {
+                            const float ms = bf16_bits_to_f32(c ? (ms2 >> 16) : (ms2 & 0xFFFFu));
+                            const float mc = bf16_bits_to_f32(c ? (mc2 >> 16) : (mc2 & 0xFFFFu));
+                            A = __fdividef(1.f, ms);
+                            Bc = mc - zp;
+                        }
+                        uint32_t bits = bmv[c];
+                        const uint32_t stream = st[c];
+                        const int fsh = 2 * ((d0 & 3) + c);          // bit position of the channel's code in its byte
+                        uint8_t *col = tile + 2 * d0 + 2 * c;
+                        if (KOUT > 0) {
+                            if (__popc(bits) == KOUT) {
+#pragma unroll
+                                for (int r = KOUT - 1; r >= 0; --r) {
+                                    const int pz = 31 - __clz(bits);
+                                    bits ^= 1u << pz;
+                                    const uint32_t nib = (stream >> (4 * r)) & 0xFu;
+                                    const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> fsh) & 3u);
+                                    const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
+                                    *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
+                                }
+                            } else {
+                                or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
+                            }
+                        } else {
+                            int r = __popc(bits) - 1;
+                            while (bits) {
+                                const int pz = 31 - __clz(bits);
+                                bits ^= 1u << pz;
+                                const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
+                                --r;
+                                const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> fsh) & 3u);
+                                const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
+                                *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
+                            }
+                        }
+                    }
+                }
+                *reinterpret_cast<uint32_t *>(tile + ROW_ZP * DT_STRIDE + 2 * d0) = zph[0] | (zph[1] << 16);
+                {   // V side: one token, two scale groups: power-of-two factor and zero-point of each
+                    const int copy = it & 1;
+                    const int tk = 16 * hf + (lane & 15), cg0 = 2 * (lane >> 4);
+                    uint32_t ve = 0x8080u;                               // exponent -128 -> factor 0
+                    uint32_t vz2 = 0u;
+                    if (32 * lg + tk < ntok) {
+                        ve = *reinterpret_cast<const uint16_t *>(gb + p.o_vs + (tk * H + h) * 4 + cg0);
+                        vz2 = *reinterpret_cast<const uint32_t *>(gb + p.o_vz + (tk * H + h) * 8 + 2 * cg0);
+                    }
+                    uint8_t *vfr = tile + (ROW_VF + copy) * DT_STRIDE + 64 * ((tk >> 1) & 3) + 8 * hf + 4 * ((tk >> 3) & 1) + 2 * (tk & 1) + 16 * cg0;
+                    uint8_t *ztr = tile + (ROW_ZT + copy) * DT_STRIDE + 2 * tk + 64 * cg0;
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        bool cl;
+                        const uint32_t fb = pow2_f16_bits((int)(int8_t)(ve >> (8 * c)), cl);
+                        clamped_any |= cl;
+                        *reinterpret_cast<uint16_t *>(vfr + 16 * c) = (uint16_t)fb;
+                        const float vz = bf16_bits_to_f32(c ? (vz2 >> 16) : (vz2 & 0xFFFFu));
+                        *reinterpret_cast<uint16_t *>(ztr + 64 * c) = (uint16_t)f16_bits_sat(vz);
+                    }
+                }
+                if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
+                __syncwarp();
                 OMMX_TR(trk + 4);
-
                 if (lane == 0) mbar_arrive(bar_tfull + 8 * unit);
             }
             __syncwarp();
@@ -551,21 +590,21 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         return;
     }
 
-    // =========================== MMA warps (phase B) ===========================
+    // =========================== MMA warps ===========================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 " OMMX_REGS_MMA ";");
     const int unit = warp;
     const int h = unit % H, gsel = unit / H;
     const uint8_t *tile = s_tiles + unit * DT_BYTES;
     const uint32_t tile_s = smem_u32(tile);
-    // ---- per-thread constants ----
-    // MMA row g carries query head (g % 4) when VFOLD (rows 4..7 repeat rows 0..3), else head g.
-    const int row_head = VFOLD ? (g & 3) : g;
-    const bool row_ok = row_head < p.gqa;
-    // q_static: bf16(q*sm_scale) * 2^-1 * 4^-pc for this lane's head row and 32 channel slots
-    uint32_t QS[16];
+    // Column n = g of every MMA is query head g of this kv head.
+    const bool head_ok = g < p.gqa;
+    // B fragments of q, fp16.  QS: bf16(q*sm_scale) * 4^-slot for the code MMAs, register r = 8*wi + i holds
+    // channels (32j + 16wi + i, + 8), the pair a code word yields in one AND.  QD: plain bf16(q*sm_scale) for
+    // the delta / zero-point MMAs, whose tile columns are channels in natural order.
+    uint32_t QS[16], QD[16];
     {
-        const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (row_ok ? row_head : 0)) * p.q_sh;
-        // this lane's 32 channels are contiguous: four 16-byte loads when the row allows it
+        const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (head_ok ? g : 0)) * p.q_sh;
+        // this lane's 32 channels for QS are contiguous: four 16-byte loads when the row allows it
         uint32_t qw[16];
         if ((reinterpret_cast<uintptr_t>(qrow) & 15u) == 0) {
 #pragma unroll
@@ -584,36 +623,51 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         for (int r = 0; r < 16; ++r) {
             const int wi = r >> 3, i = r & 7;
             const int e0 = 16 * wi + i, e1 = e0 + 8;                  // channel 32j + e0 / + e1
-            const float f = 0.5f / (float)(1 << (2 * pos_class(i)));
+            const float f = 1.f / (float)(1 << (2 * code_slot(i)));
             float lo = 0.f, hi = 0.f;
-            if (row_ok) {
+            if (head_ok) {
                 lo = bf16_round_f32(bf16_bits_to_f32((qw[e0 >> 1] >> (16 * (e0 & 1))) & 0xFFFFu) * p.sm_scale) * f;
                 hi = bf16_round_f32(bf16_bits_to_f32((qw[e1 >> 1] >> (16 * (e1 & 1))) & 0xFFFFu) * p.sm_scale) * f;
             }
-            QS[r] = pack_bf16x2(lo, hi);
+            QS[r] = pack_f16x2(lo, hi);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qrow + 16 * q + 8 * half + 2 * j);
+                float lo = 0.f, hi = 0.f;
+                if (head_ok) {
+                    lo = bf16_round_f32(bf16_bits_to_f32(q16[0]) * p.sm_scale);
+                    hi = bf16_round_f32(bf16_bits_to_f32(q16[1]) * p.sm_scale);
+                }
+                QD[2 * q + half] = pack_f16x2(lo, hi);
+            }
         }
     }
-    // V-fold constants: byte selectors of this row pair's two V scale groups
-    const int cgA = g >> 2, cgB = 2 + (g >> 2);
-    const uint32_t selA = (uint32_t)(cgA | (cgA << 4) | ((4 + cgA) << 8) | ((4 + cgA) << 12));
-    const uint32_t selB = (uint32_t)(cgB | (cgB << 4) | ((4 + cgB) << 8) | ((4 + cgB) << 12));
-    // ---- online softmax state (row g of the MMA tile) ----
-    float m_run = -INFINITY, l_run = 0.f;
-    float acc[16][4];
+    // per-lane fragment addresses inside the sidecar tile
+    const uint32_t a_delta = tile_s + ((lane & 7) + 8 * ((lane >> 3) & 1)) * DT_STRIDE + 16 * (lane >> 4);
+    const uint32_t a_zp = tile_s + ROW_ZP * DT_STRIDE + 16 * ((lane >> 3) & 1);
+    const uint8_t *p_kf = tile + ROW_KF * DT_STRIDE + 64 * j;
+    // ---- online softmax state of heads 2j and 2j+1 (the two columns this lane holds) ----
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // acc[2*cg + u]: rows = channels 32cg + 4g + u (regs 0,1) and 32cg + 4g + 2 + u (regs 2,3), columns = heads
+    float acc[8][4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-    float acc_rs[4] = {0.f, 0.f, 0.f, 0.f};      // VFOLD: sum_t P'[row][t]        (x128 offset)
-    float acc_vz[4] = {0.f, 0.f, 0.f, 0.f};      // VFOLD: sum_t P[row][t] * vz[t][cg = column]
+    for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    float accz[4] = {0.f, 0.f, 0.f, 0.f};        // rows = V scale groups: sum_t vz[t][cg] * P[t][head]
     uint32_t consumed = 0;
+    const bool do_k = !(p.abl & ABL_NO_K), do_v = !(p.abl & ABL_NO_V);
+    const bool has_delta = !(k_out == 0 || no_outlier);
 
     OMMX_TR(252);
     for (int it = 0; it < n_iters; ++it) {
-        const int s = it % NSTAGES;
-        const uint32_t ph = (it / NSTAGES) & 1;
+        const int s = it % NS;
+        const uint32_t ph = (it / NS) & 1;
         OMMX_TR(8 * it);
         if (!mbar_wait(bar_full + 8 * s, ph)) {
             if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
-            m_run = -INFINITY; l_run = 0.f;
+            m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
             break;
         }
         OMMX_TR(8 * it + 1);
@@ -621,202 +675,150 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
             uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
             const uint8_t *vreg = gb + p.o_vm;                      // v_main region of the group (1 KB aligned)
-            const uint8_t *vsc = gb + p.o_vs + h * 4;                // + token*H*4
-            const uint8_t *vzp = gb + p.o_vz + h * 8;                // + token*H*8
-            const uint8_t *ksc = gb + p.o_ks + h * 128;
 
-            // ======================= phase B: QK^T =======================
-            uint32_t QQ[16];
-            {
-                const uint4 ea = *reinterpret_cast<const uint4 *>(ksc + 32 * j);
-                const uint4 eb = *reinterpret_cast<const uint4 *>(ksc + 32 * j + 16);
-                const uint32_t E[8] = {ea.x, ea.y, ea.z, ea.w, eb.x, eb.y, eb.z, eb.w};
+            // ======================= logits =======================
+            // code words of this lane's four token rows (tokens 8*nt + g), channels 32j..32j+31
+            uint2 kw[4];
 #pragma unroll
-                for (int r = 0; r < 16; ++r) {
-                    const int wi = r >> 3, i = r & 7, bsel = i & 3;
-                    const uint32_t sel = (uint32_t)(bsel | (bsel << 4) | ((4 + bsel) << 8) | ((4 + bsel) << 12));
-                    const uint32_t t = __byte_perm(E[4 * wi + (i >> 2)], E[4 * wi + 2 + (i >> 2)], sel);
-                    const uint32_t f = lop3_and_xor(t, 0x00FF00FFu, 0x00800080u) << 7;   // 2^(e+1) pair
-                    QQ[r] = hmul2_bf16(QS[r], f);
-                }
-            }
-            float C[5][4];
-#pragma unroll
-            for (int nt = 0; nt < 5; ++nt) { C[nt][0] = C[nt][1] = C[nt][2] = C[nt][3] = 0.f; }
-            if (!(p.abl & ABL_NO_K)) {
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    const uint2 kw = *reinterpret_cast<const uint2 *>(gb + swz128((uint32_t)((8 * nt + g) * TS + h * 32 + 8 * j), p.swz));
-                    uint32_t R[8];
-                    codes_to_bf16x2(kw.x, R);
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) mma_bf16(C[nt], QQ[2 * kk], 0u, QQ[2 * kk + 1], 0u, R[2 * kk], R[2 * kk + 1]);
-                    codes_to_bf16x2(kw.y, R);
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) mma_bf16(C[nt], QQ[8 + 2 * kk], 0u, QQ[8 + 2 * kk + 1], 0u, R[2 * kk], R[2 * kk + 1]);
-                }
+            for (int nt = 0; nt < 4; ++nt) {
+                kw[nt] = make_uint2(0u, 0u);
+                if (do_k) kw[nt] = *reinterpret_cast<const uint2 *>(gb + swz128((uint32_t)((8 * nt + g) * TS + h * 32 + 8 * j), p.swz));
             }
             OMMX_TR(8 * it + 2);
-            // outlier tile (+ zp / -128 rows as n-tile 4), built by the decode warp of this unit
             if (!mbar_wait(bar_tfull + 8 * unit, consumed & 1u)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
-                m_run = -INFINITY; l_run = 0.f;
+                m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
                 break;
             }
             OMMX_TR(8 * it + 3);
-            {
-                const int mi = lane >> 3, rr = lane & 7;
+            uint32_t F[16];
 #pragma unroll
-                for (int nt = 0; nt < 5; ++nt) {
-                    if (nt < 4 && (k_out == 0 || no_outlier)) continue;
-                    int row = 8 * nt + rr;
-                    if (row >= DT_ROWS) row -= DT_ROWS;              // rows 34..39 alias rows 0..5 (columns unused)
-                    const uint32_t base = tile_s + row * DT_STRIDE + 2 * (16 * (mi >> 1) + 8 * (mi & 1));
+            for (int v = 0; v < 4; ++v) {
+                const uint4 t = reinterpret_cast<const uint4 *>(p_kf)[v];
+                F[4 * v] = t.x; F[4 * v + 1] = t.y; F[4 * v + 2] = t.z; F[4 * v + 3] = t.w;
+            }
+            float Sc[2][4], Sd[2][4], Sz[4];
 #pragma unroll
-                    for (int kp = 0; kp < 4; ++kp) {
+            for (int mt = 0; mt < 2; ++mt) { Sc[mt][0] = Sc[mt][1] = Sc[mt][2] = Sc[mt][3] = 0.f; Sd[mt][0] = Sd[mt][1] = Sd[mt][2] = Sd[mt][3] = 0.f; }
+            Sz[0] = Sz[1] = Sz[2] = Sz[3] = 0.f;
+            // Five accumulators take turns, so that neighbours in the instruction stream never wait on each other.
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int wi = q >> 2, i0 = 2 * (q & 3);
+                const uint32_t b0 = hmul2_f16(QS[2 * q], F[2 * q]), b1 = hmul2_f16(QS[2 * q + 1], F[2 * q + 1]);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    const uint32_t wlo = wi ? kw[2 * mt].y : kw[2 * mt].x, whi = wi ? kw[2 * mt + 1].y : kw[2 * mt + 1].x;
+                    mma_f16(Sc[mt], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
+                }
+                if (has_delta) {
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
                         uint32_t d0, d1, d2, d3;
-                        ldsm_x4(base + 64 * kp, d0, d1, d2, d3);
-                        mma_bf16(C[nt], QQ[4 * kp], 0u, QQ[4 * kp + 1], 0u, d0, d1);
-                        mma_bf16(C[nt], QQ[4 * kp + 2], 0u, QQ[4 * kp + 3], 0u, d2, d3);
+                        ldsm_x4(a_delta + 16 * mt * DT_STRIDE + 32 * q, d0, d1, d2, d3);
+                        mma_f16(Sd[mt], d0, d1, d2, d3, QD[2 * q], QD[2 * q + 1]);
                     }
                 }
+                uint32_t z0, z1;
+                ldsm_x2(a_zp + 32 * q, z0, z1);
+                mma_f16(Sz, z0, 0u, z1, 0u, QD[2 * q], QD[2 * q + 1]);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * (NSTAGES * unit + (consumed % NSTAGES)));   // the next tile may be built
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * (MAX_STAGES * unit + (consumed % NS)));   // the next tile may be built
             ++consumed;
             OMMX_TR(8 * it + 4);
-            // q.zp - 128*sum(q'') sits in columns 0 and 1 of n-tile 4 (lanes with j == 0)
-            float qzo = C[4][0] + C[4][1];
-            qzo = __shfl_sync(0xFFFFFFFFu, qzo, lane & ~3);
 
             // ======================= online softmax =======================
-            float x[8];
+            // x[mt][r]: token 16mt + g + 8(r>>1), head 2j + (r&1)
+            float x[2][4];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) { x[2 * nt] = C[nt][0] + qzo; x[2 * nt + 1] = C[nt][1] + qzo; }
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) x[mt][r] = fmaf(Sc[mt][r], 1048576.f, Sd[mt][r] + Sz[r & 1]);
             if (p.logit_cap > 0.f) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) x[i] = p.logit_cap * tanhf(x[i] / p.logit_cap);
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) x[mt][r] = p.logit_cap * tanhf(x[mt][r] / p.logit_cap);
             }
             const int tok_base = 32 * lg;
             if (tok_base + 32 > ntok) {
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    if (tok_base + 8 * nt + 2 * j >= ntok) x[2 * nt] = -INFINITY;
-                    if (tok_base + 8 * nt + 2 * j + 1 >= ntok) x[2 * nt + 1] = -INFINITY;
-                }
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (tok_base + 16 * mt + g + 8 * (r >> 1) >= ntok) x[mt][r] = -INFINITY;
             }
-            float mloc = x[0];
+            float corr[2], mneg[2];
 #pragma unroll
-            for (int i = 1; i < 8; ++i) mloc = fmaxf(mloc, x[i]);
-            mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 1));
-            mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 2));
-            const float m_new = fmaxf(m_run, mloc);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = fast_exp2((m_run - m_use) * LOG2E);   // m_run = -inf -> 0
-            const float mneg = -m_use * LOG2E;
-            float psum = 0.f;
-            uint32_t P[4];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const float p0 = fast_exp2(fmaf(x[2 * nt], LOG2E, mneg));
-                const float p1 = fast_exp2(fmaf(x[2 * nt + 1], LOG2E, mneg));
-                psum += p0 + p1;
-                P[nt] = pack_bf16x2(p0, p1);
+            for (int hh = 0; hh < 2; ++hh) {
+                float mloc = fmaxf(fmaxf(x[0][hh], x[0][2 + hh]), fmaxf(x[1][hh], x[1][2 + hh]));
+                mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 4));
+                mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 8));
+                mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, 16));
+                const float m_new = fmaxf(m_run[hh], mloc);
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                corr[hh] = fast_exp2((m_run[hh] - m_use) * LOG2E);   // m_run = -inf -> 0
+                mneg[hh] = -m_use * LOG2E;
+                m_run[hh] = m_new;
             }
-            l_run = l_run * corr + psum;
-            m_run = m_new;
-            if (__any_sync(0xFFFFFFFFu, corr != 1.0f)) {
+            float pr[2][4];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    acc[i][0] *= corr; acc[i][1] *= corr;
-                    if (VFOLD) { acc[i][2] *= corr; acc[i][3] *= corr; }
-                }
-                if (VFOLD) {
+            for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) { acc_rs[i] *= corr; acc_vz[i] *= corr; }
-                }
+                for (int r = 0; r < 4; ++r) pr[mt][r] = fast_exp2(fmaf(x[mt][r], LOG2E, mneg[r & 1]));
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+                l_run[hh] = l_run[hh] * corr[hh] + ((pr[0][hh] + pr[0][2 + hh]) + (pr[1][hh] + pr[1][2 + hh]));   // this lane's tokens only
+            if (__any_sync(0xFFFFFFFFu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { acc[i][0] *= corr[0]; acc[i][1] *= corr[1]; acc[i][2] *= corr[0]; acc[i][3] *= corr[1]; }
+                accz[0] *= corr[0]; accz[1] *= corr[1];
             }
-
+            // P^T as B fragments: transpose each 8x8 (token, head) block; T[ks][b] = tokens 16ks + 8b + 2j, +1 of head g
+            uint32_t T[2][2];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                T[mt][0] = movmatrix_trans(pack_f16x2(pr[mt][0], pr[mt][1]));
+                T[mt][1] = movmatrix_trans(pack_f16x2(pr[mt][2], pr[mt][3]));
+            }
             OMMX_TR(8 * it + 5);
+
             // ======================= P.V =======================
-            // lane (g, j) supplies channel column g of every n-tile: channels 16*g + i, scale group g/2
-            if (!(p.abl & ABL_NO_V)) {
-                if (VFOLD) {
-                    // P'[row][t] = P[head][t] * 2^(e_v[t][cg(row)] + 1)   (exact)
-                    uint32_t PA[4], PB[4];
+            if (do_v) {
+                const int copy = it & 1;
+                uint32_t VF[16];                                     // factor pairs, index 4cg + 2ks + b
+                {
+                    const uint8_t *p_vf = tile + (ROW_VF + copy) * DT_STRIDE + 64 * j;
 #pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) {
-                        const int ta = 8 * nt + 2 * j;
-                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vsc + ta * H * 4);
-                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vsc + (ta + 1) * H * 4);
-                        const uint32_t fa = lop3_and_xor(__byte_perm(wa, wb, selA), 0x00FF00FFu, 0x00800080u) << 7;
-                        const uint32_t fb = lop3_and_xor(__byte_perm(wa, wb, selB), 0x00FF00FFu, 0x00800080u) << 7;
-                        PA[nt] = hmul2_bf16(P[nt], fa);
-                        PB[nt] = hmul2_bf16(P[nt], fb);
+                    for (int v = 0; v < 4; ++v) {
+                        const uint4 t = reinterpret_cast<const uint4 *>(p_vf)[v];
+                        VF[4 * v] = t.x; VF[4 * v + 1] = t.y; VF[4 * v + 2] = t.z; VF[4 * v + 3] = t.w;
                     }
+                }
+                const uint8_t *p_zt = tile + (ROW_ZT + copy) * DT_STRIDE + 64 * (g & 3) + 4 * j;
 #pragma unroll
-                    for (int kt = 0; kt < 2; ++kt) {
-                        const int ta = 16 * kt + 2 * j;
-                        const uint32_t wa = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)(ta * TS + h * 32 + 4 * g), p.swz));
-                        const uint32_t wb = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)((ta + 1) * TS + h * 32 + 4 * g), p.swz));
-                        const uint32_t wc = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)((ta + 8) * TS + h * 32 + 4 * g), p.swz));
-                        const uint32_t wd = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)((ta + 9) * TS + h * 32 + 4 * g), p.swz));
-                        uint32_t R0[8], R1[8];
-                        codes_to_bf16x2(__byte_perm(wa, wb, 0x5410), R0);       // channels 0..7 of (ta, tb)
-                        codes_to_bf16x2(__byte_perm(wc, wd, 0x5410), R1);
+                for (int ks = 0; ks < 2; ++ks) {
+                    const int tA = 16 * ks + 2 * j;
+                    const uint32_t o0 = (uint32_t)(tA * TS + h * 32 + g), o1 = o0 + TS, o8 = o0 + 8 * TS, o9 = o8 + TS;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) mma_bf16(acc[i], PA[2 * kt], PB[2 * kt], PA[2 * kt + 1], PB[2 * kt + 1], R0[i], R1[i]);
-                        codes_to_bf16x2(__byte_perm(wa, wb, 0x7632), R0);       // channels 8..15
-                        codes_to_bf16x2(__byte_perm(wc, wd, 0x7632), R1);
+                    for (int cg = 0; cg < 4; ++cg) {
+                        // channels 32cg + 4g .. + 3 of four tokens: one byte each
+                        const uint32_t bA = vreg[swz128(o0 + 8 * cg, p.swz)], bA1 = vreg[swz128(o1 + 8 * cg, p.swz)];
+                        const uint32_t bB = vreg[swz128(o8 + 8 * cg, p.swz)], bB1 = vreg[swz128(o9 + 8 * cg, p.swz)];
+                        const uint32_t w01 = bA | (bA1 << 16), w89 = bB | (bB1 << 16);
+                        const uint32_t pb0 = hmul2_f16(T[ks][0], VF[4 * cg + 2 * ks]), pb1 = hmul2_f16(T[ks][1], VF[4 * cg + 2 * ks + 1]);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) mma_bf16(acc[8 + i], PA[2 * kt], PB[2 * kt], PA[2 * kt + 1], PB[2 * kt + 1], R0[i], R1[i]);
-                        // row sums of P' (the magic +128 of every raw V value comes back out through them)
-                        mma_bf16(acc_rs, PA[2 * kt], PB[2 * kt], PA[2 * kt + 1], PB[2 * kt + 1], 0x3F803F80u, 0x3F803F80u);
-                        // zero-point bias: column n = scale group n (n < 4), B[k = token][n] = vz[token][n]
-                        uint32_t z0 = 0u, z1 = 0u;
-                        if (g < 4) {
-                            z0 = (uint32_t)*reinterpret_cast<const uint16_t *>(vzp + ta * H * 8 + 2 * g)
-                               | ((uint32_t)*reinterpret_cast<const uint16_t *>(vzp + (ta + 1) * H * 8 + 2 * g) << 16);
-                            z1 = (uint32_t)*reinterpret_cast<const uint16_t *>(vzp + (ta + 8) * H * 8 + 2 * g)
-                               | ((uint32_t)*reinterpret_cast<const uint16_t *>(vzp + (ta + 9) * H * 8 + 2 * g) << 16);
-                        }
-                        mma_bf16(acc_vz, P[2 * kt], P[2 * kt], P[2 * kt + 1], P[2 * kt + 1], z0, z1);
+                        for (int u = 0; u < 2; ++u)
+                            mma_f16(acc[2 * cg + u], w01 & (0x00030003u << (2 * u)), w01 & (0x00030003u << (2 * u + 4)),
+                                    w89 & (0x00030003u << (2 * u)), w89 & (0x00030003u << (2 * u + 4)), pb0, pb1);
                     }
-                } else {
-#pragma unroll
-                    for (int kt = 0; kt < 2; ++kt) {
-                        uint32_t Vr[2][16];
-#pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            const int ta = 16 * kt + 8 * half + 2 * j, tb = ta + 1;
-                            const uint32_t wa = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)(ta * TS + h * 32 + 4 * g), p.swz));
-                            const uint32_t wb = *reinterpret_cast<const uint32_t *>(vreg + swz128((uint32_t)(tb * TS + h * 32 + 4 * g), p.swz));
-                            const uint32_t ea = vsc[ta * H * 4 + (g >> 1)], eb2 = vsc[tb * H * 4 + (g >> 1)];
-                            const uint32_t za = *reinterpret_cast<const uint16_t *>(vzp + ta * H * 8 + 2 * (g >> 1));
-                            const uint32_t zb = *reinterpret_cast<const uint16_t *>(vzp + tb * H * 8 + 2 * (g >> 1));
-                            const uint32_t vs2 = (((ea | (eb2 << 16)) ^ 0x00800080u) & 0x00FF00FFu) << 7;   // 2^(e+1) pair
-                            const uint32_t vz2 = za | (zb << 16);
-                            const uint32_t vs_p0 = hmul2_bf16(vs2, 0x3F003F00u);    // * 2^-1
-                            const uint32_t vs_p1 = hmul2_bf16(vs2, 0x3E003E00u);    // * 2^-3
-                            const uint32_t vs_p2 = hmul2_bf16(vs2, 0x3D003D00u);    // * 2^-5
-                            uint32_t R[8];
-                            const uint32_t K128 = 0x43004300u;
-                            codes_to_bf16x2(__byte_perm(wa, wb, 0x5410), R);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int pc = pos_class(i);
-                                Vr[half][i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
-                            }
-                            codes_to_bf16x2(__byte_perm(wa, wb, 0x7632), R);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int pc = pos_class(i);
-                                Vr[half][8 + i] = hfma2_bf16(hsub2_bf16(R[i], K128), pc == 0 ? vs_p0 : (pc == 1 ? vs_p1 : vs_p2), vz2);
-                            }
-                        }
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) mma_bf16(acc[i], P[2 * kt], 0u, P[2 * kt + 1], 0u, Vr[0][i], Vr[1][i]);
+                    uint32_t za0 = 0u, za2 = 0u;
+                    if (g < 4) {
+                        za0 = *reinterpret_cast<const uint32_t *>(p_zt + 32 * ks);
+                        za2 = *reinterpret_cast<const uint32_t *>(p_zt + 32 * ks + 16);
                     }
+                    mma_f16(accz, za0, 0u, za2, 0u, T[ks][0], T[ks][1]);
                 }
             }
         }
@@ -827,69 +829,68 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     }
     OMMX_TR(253);
 
-    // ---- epilogue: finalize this lane's 32 output channels, merge warps that share a head ----
-    // Every lane ends up with outv[0..15] = channels 32j + i and outv[16..31] = channels 32j + 16 + i of
-    // one (head, split) row, un-normalised; `useful` marks the lanes whose row is real.
-    float l_tot = l_run;
-    l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 1);
-    l_tot += __shfl_xor_sync(0xFFFFFFFFu, l_tot, 2);
-    float outv[32];
-    bool useful;
-    if (VFOLD) {
-        // lane (g, j): columns 2j, 2j+1 are channels of scale group j; row g has group g/4, row g+8 group 2+g/4
-        const bool lo_row = (g >> 2) == j, hi_row = (2 + (g >> 2)) == j;
-        useful = row_ok && (lo_row || hi_row);
-        const float rs = hi_row ? acc_rs[2] : acc_rs[0];
-        // bias of (head, group j) sits in lane (g, j/2), register j&1
-        const float b0 = __shfl_sync(0xFFFFFFFFu, acc_vz[0], (lane & ~3) | (j >> 1));
-        const float b1 = __shfl_sync(0xFFFFFFFFu, acc_vz[1], (lane & ~3) | (j >> 1));
-        const float bias = (j & 1) ? b1 : b0;
+    // ---- epilogue: this lane holds 16 channels of heads 2j and 2j+1; merge warps that share a head ----
+    float l_tot[2];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float f = 0.5f / (float)(1 << (2 * pos_class(i & 7)));
-            const float a0 = hi_row ? acc[i][2] : acc[i][0], a1 = hi_row ? acc[i][3] : acc[i][1];
-            outv[i] = fmaf(a0 - 128.f * rs, f, bias);
-            outv[16 + i] = fmaf(a1 - 128.f * rs, f, bias);
-        }
-    } else {
-        useful = row_ok;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) { outv[i] = acc[i][0]; outv[16 + i] = acc[i][1]; }
+    for (int hh = 0; hh < 2; ++hh) {
+        float l = l_run[hh];
+        l += __shfl_xor_sync(0xFFFFFFFFu, l, 4);
+        l += __shfl_xor_sync(0xFFFFFFFFu, l, 8);
+        l += __shfl_xor_sync(0xFFFFFFFFu, l, 16);
+        l_tot[hh] = l;
     }
-    const int out_head = h * p.gqa + row_head;
+    // outv[hh][4cg + c]: channel 32cg + 4g + c of head 2j + hh, un-normalised
+    float outv[2][16];
+#pragma unroll
+    for (int cg = 0; cg < 4; ++cg) {
+        const float bz0 = __shfl_sync(0xFFFFFFFFu, accz[0], 4 * cg + j);
+        const float bz1 = __shfl_sync(0xFFFFFFFFu, accz[1], 4 * cg + j);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int u = c & 1, v = c >> 1;
+            const float f = 1048576.f / (float)(1 << (2 * c));       // 2^(24 - FBIAS) * 4^-slot
+            outv[0][4 * cg + c] = fmaf(acc[2 * cg + u][2 * v], f, bz0);
+            outv[1][4 * cg + c] = fmaf(acc[2 * cg + u][2 * v + 1], f, bz1);
+        }
+    }
 
     // Wait for every warp (and the producer) before the ring memory is reused as scratch.
     __syncthreads();
-    float *scratch = reinterpret_cast<float *>(s_stage);             // [NCW][32 lanes][34]
+    float *scratch = reinterpret_cast<float *>(s_stage);             // [NCW][32 lanes][36]
     if (GS > 1 && gsel > 0) {
-        float *my = scratch + ((size_t)unit * 32 + lane) * 34;
-        my[0] = m_run; my[1] = l_tot;
+        float *my = scratch + ((size_t)unit * 32 + lane) * 36;
+        my[0] = m_run[0]; my[1] = m_run[1]; my[2] = l_tot[0]; my[3] = l_tot[1];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) my[2 + i] = outv[i];
+        for (int i = 0; i < 16; ++i) { my[4 + i] = outv[0][i]; my[20 + i] = outv[1][i]; }
     }
     __syncthreads();
     if (gsel == 0) {
         for (int o = 1; o < GS; ++o) {
-            const float *ot = scratch + ((size_t)(o * H + h) * 32 + lane) * 34;
-            const float m2 = ot[0], l2 = ot[1];
-            const float mn = fmaxf(m_run, m2);
-            const float mu = (mn == -INFINITY) ? 0.f : mn;
-            const float c1 = fast_exp2((m_run - mu) * LOG2E), c2 = fast_exp2((m2 - mu) * LOG2E);
-            l_tot = l_tot * c1 + l2 * c2;
+            const float *ot = scratch + ((size_t)(o * H + h) * 32 + lane) * 36;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) outv[i] = outv[i] * c1 + ot[2 + i] * c2;
-            m_run = mn;
-        }
-        if (useful) {
-            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-            float *dst = p.al + (int64_t)b * p.al_sb + (int64_t)out_head * p.al_sh + (int64_t)split * p.al_ss;
+            for (int hh = 0; hh < 2; ++hh) {
+                const float m2 = ot[hh], l2 = ot[2 + hh];
+                const float mn = fmaxf(m_run[hh], m2);
+                const float mu = (mn == -INFINITY) ? 0.f : mn;
+                const float c1 = fast_exp2((m_run[hh] - mu) * LOG2E), c2 = fast_exp2((m2 - mu) * LOG2E);
+                l_tot[hh] = l_tot[hh] * c1 + l2 * c2;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                dst[32 * j + i] = outv[i] * inv;
-                dst[32 * j + 16 + i] = outv[16 + i] * inv;
+                for (int i = 0; i < 16; ++i) outv[hh][i] = outv[hh][i] * c1 + ot[4 + 16 * hh + i] * c2;
+                m_run[hh] = mn;
             }
-            const bool lse_writer = VFOLD ? (g < 4 && j == 0) : (j == 0);
-            if (lse_writer) dst[HD] = l_tot > 0.f ? m_run + logf(l_tot) : -INFINITY;
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int head = 2 * j + hh;
+            if (head < p.gqa) {
+                const float inv = l_tot[hh] > 0.f ? 1.f / l_tot[hh] : 0.f;
+                float *dst = p.al + (int64_t)b * p.al_sb + (int64_t)(h * p.gqa + head) * p.al_sh + (int64_t)split * p.al_ss;
+#pragma unroll
+                for (int cg = 0; cg < 4; ++cg)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) dst[32 * cg + 4 * g + c] = outv[hh][4 * cg + c] * inv;
+                if (g == 0) dst[HD] = l_tot[hh] > 0.f ? m_run[hh] + logf(l_tot[hh]) : -INFINITY;
+            }
         }
     }
     OMMX_TR(254);
@@ -1151,19 +1152,26 @@ static bool make_code_map(CUtensorMap *m, const void *base, int64_t total_bytes,
 }
 
 static size_t stage1_smem(const S1Params &p) {
-    return 1024 + (size_t)NSTAGES * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
-           + (2 * NSTAGES + (1 + NSTAGES) * NCW) * 8 + 16 + MAX_STAGE_COPIES * sizeof(CopyDesc);
+    return 1024 + (size_t)p.nstages * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
+           + (2 * MAX_STAGES + (1 + MAX_STAGES) * NCW) * 8 + 16 + MAX_STAGE_COPIES * sizeof(CopyDesc);
 }
 
-template <int KOUT, bool VFOLD>
+template <int KOUT>
 static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st) {
     static size_t attr_smem = 0;                       // one per instantiation
+    static int regs_ok = -1;
+    if (regs_ok < 0) {
+        cudaFuncAttributes fa;
+        OMMX_CUDA_TRY(cudaFuncGetAttributes(&fa, decode_stage1_kernel<KOUT>));
+        regs_ok = fa.numRegs * S1_THREADS >= NCW * 32 * REGS_MMA + (S1_THREADS - NCW * 32) * REGS_DECODE ? 1 : 0;
+    }
+    if (!regs_ok) return fail(OMMX_E_CUDA, "stage 1 was compiled with fewer registers than its warp roles need");
     if (smem > attr_smem) {
-        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel<KOUT, VFOLD>,
+        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel<KOUT>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_smem = smem;
     }
-    decode_stage1_kernel<KOUT, VFOLD><<<grid, S1_THREADS, smem, st>>>(p);
+    decode_stage1_kernel<KOUT><<<grid, S1_THREADS, smem, st>>>(p);
     OMMX_CUDA_TRY(cudaGetLastError());
     count_launch();
     return 0;
@@ -1209,12 +1217,15 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.gb_bytes = (p.gb_bytes + round_to - 1) / round_to * round_to;
     p.stage_bytes = p.GS * p.gb_bytes;
     p.abl = a->abl_flags;
+    // deepest ring that fits the 227 KB a CTA may use
+    p.nstages = MAX_STAGES;
+    while (p.nstages > 2 && stage1_smem(p) > 232448) --p.nstages;
     const size_t smem = stage1_smem(p);
+    if (smem > 232448) return fail(OMMX_E_UNSUPPORTED, "stage 1 planes of one group do not fit shared memory");
     dim3 grid(a->num_kv_splits, a->batch);
-    const bool vfold = p.gqa <= 4;
-    if (p.k_out == 6) return vfold ? launch_s1<6, true>(p, grid, smem, st) : launch_s1<6, false>(p, grid, smem, st);
-    if (p.k_out == 0) return vfold ? launch_s1<0, true>(p, grid, smem, st) : launch_s1<0, false>(p, grid, smem, st);
-    return vfold ? launch_s1<-1, true>(p, grid, smem, st) : launch_s1<-1, false>(p, grid, smem, st);
+    if (p.k_out == 6) return launch_s1<6>(p, grid, smem, st);
+    if (p.k_out == 0) return launch_s1<0>(p, grid, smem, st);
+    return launch_s1<-1>(p, grid, smem, st);
 }
 
 // `after_stage1`: the previous kernel in the stream is this call's own stage 1, so stage 2 may be
