@@ -72,7 +72,7 @@ struct S1Params {
     int32_t *status;
     int32_t abl;
     // shared-memory layout of one group block (bytes)
-    int32_t GS, gb_bytes, stage_bytes, nstages;
+    int32_t GS, gb_bytes, stage_bytes, nstages, hshift;
     int32_t o_vm, o_vs, o_vz, o_ks, o_kz, o_ms, o_mc, o_bm, o_ov;
     // tensor maps of the two code planes as [bytes/128][128] uint8 with 128-byte swizzle
     uint32_t swz;                        // 0x70 when the maps are in use, else 0
@@ -233,6 +233,10 @@ __device__ __forceinline__ uint32_t code_pair(uint32_t w, int i) {
 }
 __device__ __forceinline__ int code_slot(int i) { return i < 5 ? i : i - 5; }
 
+// stage index and phase parity of ring use number `it` (ring depth ns: 4 unless the planes are large)
+__device__ __forceinline__ int ring_slot(int it, int ns) { return ns == 4 ? (it & 3) : it % ns; }
+__device__ __forceinline__ uint32_t ring_phase(int it, int ns) { return (uint32_t)(ns == 4 ? (it >> 2) : it / ns) & 1u; }
+
 // KOUT: outliers per K vector known at compile time (static, unrolled splice) or -1 (runtime).
 //
 // Every MMA is m16n8k16 fp16 with the 2-bit codes as the A operand: a code field masked in place is an
@@ -370,8 +374,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
         const int whole_groups = ntok / 32;
         for (int it = 0; it < n_iters; ++it) {
-            const int s = it % NS;
-            const uint32_t ph = (it / NS) & 1;
+            const int s = ring_slot(it, NS);
+            const uint32_t ph = ring_phase(it, NS);
             OMMX_TR(4 * it);
             if (!mbar_wait(bar_empty + 8 * s, ph ^ 1)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
@@ -435,10 +439,10 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             const int it = n / (2 * NCW), unit = (n >> 1) % NCW, hf = n & 1;
             const int trk = 8 * ((n - dw) / NDW);
             OMMX_TR(trk);
-            const int h = unit % H, gsel = unit / H;
+            const int h = unit & (H - 1), gsel = unit >> p.hshift;       // H is a power of two
             uint8_t *tile = s_tiles + unit * DT_BYTES;
-            const int s = it % NS;
-            const uint32_t ph = (it / NS) & 1;
+            const int s = ring_slot(it, NS);
+            const uint32_t ph = ring_phase(it, NS);
             if (!mbar_wait(bar_full + 8 * s, ph)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
@@ -453,8 +457,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 // for, never an older phase of the same parity.
                 uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
                 const int d0 = 64 * hf + 2 * lane;                   // first of this lane's two channels
-                if (it > 0 && !mbar_wait(bar_tempty + 8 * (MAX_STAGES * unit + ((it - 1) % NS)),
-                                         (uint32_t)((it - 1) / NS) & 1u)) {
+                if (it > 0 && !mbar_wait(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot(it - 1, NS)), ring_phase(it - 1, NS))) {
                     if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                     break;
                 }
@@ -593,7 +596,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     // =========================== MMA warps ===========================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 " OMMX_REGS_MMA ";");
     const int unit = warp;
-    const int h = unit % H, gsel = unit / H;
+    const int h = unit & (H - 1), gsel = unit >> p.hshift;
     const uint8_t *tile = s_tiles + unit * DT_BYTES;
     const uint32_t tile_s = smem_u32(tile);
     // Column n = g of every MMA is query head g of this kv head.
@@ -662,8 +665,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
 
     OMMX_TR(252);
     for (int it = 0; it < n_iters; ++it) {
-        const int s = it % NS;
-        const uint32_t ph = (it / NS) & 1;
+        const int s = ring_slot(it, NS);
+        const uint32_t ph = ring_phase(it, NS);
         OMMX_TR(8 * it);
         if (!mbar_wait(bar_full + 8 * s, ph)) {
             if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
@@ -701,9 +704,27 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) { Sc[mt][0] = Sc[mt][1] = Sc[mt][2] = Sc[mt][3] = 0.f; Sd[mt][0] = Sd[mt][1] = Sd[mt][2] = Sd[mt][3] = 0.f; }
             Sz[0] = Sz[1] = Sz[2] = Sz[3] = 0.f;
-            // Five accumulators take turns, so that neighbours in the instruction stream never wait on each other.
+            // Five accumulators take turns, so that neighbours in the instruction stream never wait on each
+            // other, and the tile fragments of k-step q+1 are fetched before the MMAs of step q are issued
+            // (the asm statements keep their order, so the order written here is the order issued).
+            uint32_t dfr[2][2][4], zfr[2][2];                    // [parity of q][m-tile][regs]
+            if (has_delta) {
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+                    ldsm_x4(a_delta + 16 * mt * DT_STRIDE, dfr[0][mt][0], dfr[0][mt][1], dfr[0][mt][2], dfr[0][mt][3]);
+            }
+            ldsm_x2(a_zp, zfr[0][0], zfr[0][1]);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
+                const int cur = q & 1, nxt = cur ^ 1;
+                if (q < 7) {
+                    if (has_delta) {
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt)
+                            ldsm_x4(a_delta + 16 * mt * DT_STRIDE + 32 * (q + 1), dfr[nxt][mt][0], dfr[nxt][mt][1], dfr[nxt][mt][2], dfr[nxt][mt][3]);
+                    }
+                    ldsm_x2(a_zp + 32 * (q + 1), zfr[nxt][0], zfr[nxt][1]);
+                }
                 const int wi = q >> 2, i0 = 2 * (q & 3);
                 const uint32_t b0 = hmul2_f16(QS[2 * q], F[2 * q]), b1 = hmul2_f16(QS[2 * q + 1], F[2 * q + 1]);
 #pragma unroll
@@ -713,18 +734,13 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 }
                 if (has_delta) {
 #pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        uint32_t d0, d1, d2, d3;
-                        ldsm_x4(a_delta + 16 * mt * DT_STRIDE + 32 * q, d0, d1, d2, d3);
-                        mma_f16(Sd[mt], d0, d1, d2, d3, QD[2 * q], QD[2 * q + 1]);
-                    }
+                    for (int mt = 0; mt < 2; ++mt)
+                        mma_f16(Sd[mt], dfr[cur][mt][0], dfr[cur][mt][1], dfr[cur][mt][2], dfr[cur][mt][3], QD[2 * q], QD[2 * q + 1]);
                 }
-                uint32_t z0, z1;
-                ldsm_x2(a_zp + 32 * q, z0, z1);
-                mma_f16(Sz, z0, 0u, z1, 0u, QD[2 * q], QD[2 * q + 1]);
+                mma_f16(Sz, zfr[cur][0], 0u, zfr[cur][1], 0u, QD[2 * q], QD[2 * q + 1]);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * (MAX_STAGES * unit + (consumed % NS)));   // the next tile may be built
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot((int)consumed, NS)));   // the next tile may be built
             ++consumed;
             OMMX_TR(8 * it + 4);
 
@@ -1198,6 +1214,7 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.sm_scale = a->sm_scale; p.logit_cap = a->logit_cap; p.status = a->status;
     const int H = p.H;
     p.GS = NCW / H;
+    p.hshift = H == 8 ? 3 : (H == 4 ? 2 : (H == 2 ? 1 : 0));
     p.o_vm = H * 1024; p.o_vs = H * 2048; p.o_vz = p.o_vs + H * 128; p.o_ks = p.o_vz + H * 256;
     p.o_kz = p.o_ks + H * 128; p.o_ms = p.o_kz + H * 256; p.o_mc = p.o_ms + H * 256; p.o_bm = p.o_mc + H * 256;
     p.o_ov = p.o_bm + H * 512;
