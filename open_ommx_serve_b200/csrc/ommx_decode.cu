@@ -977,9 +977,35 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
             }
         }
     }
+    // residual V rows of this warp (rows warp, warp+16, ...), fetched now: they do not depend on stage 1
+    const __nv_bfloat16 *vt = p.v_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
+    constexpr int PRE_T = 5, PRE_S = 10;                                 // rows / splits per warp held in registers
+    float vpre[PRE_T][4];
+#pragma unroll
+    for (int k = 0; k < PRE_T; ++k) {
+        const int r = warp + k * S2_WARPS;
+        vpre[k][0] = vpre[k][1] = vpre[k][2] = vpre[k][3] = 0.f;
+        if (r < tail) {
+            const __nv_bfloat16 *row = vt + (int64_t)r * p.t_st;
+            vpre[k][0] = __bfloat162float(row[lane]); vpre[k][1] = __bfloat162float(row[lane + 32]);
+            vpre[k][2] = __bfloat162float(row[lane + 64]); vpre[k][3] = __bfloat162float(row[lane + 96]);
+        }
+    }
     // ---- everything below reads what stage 1 wrote: wait for that grid (no-op without a
     //      programmatic launch) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The split rows of this warp are requested together with the lse values, not after the weights are
+    // known: the kernel is a chain of global round trips and this takes one link out of it.
+    float spre[PRE_S][4];
+#pragma unroll
+    for (int k = 0; k < PRE_S; ++k) {
+        const int s = warp + k * S2_WARPS;
+        spre[k][0] = spre[k][1] = spre[k][2] = spre[k][3] = 0.f;
+        if (s < nsplit) {
+            const float *row = base + (int64_t)s * p.al_ss;
+            spre[k][0] = row[lane]; spre[k][1] = row[lane + 32]; spre[k][2] = row[lane + 64]; spre[k][3] = row[lane + 96];
+        }
+    }
     float mloc = -INFINITY;
     for (int s = tid; s < nsplit; s += S2_THREADS) {
         const float l = base[(int64_t)s * p.al_ss + D];
@@ -1012,16 +1038,31 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
 
     // ---- weighted sum: warp w takes splits / rows w, w+16, ...; lane owns channels lane + 32*i ----
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int k = 0; k < PRE_S; ++k) {
+        const int s = warp + k * S2_WARPS;
+        if (s < nsplit) {
+            const float w = s_w[s];
+            a0 += w * spre[k][0]; a1 += w * spre[k][1]; a2 += w * spre[k][2]; a3 += w * spre[k][3];
+        }
+    }
 #pragma unroll 4
-    for (int s = warp; s < nsplit; s += S2_WARPS) {
+    for (int s = warp + PRE_S * S2_WARPS; s < nsplit; s += S2_WARPS) {
         const float *row = base + (int64_t)s * p.al_ss;
         const float w = s_w[s];
         a0 += w * row[lane]; a1 += w * row[lane + 32]; a2 += w * row[lane + 64]; a3 += w * row[lane + 96];
     }
     if (tail > 0) {
-        const __nv_bfloat16 *vt = p.v_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
+#pragma unroll
+        for (int k = 0; k < PRE_T; ++k) {
+            const int r = warp + k * S2_WARPS;
+            if (r < tail) {
+                const float w = s_logit[r];
+                a0 += w * vpre[k][0]; a1 += w * vpre[k][1]; a2 += w * vpre[k][2]; a3 += w * vpre[k][3];
+            }
+        }
 #pragma unroll 4
-        for (int r = warp; r < tail; r += S2_WARPS) {
+        for (int r = warp + PRE_T * S2_WARPS; r < tail; r += S2_WARPS) {
             const __nv_bfloat16 *row = vt + (int64_t)r * p.t_st;
             const float w = s_logit[r];
             a0 += w * __bfloat162float(row[lane]); a1 += w * __bfloat162float(row[lane + 32]);
