@@ -502,8 +502,12 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 }
                 OMMX_TR(trk + 3);
                 const uint32_t bmv[2] = {bm2.x, bm2.y};
-                const uint8_t *kreg = gb;                            // k_base region of the group (1 KB aligned)
-                const uint32_t kl_off = (uint32_t)(h * 32 + (d0 >> 2));   // the code byte holding this lane's channels
+                // The code byte holding this lane's channels, row pz: byte pz*TS + h*32 + d0/4 of the (1 KB aligned)
+                // k_base block, with the 16-byte chunk bits XOR-ed by the row's swizzle term.  h*32 + d0/4 splits
+                // into a part above bit 7 (added to the row) and a part below (the XOR operand).
+                const uint32_t k_hi_rel = (uint32_t)(h >> 2) * 128u;
+                const uint8_t *k_hi = gb + k_hi_rel;
+                const uint32_t k_lo = (uint32_t)((h & 3) * 32 + (d0 >> 2));
                 // this lane's entry in the fragment-ordered K factor row
                 const uint32_t kf_off = ROW_KF * DT_STRIDE + 64u * (2 * hf + (lane >> 4)) + 32u * ((lane >> 3) & 1) + 8u * (lane & 3) + 2u * ((lane >> 2) & 1);
                 uint32_t zph[2];
@@ -537,7 +541,9 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                                     const int pz = 31 - __clz(bits);
                                     bits ^= 1u << pz;
                                     const uint32_t nib = (stream >> (4 * r)) & 0xFu;
-                                    const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> fsh) & 3u);
+                                    const uint32_t row = (uint32_t)pz * (uint32_t)TS;
+                                    const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
+                                    const float cf = (float)((cb >> fsh) & 3u);
                                     const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
                                     *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
                                 }
@@ -551,7 +557,9 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                                 bits ^= 1u << pz;
                                 const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
                                 --r;
-                                const float cf = (float)((kreg[swz128(kl_off + pz * TS, p.swz)] >> fsh) & 3u);
+                                const uint32_t row = (uint32_t)pz * (uint32_t)TS;
+                                const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
+                                const float cf = (float)((cb >> fsh) & 3u);
                                 const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
                                 *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
                             }
@@ -813,15 +821,26 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     }
                 }
                 const uint8_t *p_zt = tile + (ROW_ZT + copy) * DT_STRIDE + 64 * (g & 3) + 4 * j;
+                const uint32_t v_hi_rel = (uint32_t)(h >> 2) * 128u, v_lo = (uint32_t)((h & 3) * 32 + g);
 #pragma unroll
                 for (int ks = 0; ks < 2; ++ks) {
                     const int tA = 16 * ks + 2 * j;
-                    const uint32_t o0 = (uint32_t)(tA * TS + h * 32 + g), o1 = o0 + TS, o8 = o0 + 8 * TS, o9 = o8 + TS;
+                    // Byte 8cg + g of a token row's 32-byte head slice, four scale groups per row.  The swizzle term
+                    // of a row only touches bits 4..6, so two XORs give the addresses of groups 0 and 2 and the
+                    // other two are 8 bytes on.
+                    uint32_t vb[4][4];                               // [token of (tA, tA+1, tA+8, tA+9)][scale group]
+#pragma unroll
+                    for (int tt = 0; tt < 4; ++tt) {
+                        const uint32_t rowhi = (uint32_t)(tA + (tt & 1) + 8 * (tt >> 1)) * (uint32_t)TS + v_hi_rel;
+                        const uint32_t tm = (rowhi >> 3) & p.swz;
+                        const uint8_t *r0 = vreg + (rowhi + (v_lo ^ tm)), *r1 = vreg + (rowhi + ((v_lo ^ 16u) ^ tm));
+                        vb[tt][0] = r0[0]; vb[tt][1] = r0[8];
+                        vb[tt][2] = r1[0]; vb[tt][3] = r1[8];
+                    }
 #pragma unroll
                     for (int cg = 0; cg < 4; ++cg) {
                         // channels 32cg + 4g .. + 3 of four tokens: one byte each
-                        const uint32_t bA = vreg[swz128(o0 + 8 * cg, p.swz)], bA1 = vreg[swz128(o1 + 8 * cg, p.swz)];
-                        const uint32_t bB = vreg[swz128(o8 + 8 * cg, p.swz)], bB1 = vreg[swz128(o9 + 8 * cg, p.swz)];
+                        const uint32_t bA = vb[0][cg], bA1 = vb[1][cg], bB = vb[2][cg], bB1 = vb[3][cg];
                         const uint32_t w01 = bA | (bA1 << 16), w89 = bB | (bB1 << 16);
                         const uint32_t pb0 = hmul2_f16(T[ks][0], VF[4 * cg + 2 * ks]), pb1 = hmul2_f16(T[ks][1], VF[4 * cg + 2 * ks + 1]);
 #pragma unroll
