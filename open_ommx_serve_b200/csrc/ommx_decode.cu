@@ -5,26 +5,25 @@
 // of the reference).  One CTA serves one (split, sequence) pair and ALL local kv heads of its
 // token range, so every page row it touches is a full contiguous line:
 //
-//   producer warp   streams whole pages / group-slot planes into a 4-stage shared-memory ring
-//                   with 1-D bulk async copies (cp.async.bulk + mbarrier transaction counts);
-//                   page ids and group slots of the split are prefetched into shared memory once.
-//   8 consumer warps each own one (group, kv head) unit per stage and keep a private online-
-//                   softmax state.  Per unit:
-//     phase A (lane = 4 channels): walk the outlier bitmask with clz, decode the FP4 nibble,
-//                   and write the delta between the outlier value and the base code it replaces,
-//                   expressed in code units, into a per-warp bf16 tile [token][channel-slot].
-//     phase B (mma lanes): 2-bit codes -> bf16 with one LOP3 per pair (magic exponent, value
-//                   128 + code*4^p), per-channel power-of-two scale folded into q, QK^T on
-//                   mma.sync m16n8k16 (GQA rows padded to 16); the outlier tile is a second B
-//                   operand read with ldmatrix; one extra tile row carries zp/scale and one
-//                   carries -128, so q.zp and the magic offset come out of the same MMAs.
-//                   Online softmax with quad shuffles, P in bf16, V dequantized in bf16x2
-//                   (code*vs+vz, as the reference) and P.V on the same MMA shape.
+//   producer warp   streams whole pages / group-slot planes into a shared-memory ring: the two
+//                   code planes through swizzled tensor maps, the small planes with 1-D bulk
+//                   copies, completion through mbarrier transaction counts; page ids, group
+//                   slots and the copy roles of a stage are tabulated in shared memory once.
+//   15 decode warps build, two per (group, kv head) unit, the unit's sidecar tile: outlier
+//                   deltas (bit walk with clz, FP4 nibble, base code byte) as fp16
+//                   [token][channel], zero-points, and the power-of-two K and V scale factors
+//                   laid out in MMA-fragment order.
+//   8 MMA warps     own one unit per stage and a private online-softmax state.  All MMAs are
+//                   m16n8k16 fp16 with the 2-bit codes as the A operand - a code field masked in
+//                   place is the fp16 subnormal code * 4^slot * 2^-24, exact and offset-free - and
+//                   the query heads as the 8 columns: logits = codes.(q*2^e) + delta.q + zp.q,
+//                   softmax over token rows, P transposed with movmatrix, output =
+//                   codes^T.(P*2^e_v) + vz^T.P.
 //
 // Numerics follow the reference kernel's rounding points: q*sm_scale rounded to bf16, exact
-// code*2^e products, the outlier delta rounded to bf16, fp32 accumulation, P rounded to bf16, V
-// dequantized to bf16.  One point differs at the bf16-rounding level: q.zp uses the bf16
-// q*sm_scale instead of fp32 q.
+// code*2^e products, the outlier delta rounded to bf16, fp32 accumulation, V as exact code*2^e
+// products with the zero-point bias summed apart.  Two points differ inside the gate: q.zp uses
+// the bf16 q*sm_scale instead of fp32 q, and P is rounded to fp16 (11 bits) instead of bf16.
 #include "ommx_common.cuh"
 #include <cuda.h>                       // CUtensorMap (types only; the encoder is looked up at run time)
 #include <mutex>
