@@ -21,10 +21,9 @@ def _run_and_check(case, **kw):
     max_abs = kw.pop("max_abs", 2e-2)
     o, lse = case.run(**kw)
     ctx = str(case.seq_lens[:6])
-    # GQA groups of at most 4 run the reference's split-PV arithmetic (exact code*scale products, zero-point
-    # bias summed apart); larger groups its fused form bf16(code*scale + zp)
-    want_o, want_lse = case.oracle_kernel_arith(num_kv_splits=int(kw.get("num_kv_splits") or 1),
-                                                split_pv=case.Hq // case.H <= 4)
+    # every GQA width runs the reference's split-PV arithmetic (exact code*scale products, zero-point bias
+    # summed apart)
+    want_o, want_lse = case.oracle_kernel_arith(num_kv_splits=int(kw.get("num_kv_splits") or 1), split_pv=True)
     check_close(o, want_o, max_abs=max_abs, ctx="kernel-arith " + ctx)
     # lse: the kernel forms q.zp from the bf16-rounded q*sm_scale (the reference from fp32 q), a common
     # logit offset of up to ~2^-9 * |q.zp| that cancels in o; it shows in lse when K is scaled x30
@@ -206,6 +205,34 @@ def test_decode_status_word_on_bad_tables():
     bits = int(status.item())
     assert bits & _lib.ST_BAD_PAGE and bits & _lib.ST_BAD_GROUP
     assert torch.isfinite(o).all()                  # the access was skipped, nothing trapped
+
+
+def test_decode_scale_exponent_out_of_fp16_range_is_clamped_and_reported():
+    """Scale factors travel as fp16 powers of two: exponents above 11 are clamped and flagged,
+    tiny ones (below 2^-18) drop their term; neither traps nor produces a non-finite output."""
+    from open_ommx_serve_b200 import _lib
+    case = Case([500], seed=12)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o_ref, _ = case.run(status=status)
+    assert int(status.item()) == 0
+    vs = case.planes["v_scale"]
+    vs.view(-1)[5] = 13                              # one V scale step of 2^13
+    ks = case.planes["k_scale"]
+    ks.view(-1)[7] = -40                             # one K scale step of 2^-40
+    o, _ = case.run(status=status)
+    assert int(status.item()) & _lib.ST_SCALE_RANGE
+    assert torch.isfinite(o).all()
+
+
+def test_decode_128k_one_kv_head_shard():
+    """The 8-way sharded long-context shape: 128K tokens, one local kv head (4 query heads), 8 groups
+    in flight per CTA.  Checked through split-count invariance and the fp32 oracle."""
+    case = Case([131072], H=1, Hq=4, seed=77)
+    o148, l148 = case.run(num_kv_splits=148)
+    o32, l32 = case.run(num_kv_splits=32)
+    assert (o148 - o32).abs().max().item() < 5e-3
+    assert (l148 - l32).abs().max().item() < 5e-3
+    check_fp32(o148, case.oracle()[0], ctx="128K fp32")
 
 
 def test_decode_refusals():
