@@ -158,6 +158,49 @@ int ommx_b200_decode_stage2(const ommx_decode_args *args, void *stream);   /* at
 int ommx_b200_decode_static_ws(const ommx_decode_args *args, void *stream);
 
 /*
+ * Device-resident decode-step store for a pool of sequences.  Replaces the host loop of
+ * MultiSeqKVPool.append_decode_device + decode_inputs_device
+ * (ommx_gpu_serve/attention/kv_pool.py:440-488, :1048-1105) and the ring copies
+ * _kv_write_token / _kv_gather_tail (attention/kv_store_ops.py:22,42): one call appends one
+ * new bf16 K/V row per sequence to its residual ring, quantizes and packs the 32-token group
+ * that the step completed (if any) straight from the ring into the sequence's next pages and
+ * group slot, advances the device-side sequence lengths, and writes the decode inputs of the
+ * step (packed length, residual length, gathered residual rows).  No host synchronisation, a
+ * fixed launch shape (CUDA-graph capturable), nothing allocated.
+ *
+ * A sequence of seq tokens keeps tokens [0, sink) and [boundary, seq) as bf16 rows, with
+ * boundary = sink + floor((seq - sink - recent) / 32) * 32 (or min(sink, seq) while seq <= sink +
+ * recent), and tokens [sink, boundary) in the planes.  Ring row of token pos:
+ * pos < sink ? pos : sink + (pos - sink) % (ring_cap - sink); ring_cap - sink >= recent + 32.
+ */
+typedef struct ommx_kv_pool {
+    ommx_kv_planes planes;            /* pooled planes of all sequences */
+    void *k_hist, *v_hist;            /* bf16 [num_seqs, ring_cap, n_kv_heads, head_dim] */
+    int32_t num_seqs, ring_cap;
+    int32_t sink_tokens, recent_window;
+    int32_t *seq_len;                 /* device int32 [num_seqs]: tokens held, advanced by the call */
+    const int32_t *req_to_token;      /* device int32 [num_seqs, pages_per_seq] page ids */
+    const int32_t *req_to_group;      /* device int32 [num_seqs, groups_per_seq] group slots */
+    int32_t pages_per_seq, groups_per_seq;
+} ommx_kv_pool;
+
+typedef struct ommx_kv_append_args {
+    ommx_kv_pool pool;
+    const void *k_new, *v_new;        /* bf16 [batch, n_kv_heads, head_dim]; NULL with advance = 0 */
+    int64_t new_stride_b, new_stride_h;
+    const int32_t *slots;             /* device int32 [batch]: pool slot of each row, NULL = 0..batch-1 */
+    int32_t batch;
+    int32_t advance;                  /* 1: append + pack + advance; 0: only (re)build the decode inputs */
+    int32_t outlier_select, use_pow2; /* as in ommx_pack_args; outlier_select must be 1 (signed) */
+    void *k_tail, *v_tail;            /* out, optional: bf16 [batch, max_tail, n_kv_heads, head_dim] */
+    int32_t max_tail;
+    int32_t *b_seq_len, *b_tail_len;  /* out, optional: device int32 [batch] */
+    int32_t *status;                  /* optional */
+} ommx_kv_append_args;
+
+int ommx_b200_kv_append_decode(const ommx_kv_append_args *args, void *stream);
+
+/*
  * Split count this library prefers for (max context, batch, local kv heads) on the current
  * device.  Replaces _auto_num_kv_splits (attention/paged_decode.py:409-461), which callers
  * use to size attn_logits once.

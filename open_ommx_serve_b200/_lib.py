@@ -58,6 +58,23 @@ class DecodeArgs(C.Structure):
                 ("abl_flags", C.c_int32)]
 
 
+class KVPool(C.Structure):
+    _fields_ = [("planes", KVPlanes), ("k_hist", C.c_void_p), ("v_hist", C.c_void_p),
+                ("num_seqs", C.c_int32), ("ring_cap", C.c_int32),
+                ("sink_tokens", C.c_int32), ("recent_window", C.c_int32),
+                ("seq_len", C.c_void_p), ("req_to_token", C.c_void_p), ("req_to_group", C.c_void_p),
+                ("pages_per_seq", C.c_int32), ("groups_per_seq", C.c_int32)]
+
+
+class KVAppendArgs(C.Structure):
+    _fields_ = [("pool", KVPool), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
+                ("new_stride_b", C.c_int64), ("new_stride_h", C.c_int64),
+                ("slots", C.c_void_p), ("batch", C.c_int32), ("advance", C.c_int32),
+                ("outlier_select", C.c_int32), ("use_pow2", C.c_int32),
+                ("k_tail", C.c_void_p), ("v_tail", C.c_void_p), ("max_tail", C.c_int32),
+                ("b_seq_len", C.c_void_p), ("b_tail_len", C.c_void_p), ("status", C.c_void_p)]
+
+
 #: every symbol include/ommx_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "ommx_b200_pack_kv": (C.c_int, [C.POINTER(PackArgs), C.c_void_p]),
@@ -65,6 +82,7 @@ SYMBOLS = {
     "ommx_b200_decode_stage1": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_decode_stage2": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_decode_static_ws": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
+    "ommx_b200_kv_append_decode": (C.c_int, [C.POINTER(KVAppendArgs), C.c_void_p]),
     "ommx_b200_auto_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
     "ommx_b200_min_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32]),
     "ommx_b200_merge_states": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,

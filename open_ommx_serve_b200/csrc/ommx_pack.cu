@@ -6,9 +6,11 @@
 // fp32 operation in the same order (no FMA contraction: explicit __f*_rn intrinsics), and the
 // two library calls of the reference (log2, log) are replaced by frozen threshold tables.
 //
-// K kernel: one warp per (32-token group, kv head, 16-channel block); lane = token.  Outlier
-//   selection is the reference's stable-sort rule done with warp reductions: the r-th pick is the
-//   max (min) key over unpicked lanes, ties to the lowest lane (redux.sync + ballot).
+// K kernels: the reference's stable-sort selection rule (the r-th pick is the max (min) key over
+//   unpicked tokens, ties to the lowest token) in two interchangeable forms.  pack_k_lane_kernel
+//   (signed rule, k in {0,2,4,6,8}): one warp per (group, kv head, 32 channels), lane = channel,
+//   per-lane loops over 32 register values.  pack_k_kernel (any rule, k <= 16): one warp per
+//   (group, kv head, 16 channels), lane = token, warp reductions (redux.sync + ballot).
 // V kernel: one thread per (token, head, 32-channel group).
 #include "ommx_common.cuh"
 
@@ -24,6 +26,11 @@ template <> __device__ __forceinline__ float load_as_f32<__nv_bfloat16>(const __
 }
 template <> __device__ __forceinline__ float load_as_f32<__half>(const __half *p) { return __half2float(*p); }
 
+// a 16-bit storage pattern of T as fp32 (T = float never takes this path)
+template <typename T> __device__ __forceinline__ float bits16_as_f32(uint32_t b) { return 0.f; }
+template <> __device__ __forceinline__ float bits16_as_f32<__nv_bfloat16>(uint32_t b) { return __uint_as_float(b << 16); }
+template <> __device__ __forceinline__ float bits16_as_f32<__half>(uint32_t b) { return __half2float(__ushort_as_half((unsigned short)b)); }
+
 // Monotone map fp32 -> uint32 (larger float <=> larger key); -0.0 is folded onto +0.0 first so
 // that equal values tie exactly as they do under the reference's float comparisons.
 __device__ __forceinline__ uint32_t f32_key(float x) {
@@ -35,7 +42,22 @@ __device__ __forceinline__ float key_f32(uint32_t k) {
     return __uint_as_float(u);
 }
 
+// Decode-step source: instead of a linear block of tokens, unit "group" i is batch row i of a pool of
+// sequences; its 32 tokens are the group the step completed (none: the unit returns), read from the
+// residual ring, and its destination comes from the sequence's own page / group-slot tables.
+struct PoolSrc {
+    const int32_t *seq;               // null = linear source
+    const int32_t *slots;
+    const int32_t *r2t, *r2g;
+    int32_t ring_cap, sink, recent, groups_per_seq, pages_per_seq;
+};
+__device__ __forceinline__ int pool_groups_at(const PoolSrc &ps, int seq) {
+    const int spare = seq - ps.sink - ps.recent;
+    return spare > 0 ? spare / 32 : 0;
+}
+
 struct PackKParams {
+    PoolSrc pool;
     const void *k;
     int64_t stride_token, stride_head;
     int32_t num_groups, H, D, page_size;
@@ -199,7 +221,208 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_kernel(PackKParams p) 
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// K kernel, lane-per-channel form, for the signed selection rule with a compile-time (KT, KB) =
+// (picks from the top, picks from the bottom).  One warp per (32-token group, kv head, 32-channel
+// block); lane = channel; the lane holds its channel's 32 token values in registers, so selection,
+// min/max and quantization are plain per-lane loops over registers: no warp reductions, and every
+// per-channel step (scale snap, zero-point, FP4 map) runs for 32 channels at once.  The 2-bit codes
+// (lane-major: one lane, 32 tokens) are turned token-major (one lane, 32 channels = the 8 bytes of
+// a token's row) by a five-stage shuffle butterfly.  Same arithmetic, in the same order, as
+// pack_k_kernel; the two are interchangeable bit for bit.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int KT, int KB>
+__global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_lane_kernel(PackKParams p) {
+    constexpr int K = KT + KB;
+    constexpr int NB = (K + 1) / 2;
+    static_assert(K <= 8, "the nibble stream is kept in 32 bits");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk = p.D / 32;
+    const int unit = blockIdx.x * PACK_WARPS + warp;           // (group, head, 32-channel block)
+    if (unit >= p.num_groups * p.H * nblk) return;
+    const int blk = unit % nblk;
+    const int gh = unit / nblk;
+    const int g = gh / p.H, h = gh - g * p.H;
+    const int D = p.D;
+
+    // ---- this channel's 32 token values ----
+    const T *col = reinterpret_cast<const T *>(p.k) + (int64_t)h * p.stride_head + blk * 32 + lane;
+    float x[32];
+    int grp = g, seq_slot = 0;                // pool source: group index inside the sequence, sequence slot
+    if (p.pool.seq) {
+        seq_slot = p.pool.slots ? p.pool.slots[g] : g;
+        const int pos = p.pool.seq[seq_slot];
+        grp = pool_groups_at(p.pool, pos);
+        if (pool_groups_at(p.pool, pos + 1) == grp) return;          // this step completes no group
+        const int rec = p.pool.ring_cap - p.pool.sink;
+        const int first = (grp * 32) % rec;                           // ring row (behind the sink rows) of token 0
+        col += (int64_t)(seq_slot * p.pool.ring_cap + p.pool.sink) * p.stride_token;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            int rr = first + t;
+            if (rr >= rec) rr -= rec;
+            x[t] = load_as_f32(col + (int64_t)rr * p.stride_token);
+        }
+    } else {
+        col += (int64_t)(g * 32) * p.stride_token;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) x[t] = load_as_f32(col + (int64_t)t * p.stride_token);
+    }
+
+    const int slot = p.pool.seq ? p.pool.r2g[seq_slot * p.pool.groups_per_seq + grp] : (p.dst_groups ? p.dst_groups[g] : g);
+    const bool slot_ok = (slot >= 0 && slot < p.num_group_slots);
+    if (!slot_ok && lane == 0) or_status(p.status, OMMX_ST_BAD_GROUP);
+    const bool store_f32 = (p.scale_kind == OMMX_SCALE_F32);
+
+    bool bad = false;
+    uint32_t cand[32];                        // order keys; 0 marks a picked token (no finite value has key 0)
+#pragma unroll
+    for (int t = 0; t < 32; ++t) {
+        bad |= !isfinite(x[t]);
+        cand[t] = f32_key(x[t]);
+    }
+    // ---- outlier selection: r-th pick = extreme key over unpicked tokens, ties -> lowest token ----
+    uint32_t omask = 0;
+    uint32_t pick_key[K > 0 ? K : 1];
+    int pick_tok[K > 0 ? K : 1];
+#pragma unroll
+    for (int r = 0; r < K; ++r) {
+        uint32_t m;
+        if (r < KT) {
+            m = cand[0];
+#pragma unroll
+            for (int t = 1; t < 32; ++t) m = max(m, cand[t]);
+        } else {
+            // a picked token (0) must lose the min scan: compare key - 1, which wraps 0 to the top
+            m = cand[0] - 1u;
+#pragma unroll
+            for (int t = 1; t < 32; ++t) m = min(m, cand[t] - 1u);
+            m += 1u;
+        }
+        bool found = false;
+        int tok = 0;
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            const bool hit = !found && cand[t] == m;
+            if (hit) { tok = t; cand[t] = 0u; }
+            found |= hit;
+        }
+        pick_key[r] = m;
+        pick_tok[r] = tok;
+        omask |= 1u << tok;
+    }
+    // ---- base affine over the tokens that were not picked ----
+    uint32_t kmax = cand[0], kmin = cand[0] - 1u;
+#pragma unroll
+    for (int t = 1; t < 32; ++t) { kmax = max(kmax, cand[t]); kmin = min(kmin, cand[t] - 1u); }
+    kmin += 1u;
+    const float mn = key_f32(kmin), mx = key_f32(kmax);
+    int e;
+    const float scale = snap_scale(__fsub_rn(mx, mn), p.use_pow2, p.scale_kind, e);
+    const float zp = store_f32 ? mn : bf16_round_f32(mn);
+    // dividing by a power of two and multiplying by its reciprocal round identically
+    const bool by_mul = p.use_pow2 && e >= -126 && e <= 126;
+    const float inv = __uint_as_float((uint32_t)(by_mul ? 127 - e : 127) << 23);
+    uint32_t cw0 = 0, cw1 = 0;                // this channel's codes, token t at bits 2t
+#pragma unroll
+    for (int t = 0; t < 32; ++t) {
+        const float d = __fsub_rn(x[t], zp);
+        float qv = rintf(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
+        qv = fminf(fmaxf(qv, 0.f), 3.f);
+        if (t < 16) cw0 |= (uint32_t)(int)qv << (2 * t);
+        else cw1 |= (uint32_t)(int)qv << (2 * (t - 16));
+    }
+    // ---- outlier values ----
+    float ms = 0.f, mc = 0.f;
+    uint32_t val = 0;
+    if (K > 0) {
+        if (p.outlier_map) {
+            uint32_t okmin = pick_key[0], okmax = pick_key[0];
+#pragma unroll
+            for (int r = 1; r < K; ++r) { okmin = min(okmin, pick_key[r]); okmax = max(okmax, pick_key[r]); }
+            const float omn = key_f32(okmin), omx = key_f32(okmax);
+            mc = __fmul_rn(__fadd_rn(omx, omn), 0.5f);
+            // the reference evaluates 12.0 / range as reciprocal(range) * 12
+            ms = __fmul_rn(__frcp_rn(fmaxf(__fsub_rn(omx, omn), 1e-8f)), 12.0f);
+            if (!store_f32) { mc = bf16_round_f32(mc); ms = bf16_round_f32(ms); }
+        }
+#pragma unroll
+        for (int r = 0; r < K; ++r) {
+            const float xo = key_f32(pick_key[r]);            // the picked value (-0.0 reads back as +0.0: same code)
+            const float mapped = p.outlier_map ? __fmul_rn(__fsub_rn(xo, mc), ms) : __fdiv_rn(__fsub_rn(xo, zp), scale);
+            const uint32_t fp4 = (uint32_t)fp4_encode_tbl(mapped, c_fp4_thresh);
+            const int rank = __popc(omask & ((1u << pick_tok[r]) - 1u));
+            val |= fp4 << (4 * rank);
+        }
+    }
+    // ---- per-channel planes: consecutive lanes, consecutive entries ----
+    if (slot_ok) {
+        const int64_t off = ((int64_t)slot * p.H + h) * D + blk * 32 + lane;
+        if (p.scale_kind == OMMX_SCALE_INT8_EXP) reinterpret_cast<int8_t *>(p.k_scale)[off] = (int8_t)e;
+        else if (p.scale_kind == OMMX_SCALE_BF16) reinterpret_cast<uint16_t *>(p.k_scale)[off] = (uint16_t)f32_to_bf16_bits(scale);
+        else reinterpret_cast<float *>(p.k_scale)[off] = scale;
+        if (store_f32) reinterpret_cast<float *>(p.k_zp)[off] = zp;
+        else reinterpret_cast<uint16_t *>(p.k_zp)[off] = (uint16_t)f32_to_bf16_bits(zp);
+        if (K > 0) {
+            if (p.outlier_map) {
+                if (store_f32) {
+                    reinterpret_cast<float *>(p.k_mapscale)[off] = ms;
+                    reinterpret_cast<float *>(p.k_mapcenter)[off] = mc;
+                } else {
+                    reinterpret_cast<uint16_t *>(p.k_mapscale)[off] = (uint16_t)f32_to_bf16_bits(ms);
+                    reinterpret_cast<uint16_t *>(p.k_mapcenter)[off] = (uint16_t)f32_to_bf16_bits(mc);
+                }
+            }
+            reinterpret_cast<uint32_t *>(p.k_obmp)[off] = omask;
+#pragma unroll
+            for (int i = 0; i < NB; ++i) p.k_oval[off * NB + i] = (uint8_t)(val >> (8 * i));
+        }
+    }
+    if (bad) or_status(p.status, OMMX_ST_NONFINITE);
+
+    // ---- codes: lane-major (channel, 32 tokens) -> token-major (token, 32 channels) ----
+    // Stage s swaps element (lane, c) having lane bit s clear and c bit s set with element (lane^s, c^s).
+    {
+        const uint32_t send = (lane & 16) ? cw0 : cw1;
+        const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, send, 16);
+        if (lane & 16) cw0 = got; else cw1 = got;
+    }
+    {
+        const uint32_t g0 = __shfl_xor_sync(0xFFFFFFFFu, cw0, 8), g1 = __shfl_xor_sync(0xFFFFFFFFu, cw1, 8);
+        const uint32_t sel = (lane & 8) ? 0x3276u : 0x5410u;
+        cw0 = __byte_perm(cw0, g0, sel); cw1 = __byte_perm(cw1, g1, sel);
+    }
+    {
+        const uint32_t g0 = __shfl_xor_sync(0xFFFFFFFFu, cw0, 4), g1 = __shfl_xor_sync(0xFFFFFFFFu, cw1, 4);
+        const uint32_t sel = (lane & 4) ? 0x3715u : 0x6240u;
+        cw0 = __byte_perm(cw0, g0, sel); cw1 = __byte_perm(cw1, g1, sel);
+    }
+    {
+        const uint32_t g0 = __shfl_xor_sync(0xFFFFFFFFu, cw0, 2), g1 = __shfl_xor_sync(0xFFFFFFFFu, cw1, 2);
+        if (lane & 2) { cw0 = (cw0 & 0xF0F0F0F0u) | ((g0 >> 4) & 0x0F0F0F0Fu); cw1 = (cw1 & 0xF0F0F0F0u) | ((g1 >> 4) & 0x0F0F0F0Fu); }
+        else          { cw0 = (cw0 & 0x0F0F0F0Fu) | ((g0 << 4) & 0xF0F0F0F0u); cw1 = (cw1 & 0x0F0F0F0Fu) | ((g1 << 4) & 0xF0F0F0F0u); }
+    }
+    {
+        const uint32_t g0 = __shfl_xor_sync(0xFFFFFFFFu, cw0, 1), g1 = __shfl_xor_sync(0xFFFFFFFFu, cw1, 1);
+        if (lane & 1) { cw0 = (cw0 & 0xCCCCCCCCu) | ((g0 >> 2) & 0x33333333u); cw1 = (cw1 & 0xCCCCCCCCu) | ((g1 >> 2) & 0x33333333u); }
+        else          { cw0 = (cw0 & 0x33333333u) | ((g0 << 2) & 0xCCCCCCCCu); cw1 = (cw1 & 0x33333333u) | ((g1 << 2) & 0xCCCCCCCCu); }
+    }
+    // lane = token now: its 8 code bytes of this channel block
+    const int ps = p.page_size;
+    const int tok = grp * 32 + lane;
+    int page = tok / ps;
+    if (p.pool.seq) page = p.pool.r2t[seq_slot * p.pool.pages_per_seq + page];
+    else if (p.dst_pages) page = p.dst_pages[page];
+    const bool page_ok = (page >= 0 && page < p.num_pages);
+    if (!page_ok) or_status(p.status, OMMX_ST_BAD_PAGE);
+    if (page_ok) {
+        uint8_t *dst = p.k_base + (((int64_t)page * ps + (tok % ps)) * p.H + h) * (D / 4) + 8 * blk;
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(cw0, cw1);
+    }
+}
+
 struct PackVParams {
+    PoolSrc pool;
     const void *v;
     int64_t stride_token, stride_head;
     int32_t num_tokens, H, D, page_size;
@@ -217,15 +440,43 @@ __global__ void __launch_bounds__(128) pack_v_kernel(PackVParams p) {
     if (idx >= (int64_t)p.num_tokens * p.H * ngv) return;
     const int cg = (int)(idx % ngv);
     const int h = (int)((idx / ngv) % p.H);
-    const int t = (int)(idx / ((int64_t)ngv * p.H));
-    const T *row = reinterpret_cast<const T *>(p.v) + (int64_t)t * p.stride_token + (int64_t)h * p.stride_head + cg * 32;
+    int t = (int)(idx / ((int64_t)ngv * p.H));
+    const T *row = reinterpret_cast<const T *>(p.v) + (int64_t)h * p.stride_head + cg * 32;
+    int seq_slot = 0;
+    if (p.pool.seq) {
+        const int i = t / 32, tt = t % 32;                              // batch row, token inside the completed group
+        seq_slot = p.pool.slots ? p.pool.slots[i] : i;
+        const int pos = p.pool.seq[seq_slot];
+        const int grp = pool_groups_at(p.pool, pos);
+        if (pool_groups_at(p.pool, pos + 1) == grp) return;
+        const int rec = p.pool.ring_cap - p.pool.sink;
+        const int rr = (grp * 32 + tt) % rec;
+        row += (int64_t)(seq_slot * p.pool.ring_cap + p.pool.sink + rr) * p.stride_token;
+        t = grp * 32 + tt;                                              // token index inside the sequence's packed part
+    } else {
+        row += (int64_t)t * p.stride_token;
+    }
     float x[32];
     bool bad = false;
+    if (sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+        // 64 contiguous bytes: four 16-byte loads
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        x[i] = load_as_f32(row + i);
-        if (!isfinite(x[i])) bad = true;
+        for (int v = 0; v < 4; ++v) {
+            const uint4 w = reinterpret_cast<const uint4 *>(row)[v];
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x[8 * v + 2 * i] = bits16_as_f32<T>(ww[i] & 0xFFFFu);
+                x[8 * v + 2 * i + 1] = bits16_as_f32<T>(ww[i] >> 16);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = load_as_f32(row + i);
     }
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+        if (!isfinite(x[i])) bad = true;
     float mn = x[0], mx = x[0];
 #pragma unroll
     for (int i = 1; i < 32; ++i) { mn = fminf(mn, x[i]); mx = fmaxf(mx, x[i]); }
@@ -234,17 +485,22 @@ __global__ void __launch_bounds__(128) pack_v_kernel(PackVParams p) {
     const float scale = snap_scale(__fsub_rn(mx, mn), p.use_pow2, p.scale_kind, e);
     const bool store_f32 = (p.scale_kind == OMMX_SCALE_F32);
     const float zp = store_f32 ? mn : bf16_round_f32(mn);
+    // dividing by a power of two and multiplying by its reciprocal round identically
+    const bool by_mul = p.use_pow2 && e >= -126 && e <= 126;
+    const float inv = __uint_as_float((uint32_t)(by_mul ? 127 - e : 127) << 23);
     uint32_t w0 = 0, w1 = 0;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-        float qv = rintf(__fdiv_rn(__fsub_rn(x[i], zp), scale));
+        const float d = __fsub_rn(x[i], zp);
+        float qv = rintf(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
         qv = fminf(fmaxf(qv, 0.f), 3.f);
         uint32_t c = (uint32_t)(int)qv;
         if (i < 16) w0 |= c << (2 * i); else w1 |= c << (2 * (i - 16));
     }
     if (bad) or_status(p.status, OMMX_ST_NONFINITE);
     int page = t / p.page_size;
-    if (p.dst_pages) page = p.dst_pages[page];
+    if (p.pool.seq) page = p.pool.r2t[seq_slot * p.pool.pages_per_seq + page];
+    else if (p.dst_pages) page = p.dst_pages[page];
     if (page < 0 || page >= p.num_pages) { or_status(p.status, OMMX_ST_BAD_PAGE); return; }
     const int64_t loc = ((int64_t)page * p.page_size + (t % p.page_size)) * p.H + h;
     uint2 *dst = reinterpret_cast<uint2 *>(p.v_main + loc * (p.D / 4) + cg * 8);
@@ -261,6 +517,7 @@ template <typename T>
 static int launch_pack(const ommx_pack_args *a, cudaStream_t st) {
     const ommx_kv_planes &pl = a->planes;
     PackKParams kp;
+    memset(&kp.pool, 0, sizeof(kp.pool));
     kp.k = a->k; kp.stride_token = a->stride_token; kp.stride_head = a->stride_head;
     kp.num_groups = a->num_tokens / 32; kp.H = pl.n_kv_heads; kp.D = pl.head_dim; kp.page_size = pl.page_size;
     kp.dst_pages = a->dst_pages; kp.dst_groups = a->dst_groups;
@@ -271,12 +528,26 @@ static int launch_pack(const ommx_pack_args *a, cudaStream_t st) {
     kp.k_mapscale = pl.k_mapscale; kp.k_mapcenter = pl.k_mapcenter;
     kp.k_obmp = (uint8_t *)pl.k_obmp; kp.k_oval = (uint8_t *)pl.k_oval; kp.status = a->status;
     const int units = kp.num_groups * kp.H * (kp.D / PACK_BLK);
+    // the lane-per-channel kernel serves the signed rule with the usual outlier counts; everything else
+    // (absolute selection, odd or large k) goes through the warp-reduction kernel
+    const int lane_units = kp.num_groups * kp.H * (kp.D / 32);
+    const unsigned lane_grid = (unsigned)((lane_units + PACK_WARPS - 1) / PACK_WARPS);
+    const bool k_base_8 = (((uintptr_t)pl.k_base & 7) == 0);
+    const int ksel = (kp.select_signed && k_base_8) ? kp.k_out : -1;
     if (units > 0) {
-        pack_k_kernel<T><<<(units + PACK_WARPS - 1) / PACK_WARPS, PACK_WARPS * 32, 0, st>>>(kp);
+        switch (ksel) {
+            case 0: pack_k_lane_kernel<T, 0, 0><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            case 2: pack_k_lane_kernel<T, 1, 1><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            case 4: pack_k_lane_kernel<T, 2, 2><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            case 6: pack_k_lane_kernel<T, 3, 3><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            case 8: pack_k_lane_kernel<T, 4, 4><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            default: pack_k_kernel<T><<<(units + PACK_WARPS - 1) / PACK_WARPS, PACK_WARPS * 32, 0, st>>>(kp); break;
+        }
         OMMX_CUDA_TRY(cudaGetLastError());
         count_launch();
     }
     PackVParams vp;
+    memset(&vp.pool, 0, sizeof(vp.pool));
     vp.v = a->v; vp.stride_token = a->stride_token; vp.stride_head = a->stride_head;
     vp.num_tokens = a->num_tokens; vp.H = pl.n_kv_heads; vp.D = pl.head_dim; vp.page_size = pl.page_size;
     vp.dst_pages = a->dst_pages; vp.num_pages = pl.num_pages; vp.use_pow2 = a->use_pow2; vp.scale_kind = pl.scale_kind;
@@ -284,6 +555,148 @@ static int launch_pack(const ommx_pack_args *a, cudaStream_t st) {
     const int64_t nthreads = (int64_t)a->num_tokens * pl.n_kv_heads * (pl.head_dim / 32);
     if (nthreads > 0) {
         pack_v_kernel<T><<<(unsigned)((nthreads + 127) / 128), 128, 0, st>>>(vp);
+        OMMX_CUDA_TRY(cudaGetLastError());
+        count_launch();
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Device-resident decode-step store (reference: MultiSeqKVPool.append_decode_device /
+// decode_inputs_device, attention/kv_pool.py:440-488, :1048-1105; ring copies
+// attention/kv_store_ops.py:22-57).  Four fixed-shape launches, no host synchronisation:
+//   kv_ring_write_kernel   new row -> ring row of position seq
+//   pack_k_lane_kernel     } pool source: every batch row whose step completed a 32-token group
+//   pack_v_kernel          } packs it from the ring into its next pages / group slot; the rest return
+//   kv_finalize_kernel     seq += 1, packed / residual lengths, residual rows gathered for the decode call
+// ---------------------------------------------------------------------------------------------
+struct StoreParams {
+    PoolSrc pool;
+    __nv_bfloat16 *k_hist, *v_hist;
+    const __nv_bfloat16 *k_new, *v_new;
+    int64_t new_sb, new_sh;
+    int32_t H, D, num_seqs, advance;
+    __nv_bfloat16 *k_tail, *v_tail;
+    int32_t max_tail;
+    int32_t *b_seq_len, *b_tail_len, *seq_len, *status;
+};
+
+__device__ __forceinline__ int ring_row(const PoolSrc &ps, int pos) {
+    return pos < ps.sink ? pos : ps.sink + (pos - ps.sink) % (ps.ring_cap - ps.sink);
+}
+
+// grid (batch), 128 threads: one new K row and one new V row of H*D bf16 each
+__global__ void __launch_bounds__(128) kv_ring_write_kernel(StoreParams p) {
+    const int i = blockIdx.x;
+    const int r = p.pool.slots ? p.pool.slots[i] : i;
+    if (r < 0 || r >= p.num_seqs) { if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_GROUP); return; }
+    const int pos = p.seq_len[r];
+    if (pos < 0) { if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_LENGTH); return; }
+    const int64_t dst = ((int64_t)r * p.pool.ring_cap + ring_row(p.pool, pos)) * p.H * p.D;
+    for (int x = threadIdx.x; x < p.H * p.D; x += blockDim.x) {
+        const int h = x / p.D, c = x - h * p.D;
+        p.k_hist[dst + x] = p.k_new[(int64_t)i * p.new_sb + (int64_t)h * p.new_sh + c];
+        p.v_hist[dst + x] = p.v_new[(int64_t)i * p.new_sb + (int64_t)h * p.new_sh + c];
+    }
+}
+
+// grid (batch, rows): block (i, y) copies residual rows y, y + gridDim.y, ...; block (i, 0) also advances
+// the sequence and writes the two lengths.  Every block derives the lengths from the same old value.
+__global__ void __launch_bounds__(128) kv_finalize_kernel(StoreParams p) {
+    const int i = blockIdx.x;
+    const int r = p.pool.slots ? p.pool.slots[i] : i;
+    if (r < 0 || r >= p.num_seqs) return;
+    const int seq = p.seq_len[r] + (p.advance ? 1 : 0);
+    const int sink = p.pool.sink;
+    const int spare = seq - sink - p.pool.recent;
+    const int boundary = spare > 0 ? sink + spare / 32 * 32 : min(sink, seq);
+    const int n_sink = min(sink, seq), n_rec = max(seq - boundary, 0);
+    const int n_tail = min(n_sink + n_rec, p.max_tail);
+    if (p.k_tail && p.v_tail) {
+        const int HD = p.H * p.D;
+        for (int row = blockIdx.y; row < n_tail; row += gridDim.y) {
+            const int pos = row < n_sink ? row : boundary + (row - n_sink);
+            const uint4 *ks = reinterpret_cast<const uint4 *>(p.k_hist + ((int64_t)r * p.pool.ring_cap + ring_row(p.pool, pos)) * HD);
+            const uint4 *vs = reinterpret_cast<const uint4 *>(p.v_hist + ((int64_t)r * p.pool.ring_cap + ring_row(p.pool, pos)) * HD);
+            uint4 *kd = reinterpret_cast<uint4 *>(p.k_tail + ((int64_t)i * p.max_tail + row) * HD);
+            uint4 *vd = reinterpret_cast<uint4 *>(p.v_tail + ((int64_t)i * p.max_tail + row) * HD);
+            for (int x = threadIdx.x; x < HD / 8; x += blockDim.x) { kd[x] = ks[x]; vd[x] = vs[x]; }
+        }
+    }
+    if (blockIdx.y == 0 && threadIdx.x == 0) {
+        if (p.b_seq_len) p.b_seq_len[i] = max(boundary - sink, 0);
+        if (p.b_tail_len) p.b_tail_len[i] = n_tail;
+    }
+}
+
+// seq_len is advanced by its own one-thread-per-row kernel after every reader of the old value has run
+__global__ void kv_advance_kernel(StoreParams p, int batch) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= batch) return;
+    const int r = p.pool.slots ? p.pool.slots[i] : i;
+    if (r >= 0 && r < p.num_seqs) p.seq_len[r] += 1;
+}
+
+static int launch_append(const ommx_kv_append_args *a, cudaStream_t st) {
+    const ommx_kv_pool &pool = a->pool;
+    const ommx_kv_planes &pl = pool.planes;
+    StoreParams sp;
+    sp.pool.seq = pool.seq_len; sp.pool.slots = a->slots; sp.pool.r2t = pool.req_to_token; sp.pool.r2g = pool.req_to_group;
+    sp.pool.ring_cap = pool.ring_cap; sp.pool.sink = pool.sink_tokens; sp.pool.recent = pool.recent_window;
+    sp.pool.groups_per_seq = pool.groups_per_seq; sp.pool.pages_per_seq = pool.pages_per_seq;
+    sp.k_hist = (__nv_bfloat16 *)pool.k_hist; sp.v_hist = (__nv_bfloat16 *)pool.v_hist;
+    sp.k_new = (const __nv_bfloat16 *)a->k_new; sp.v_new = (const __nv_bfloat16 *)a->v_new;
+    sp.new_sb = a->new_stride_b; sp.new_sh = a->new_stride_h;
+    sp.H = pl.n_kv_heads; sp.D = pl.head_dim; sp.num_seqs = pool.num_seqs; sp.advance = a->advance ? 1 : 0;
+    sp.k_tail = (__nv_bfloat16 *)a->k_tail; sp.v_tail = (__nv_bfloat16 *)a->v_tail; sp.max_tail = a->max_tail;
+    sp.b_seq_len = a->b_seq_len; sp.b_tail_len = a->b_tail_len; sp.seq_len = pool.seq_len; sp.status = a->status;
+    const int B = a->batch;
+    if (a->advance) {
+        kv_ring_write_kernel<<<B, 128, 0, st>>>(sp);
+        OMMX_CUDA_TRY(cudaGetLastError());
+        count_launch();
+        PackKParams kp;
+        kp.pool = sp.pool;
+        kp.k = pool.k_hist; kp.stride_token = (int64_t)sp.H * sp.D; kp.stride_head = sp.D;
+        kp.num_groups = B; kp.H = sp.H; kp.D = sp.D; kp.page_size = pl.page_size;
+        kp.dst_pages = nullptr; kp.dst_groups = nullptr;
+        kp.num_pages = pl.num_pages; kp.num_group_slots = pl.num_group_slots;
+        kp.k_out = pl.outliers_per_vector; kp.select_signed = 1; kp.use_pow2 = a->use_pow2;
+        kp.outlier_map = pl.kv_outlier_map; kp.scale_kind = pl.scale_kind;
+        kp.k_base = (uint8_t *)pl.k_base; kp.k_scale = pl.k_scale; kp.k_zp = pl.k_zp;
+        kp.k_mapscale = pl.k_mapscale; kp.k_mapcenter = pl.k_mapcenter;
+        kp.k_obmp = (uint8_t *)pl.k_obmp; kp.k_oval = (uint8_t *)pl.k_oval; kp.status = a->status;
+        const int lane_units = B * kp.H * (kp.D / 32);
+        const unsigned lane_grid = (unsigned)((lane_units + PACK_WARPS - 1) / PACK_WARPS);
+        typedef __nv_bfloat16 T;
+        switch (kp.k_out) {
+            case 0: pack_k_lane_kernel<T, 0, 0><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            case 2: pack_k_lane_kernel<T, 1, 1><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            case 4: pack_k_lane_kernel<T, 2, 2><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            case 6: pack_k_lane_kernel<T, 3, 3><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+            default: pack_k_lane_kernel<T, 4, 4><<<lane_grid, PACK_WARPS * 32, 0, st>>>(kp); break;
+        }
+        OMMX_CUDA_TRY(cudaGetLastError());
+        count_launch();
+        PackVParams vp;
+        vp.pool = sp.pool;
+        vp.v = pool.v_hist; vp.stride_token = kp.stride_token; vp.stride_head = sp.D;
+        vp.num_tokens = B * 32; vp.H = sp.H; vp.D = sp.D; vp.page_size = pl.page_size;
+        vp.dst_pages = nullptr; vp.num_pages = pl.num_pages; vp.use_pow2 = a->use_pow2; vp.scale_kind = pl.scale_kind;
+        vp.v_main = (uint8_t *)pl.v_main; vp.v_scale = pl.v_scale; vp.v_zp = pl.v_zp; vp.status = a->status;
+        const int64_t nthreads = (int64_t)vp.num_tokens * vp.H * (vp.D / 32);
+        pack_v_kernel<T><<<(unsigned)((nthreads + 127) / 128), 128, 0, st>>>(vp);
+        OMMX_CUDA_TRY(cudaGetLastError());
+        count_launch();
+    }
+    if (a->b_seq_len || a->b_tail_len || (a->k_tail && a->v_tail)) {
+        dim3 grid(B, (a->k_tail && a->v_tail) ? 8 : 1);
+        kv_finalize_kernel<<<grid, 128, 0, st>>>(sp);
+        OMMX_CUDA_TRY(cudaGetLastError());
+        count_launch();
+    }
+    if (a->advance) {
+        kv_advance_kernel<<<(B + 127) / 128, 128, 0, st>>>(sp, B);
         OMMX_CUDA_TRY(cudaGetLastError());
         count_launch();
     }
@@ -326,4 +739,48 @@ extern "C" int ommx_b200_pack_kv(const ommx_pack_args *a, void *stream) {
         case OMMX_DT_F16: return launch_pack<__half>(a, st);
         default: return fail(OMMX_E_ARG, "pack: in_dtype=%d", a->in_dtype);
     }
+}
+
+extern "C" int ommx_b200_kv_append_decode(const ommx_kv_append_args *a, void *stream) {
+    using namespace ommx;
+    if (!a) return fail(OMMX_E_ARG, "kv_append: null args");
+    const ommx_kv_pool &pool = a->pool;
+    const ommx_kv_planes &pl = pool.planes;
+    if (a->batch <= 0) return fail(OMMX_E_ARG, "kv_append: batch=%d", a->batch);
+    if (!pool.k_hist || !pool.v_hist || !pool.seq_len || !pool.req_to_token || !pool.req_to_group)
+        return fail(OMMX_E_ARG, "kv_append: ring, seq_len and the two tables must not be null");
+    if (pool.num_seqs <= 0 || pool.sink_tokens < 0 || pool.recent_window < 0)
+        return fail(OMMX_E_ARG, "kv_append: num_seqs=%d sink=%d recent=%d", pool.num_seqs, pool.sink_tokens, pool.recent_window);
+    if (pool.ring_cap - pool.sink_tokens < pool.recent_window + 32)
+        return fail(OMMX_E_ARG, "kv_append: ring_cap=%d must hold sink + recent + 32 rows (%d)", pool.ring_cap,
+                    pool.sink_tokens + pool.recent_window + 32);
+    if (pool.pages_per_seq <= 0 || pool.groups_per_seq <= 0)
+        return fail(OMMX_E_ARG, "kv_append: pages_per_seq/groups_per_seq must be positive");
+    if (pl.head_dim % 32 != 0 || pl.head_dim <= 0 || pl.n_kv_heads <= 0)
+        return fail(OMMX_E_UNSUPPORTED, "kv_append: head_dim=%d n_kv_heads=%d", pl.head_dim, pl.n_kv_heads);
+    if (pl.page_size <= 0 || 32 % pl.page_size != 0)
+        return fail(OMMX_E_ARG, "kv_append: page_size=%d must divide 32", pl.page_size);
+    if (a->advance) {
+        if (!a->k_new || !a->v_new) return fail(OMMX_E_ARG, "kv_append: k_new/v_new are null");
+        if (a->outlier_select != 1)
+            return fail(OMMX_E_UNSUPPORTED, "kv_append: only the signed outlier rule is served");
+        const int k = pl.outliers_per_vector;
+        if (k != 0 && k != 2 && k != 4 && k != 6 && k != 8)
+            return fail(OMMX_E_UNSUPPORTED, "kv_append: outliers_per_vector=%d (served: 0, 2, 4, 6, 8)", k);
+        if (pl.scale_kind == OMMX_SCALE_INT8_EXP && !a->use_pow2)
+            return fail(OMMX_E_ARG, "kv_append: int8 exponent scales need use_pow2");
+        if (!pl.k_base || !pl.k_scale || !pl.k_zp || !pl.v_main || !pl.v_scale || !pl.v_zp)
+            return fail(OMMX_E_ARG, "kv_append: a destination plane is null");
+        if (k > 0 && (!pl.k_obmp || !pl.k_oval)) return fail(OMMX_E_ARG, "kv_append: k>0 needs k_obmp and k_oval");
+        if (k > 0 && pl.kv_outlier_map && (!pl.k_mapscale || !pl.k_mapcenter))
+            return fail(OMMX_E_ARG, "kv_append: kv_outlier_map needs k_mapscale and k_mapcenter");
+        if (((uintptr_t)pl.k_base & 7) || ((uintptr_t)pl.v_main & 7) || ((uintptr_t)pl.k_obmp & 3))
+            return fail(OMMX_E_ARG, "kv_append: k_base/v_main must be 8-byte and k_obmp 4-byte aligned");
+    }
+    if ((a->k_tail != nullptr) != (a->v_tail != nullptr)) return fail(OMMX_E_ARG, "kv_append: k_tail and v_tail go together");
+    if (a->k_tail && (a->max_tail <= 0 || (pl.n_kv_heads * pl.head_dim) % 8 != 0 ||
+                      ((uintptr_t)a->k_tail & 15) || ((uintptr_t)a->v_tail & 15) ||
+                      ((uintptr_t)pool.k_hist & 15) || ((uintptr_t)pool.v_hist & 15)))
+        return fail(OMMX_E_ARG, "kv_append: residual buffers need max_tail > 0 and 16-byte alignment");
+    return launch_append(a, (cudaStream_t)stream);
 }

@@ -27,7 +27,8 @@ def test_abi_version_matches_header():
 
 def test_struct_layouts_match_header_field_order():
     for struct, cls in (("ommx_kv_planes", _lib.KVPlanes), ("ommx_pack_args", _lib.PackArgs),
-                        ("ommx_decode_args", _lib.DecodeArgs)):
+                        ("ommx_decode_args", _lib.DecodeArgs), ("ommx_kv_pool", _lib.KVPool),
+                        ("ommx_kv_append_args", _lib.KVAppendArgs)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), HEADER, re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         names = []
@@ -53,6 +54,12 @@ def test_host_side_rejections():
     d.q_dtype = _lib.OMMX_DT_BF16
     d.planes.head_dim = 64
     assert lib.ommx_b200_decode(C.byref(d), None) == -2 and "head_dim" in _lib.last_error()
+    ap = _lib.KVAppendArgs()
+    assert lib.ommx_b200_kv_append_decode(C.byref(ap), None) == -1 and "batch" in _lib.last_error()
+    ap.batch = 2
+    ap.pool.k_hist = ap.pool.v_hist = ap.pool.seq_len = ap.pool.req_to_token = ap.pool.req_to_group = 256
+    ap.pool.num_seqs, ap.pool.sink_tokens, ap.pool.recent_window, ap.pool.ring_cap = 2, 8, 32, 60
+    assert lib.ommx_b200_kv_append_decode(C.byref(ap), None) == -1 and "ring_cap" in _lib.last_error()
     with pytest.raises(NotImplementedError):
         _lib.check(-2, "x")
     with pytest.raises(ValueError):
