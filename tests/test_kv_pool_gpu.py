@@ -128,6 +128,68 @@ def test_store_feeds_decode_without_host_state():
         check_fp32(o[r], want, ctx=f"req {r}")
 
 
+def test_decode_step_is_graph_capturable():
+    """One CUDA graph holds store + decode of a step; replaying it walks the sequences forward,
+    including the steps on which a group completes, with no host work between replays."""
+    from open_ommx_serve_b200 import ommx_paged_decode_attention_canonical
+    from open_ommx_serve_b200.attention.paged_decode import _auto_num_kv_splits
+    H, Hq, lens, B = 2, 8, [70, 200], 2
+    pool = _pool(B, 512, H)
+    eager = _pool(B, 512, H)
+    for r, T in enumerate(lens):
+        K, V = gaussian_kv(300 + r, T, H, 128)
+        for pl in (pool, eager):
+            pl.append_block(r, K.cuda().bfloat16(), V.cuda().bfloat16())
+    k_in = torch.zeros(B, H, 128, dtype=torch.bfloat16, device="cuda")
+    v_in = torch.zeros_like(k_in)
+    q_in = torch.zeros(B, Hq, 128, dtype=torch.bfloat16, device="cuda")
+    o = torch.zeros(B, Hq, 128, device="cuda")
+    lse = torch.zeros(B, Hq, device="cuda")
+    max_packed = pool.window.packed_len(512)
+    splits = _auto_num_kv_splits(max_packed, B, device=torch.device("cuda"), kv_heads=H)
+    ws = torch.empty(B, Hq, splits + 1, 129, device="cuda")
+
+    def step(pl, out_o, out_lse):
+        pl.append_decode_device(k_in, v_in, B)
+        d = pl.decode_inputs_device(B, max_packed)
+        ommx_paged_decode_attention_canonical(
+            q_in, d["k_base"], d["k_scale"], d["k_zp"], None, d["k_oval"], d["v_main"], d["v_scale"], d["v_zp"],
+            d["k_tail"], d["v_tail"], d["b_tail_len"], out_o, out_lse, d["req_to_token"], d["req_to_group"],
+            d["b_seq_len"], sm_scale=128 ** -0.5, page_size=d["page_size"], k_outliers_per_vector=6,
+            bitmap_read=True, k_obmp=d["k_obmp"], k_fp4_mapscale=d["k_fp4_mapscale"],
+            k_fp4_mapcenter=d["k_fp4_mapcenter"], kv_outlier_map=True, kv_int8_scale=True, num_kv_splits=splits,
+            max_seq_len=d["max_seq_len"], max_tail_len=d["max_tail_len"], attn_logits=ws)
+
+    g = torch.Generator().manual_seed(3)
+    rows = [(torch.randn(B, H, 128, generator=g).bfloat16(), torch.randn(B, H, 128, generator=g).bfloat16(),
+             torch.randn(B, Hq, 128, generator=g).bfloat16()) for _ in range(41)]
+    k_in.copy_(rows[0][0]); v_in.copy_(rows[0][1]); q_in.copy_(rows[0][2])
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        step(pool, o, lse)                                    # warm-up outside capture (step 0)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    k_in.copy_(rows[1][0]); v_in.copy_(rows[1][1]); q_in.copy_(rows[1][2])
+    with torch.cuda.graph(graph):
+        step(pool, o, lse)                                    # capture launches nothing: step 1 runs at first replay
+    o_e = torch.zeros_like(o)
+    lse_e = torch.zeros_like(lse)
+    k_keep, v_keep, q_keep = k_in.clone(), v_in.clone(), q_in.clone()
+    k_in.copy_(rows[0][0]); v_in.copy_(rows[0][1]); q_in.copy_(rows[0][2])
+    step(eager, o_e, lse_e)
+    for i in range(1, 41):
+        k_in.copy_(rows[i][0]); v_in.copy_(rows[i][1]); q_in.copy_(rows[i][2])
+        graph.replay()
+        step(eager, o_e, lse_e)
+        assert torch.equal(o, o_e) and torch.equal(lse, lse_e), f"step {i}"
+    assert pool.seq_lens() == eager.seq_lens() == [lens[0] + 41, lens[1] + 41]
+    for name, t in pool.planes.items():
+        if t is not None:
+            assert torch.equal(t, eager.planes[name]), name
+    del k_keep, v_keep, q_keep
+
+
 def test_refusals():
     from open_ommx_serve_b200.attention.kv_pool import MultiSeqKVPool
     with pytest.raises(NotImplementedError):
