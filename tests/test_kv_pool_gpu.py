@@ -190,6 +190,28 @@ def test_decode_step_is_graph_capturable():
     del k_keep, v_keep, q_keep
 
 
+def test_single_request_store_mirrors_the_pool():
+    from open_ommx_serve_b200.attention.kv_store import CanonicalKVStore
+    from open_ommx_serve_b200.attention.kv_window import WindowSpec
+    H = 2
+    st = CanonicalKVStore(128, H, 512, window=WindowSpec(SINK, RECENT, 32, 16))
+    K, V = gaussian_kv(77, 90, H, 128)
+    st.append_block(K.cuda().bfloat16(), V.cuda().bfloat16())
+    g = torch.Generator().manual_seed(1)
+    for _ in range(50):
+        kn, vn = torch.randn(H, 128, generator=g).bfloat16(), torch.randn(H, 128, generator=g).bfloat16()
+        st.append(kn.cuda(), vn.cuda())
+        K, V = torch.cat([K, kn[None].float()]), torch.cat([V, vn[None].float()])
+    assert st.seq_len == 140
+    _check_against_history(st.pool, [K], [V])
+    d = st.decode_inputs()
+    assert int(d["b_seq_len"].item()) == 96 and d["planes"]["req_to_group"].shape[0] == 1
+    with pytest.raises(RuntimeError):
+        st.append_block(K.cuda().bfloat16(), V.cuda().bfloat16())
+    st.reset_inplace()
+    assert st.seq_len == 0
+
+
 def test_refusals():
     from open_ommx_serve_b200.attention.kv_pool import MultiSeqKVPool
     with pytest.raises(NotImplementedError):
