@@ -72,37 +72,6 @@ __device__ __forceinline__ float bf16_round_f32(float x) {
 __device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
     return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
 }
-// pack two floats into a bf16x2 register (lo = a, hi = b), round to nearest even
-__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
-    return r;
-}
-__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t hsub2_bf16(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t orv) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(x), "r"(mask), "r"(orv));  // (x & mask) | orv
-    return r;
-}
-__device__ __forceinline__ uint32_t lop3_and_xor(uint32_t x, uint32_t mask, uint32_t xv) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(x), "r"(mask), "r"(xv));   // (x & mask) ^ xv
-    return r;
-}
 __device__ __forceinline__ void or_status(int32_t *status, int bits) {
     if (status != nullptr) atomicOr(status, bits);
 }
