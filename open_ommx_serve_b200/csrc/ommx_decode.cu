@@ -694,50 +694,37 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 break;
             }
             OMMX_TR(8 * it + 3);
-            uint32_t F[16];
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const uint4 t = reinterpret_cast<const uint4 *>(p_kf)[v];
-                F[4 * v] = t.x; F[4 * v + 1] = t.y; F[4 * v + 2] = t.z; F[4 * v + 3] = t.w;
-            }
             float Sc[2][4], Sd[2][4], Sz[4];
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) { Sc[mt][0] = Sc[mt][1] = Sc[mt][2] = Sc[mt][3] = 0.f; Sd[mt][0] = Sd[mt][1] = Sd[mt][2] = Sd[mt][3] = 0.f; }
             Sz[0] = Sz[1] = Sz[2] = Sz[3] = 0.f;
             // Five accumulators take turns, so that neighbours in the instruction stream never wait on each
-            // other, and the tile fragments of k-step q+1 are fetched before the MMAs of step q are issued
+            // other, and every tile fragment is fetched two or three MMAs before the MMA that takes it
             // (the asm statements keep their order, so the order written here is the order issued).
-            uint32_t dfr[2][2][4], zfr[2][2];                    // [parity of q][m-tile][regs]
-            if (has_delta) {
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-                    ldsm_x4(a_delta + 16 * mt * DT_STRIDE, dfr[0][mt][0], dfr[0][mt][1], dfr[0][mt][2], dfr[0][mt][3]);
-            }
-            ldsm_x2(a_zp, zfr[0][0], zfr[0][1]);
+            uint32_t d0f[4], d1f[4], zf[2];                      // delta fragments of m-tile 0 / 1, zero-point fragment
+            if (has_delta) ldsm_x4(a_delta, d0f[0], d0f[1], d0f[2], d0f[3]);
+            ldsm_x2(a_zp, zf[0], zf[1]);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                const int cur = q & 1, nxt = cur ^ 1;
-                if (q < 7) {
-                    if (has_delta) {
-#pragma unroll
-                        for (int mt = 0; mt < 2; ++mt)
-                            ldsm_x4(a_delta + 16 * mt * DT_STRIDE + 32 * (q + 1), dfr[nxt][mt][0], dfr[nxt][mt][1], dfr[nxt][mt][2], dfr[nxt][mt][3]);
-                    }
-                    ldsm_x2(a_zp + 32 * (q + 1), zfr[nxt][0], zfr[nxt][1]);
-                }
                 const int wi = q >> 2, i0 = 2 * (q & 3);
-                const uint32_t b0 = hmul2_f16(QS[2 * q], F[2 * q]), b1 = hmul2_f16(QS[2 * q + 1], F[2 * q + 1]);
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    const uint32_t wlo = wi ? kw[2 * mt].y : kw[2 * mt].x, whi = wi ? kw[2 * mt + 1].y : kw[2 * mt + 1].x;
-                    mma_f16(Sc[mt], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
+                const uint2 fq = reinterpret_cast<const uint2 *>(p_kf)[q];      // this k-step's two factor pairs
+                const uint32_t b0 = hmul2_f16(QS[2 * q], fq.x), b1 = hmul2_f16(QS[2 * q + 1], fq.y);
+                if (has_delta) ldsm_x4(a_delta + 16 * DT_STRIDE + 32 * q, d1f[0], d1f[1], d1f[2], d1f[3]);
+                {
+                    const uint32_t wlo = wi ? kw[0].y : kw[0].x, whi = wi ? kw[1].y : kw[1].x;
+                    mma_f16(Sc[0], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
                 }
-                if (has_delta) {
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt)
-                        mma_f16(Sd[mt], dfr[cur][mt][0], dfr[cur][mt][1], dfr[cur][mt][2], dfr[cur][mt][3], QD[2 * q], QD[2 * q + 1]);
+                if (has_delta) mma_f16(Sd[0], d0f[0], d0f[1], d0f[2], d0f[3], QD[2 * q], QD[2 * q + 1]);
+                mma_f16(Sz, zf[0], 0u, zf[1], 0u, QD[2 * q], QD[2 * q + 1]);
+                if (q < 7) {
+                    if (has_delta) ldsm_x4(a_delta + 32 * (q + 1), d0f[0], d0f[1], d0f[2], d0f[3]);
+                    ldsm_x2(a_zp + 32 * (q + 1), zf[0], zf[1]);
                 }
-                mma_f16(Sz, zfr[cur][0], 0u, zfr[cur][1], 0u, QD[2 * q], QD[2 * q + 1]);
+                {
+                    const uint32_t wlo = wi ? kw[2].y : kw[2].x, whi = wi ? kw[3].y : kw[3].x;
+                    mma_f16(Sc[1], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
+                }
+                if (has_delta) mma_f16(Sd[1], d1f[0], d1f[1], d1f[2], d1f[3], QD[2 * q], QD[2 * q + 1]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot((int)consumed, NS)));   // the next tile may be built
