@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generate the golden fixtures in this folder by running the REFERENCE project's own CPU code.
 
-    python tests/golden/make_golden.py [/path/to/open_ommx_serve]      (default /root/reference)
+    python tests/golden/make_golden.py /path/to/open_ommx_serve
 
 It imports, unmodified, from the reference checkout:
   * ommx_gpu_serve.attention.pack.ommx_pack_kv_canonical_block / dequant_kv_canonical
@@ -22,7 +22,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/open_ommx_serve")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 HERE = os.path.dirname(os.path.abspath(__file__))
 
