@@ -456,6 +456,73 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_batch32(args, local_rank):
+    """Secondary workload (not the headline line): batch 32, ragged contexts 1K..32K, split partition 512,
+    every step stores one new token per sequence through the device-resident pool and decodes, per layer."""
+    import torch
+    from open_ommx_serve_b200 import _lib, ommx_paged_decode_attention_canonical
+    from open_ommx_serve_b200.attention.kv_pool import MultiSeqKVPool
+    from open_ommx_serve_b200.attention.kv_window import WindowSpec
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    B, max_len, part = 32, 32768 + 256, 512
+    lens = torch.randint(1024, 32769, (B,), generator=torch.Generator().manual_seed(42)).tolist()
+    win = WindowSpec(8, 32, 32, PAGE)
+    pools = []
+    cg = torch.Generator(device=device)
+    for layer in range(LAYERS):
+        pool = MultiSeqKVPool(D, HKV, B, max_len, outliers_per_vector=K_OUT, window=win, device=device)
+        cg.manual_seed(1000 + layer)
+        for r, T in enumerate(lens):
+            K = torch.randn(T, HKV, D, generator=cg, device=device)
+            V = torch.randn(T, HKV, D, generator=cg, device=device)
+            K[:, :, :4] *= 12.0
+            pool.append_block(r, K.bfloat16(), V.bfloat16())
+        pools.append(pool)
+    max_packed = win.packed_len(max_len)
+    splits = (max_packed + part - 1) // part
+    ws = torch.empty(B, HQ, splits + 1, D + 1, dtype=torch.float32, device=device)
+    q = torch.randn(LAYERS, B, HQ, D, generator=cg, device=device).bfloat16()
+    kn = torch.randn(LAYERS, B, HKV, D, generator=cg, device=device).bfloat16()
+    vn = torch.randn(LAYERS, B, HKV, D, generator=cg, device=device).bfloat16()
+    o = torch.zeros(LAYERS, B, HQ, D, dtype=torch.float32, device=device)
+    lse = torch.zeros(LAYERS, B, HQ, dtype=torch.float32, device=device)
+
+    def step():
+        for i, pool in enumerate(pools):
+            pool.append_decode_device(kn[i], vn[i], B)
+            d = pool.decode_inputs_device(B, max_packed)
+            ommx_paged_decode_attention_canonical(
+                q[i], d["k_base"], d["k_scale"], d["k_zp"], None, d["k_oval"], d["v_main"], d["v_scale"], d["v_zp"],
+                d["k_tail"], d["v_tail"], d["b_tail_len"], o[i], lse[i], d["req_to_token"], d["req_to_group"],
+                d["b_seq_len"], sm_scale=D ** -0.5, page_size=PAGE, k_outliers_per_vector=K_OUT, bitmap_read=True,
+                k_obmp=d["k_obmp"], k_fp4_mapscale=d["k_fp4_mapscale"], k_fp4_mapcenter=d["k_fp4_mapcenter"],
+                kv_outlier_map=True, kv_int8_scale=True, num_kv_splits=splits, max_seq_len=max_packed,
+                max_tail_len=d["max_tail_len"], attn_logits=ws)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    lib = _lib.load()
+    lib.ommx_b200_reset_launch_count()
+    sampler = ClockSampler(local_rank)
+    with sampler:
+        times = timed_graph(step, args.steps, args.warmup, flush, torch)
+    ms = sum(times) / len(times)
+    packed = sum(win.packed_len(T + args.warmup + args.steps // 2) for T in lens)
+    bytes_layer = packed * HKV * 132 + sum(T - win.packed_len(T) for T in lens) * HKV * D * 4
+    status = max(int(p.status.item()) for p in pools)
+    print(json.dumps({
+        "metric": "ommx_store_plus_decode_us_per_layer", "value": ms * 1e3 / LAYERS, "unit": "us", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"llama3.1-8b geometry, {LAYERS} layers, batch 32, contexts uniform 1K..32K (seed 42), "
+                               f"split partition 512 ({splits} splits), one new token stored per sequence per step "
+                               "(device-resident pool), then decode; CUDA-graph replay, L2 flushed between steps",
+                   "sum_ctx": sum(lens), "splits": splits},
+        "hbm_gbs": bytes_layer / (ms / LAYERS) / 1e6, "tokens_per_s": B / (ms * 1e-3),
+        "gpu_launches": int(lib.ommx_b200_launch_count()), "device_status": status, "clocks": sampler.summary()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -467,6 +534,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers in the stack (32 = the benchmark)")
     ap.add_argument("--profile", action="store_true", help="eager launches only, for ncu (use a small --layers)")
+    ap.add_argument("--workload", default="b1", choices=("b1", "batch32"),
+                    help="b1 = the headline line; batch32 = ragged batch with the per-step store (own JSON line)")
     args = ap.parse_args()
     globals()["LAYERS"] = args.layers
     rank = int(os.environ.get("RANK", "0"))
@@ -478,6 +547,10 @@ def main():
         run_reference(args, rank, world)
         return
     args.warmup = max(3, args.warmup)
+    if args.workload == "batch32":
+        if world == 1:
+            run_batch32(args, local_rank)
+        return
     run_ours(args, rank, world, local_rank)
 
 

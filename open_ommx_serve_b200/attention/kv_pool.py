@@ -90,6 +90,23 @@ class MultiSeqKVPool:
         self.b_seq = torch.zeros(self.num_seqs, dtype=torch.int32, device=dev)
         self.b_tail = torch.zeros(self.num_seqs, dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._sel = None                     # batch row -> request slot (None: row i is slot i)
+        self._r2t_sel = self._r2g_sel = None
+
+    def select_slots(self, slots=None) -> None:
+        """Choose which request slots the batch rows of the following calls stand for (``None``: row i =
+        slot i).  A host-side event (the batch changed), done outside the decode loop: the tables of the
+        chosen slots are gathered once here so that the per-step calls allocate nothing."""
+        if slots is None:
+            self._sel = self._r2t_sel = self._r2g_sel = None
+            return
+        idx = [int(x) for x in slots]
+        if len(set(idx)) != len(idx) or any(not 0 <= x < self.num_seqs for x in idx):
+            raise ValueError(f"slots must be distinct and inside [0, {self.num_seqs}); got {idx}")
+        self._sel = torch.tensor(idx, dtype=torch.int32, device=self.device)
+        sel = self._sel.long()
+        self._r2t_sel = self._req_to_token.index_select(0, sel).contiguous()
+        self._r2g_sel = self._req_to_group.index_select(0, sel).contiguous()
 
     # ── helpers ──────────────────────────────────────────────────────────────
     def _ring_row(self, pos: torch.Tensor) -> torch.Tensor:
@@ -108,7 +125,9 @@ class MultiSeqKVPool:
         if K is not None:
             a.k_new, a.v_new = K.data_ptr(), V.data_ptr()
             a.new_stride_b, a.new_stride_h = int(K.stride(0)), int(K.stride(1))
-        a.slots = None
+        a.slots = None if self._sel is None else self._sel.data_ptr()
+        if self._sel is not None and int(B) != int(self._sel.numel()):
+            raise ValueError(f"batch {B} does not match the {int(self._sel.numel())} selected slots")
         a.batch, a.advance = int(B), 1 if advance else 0
         a.outlier_select, a.use_pow2 = 1, 1
         a.k_tail, a.v_tail, a.max_tail = self.k_tail.data_ptr(), self.v_tail.data_ptr(), self.max_tail_len
@@ -152,7 +171,8 @@ class MultiSeqKVPool:
         return target
 
     def append_decode_device(self, K: torch.Tensor, V: torch.Tensor, B: int) -> None:
-        """One decode step for rows ``0..B-1`` (row i = request slot i): ``K``/``V`` are ``[B, H, D]`` bf16.
+        """One decode step for rows ``0..B-1`` (row i = request slot i, or the slots chosen with
+        ``select_slots``): ``K``/``V`` are ``[B, H, D]`` bf16.
 
         Ring write, quantize + pack of completed groups, length advance and the decode inputs of the
         step, on the device, without a host loop or synchronisation (CUDA-graph capturable)."""
@@ -174,7 +194,8 @@ class MultiSeqKVPool:
         return dict(k_base=p["k_base"], k_scale=p["k_scale"], k_zp=p["k_zp"], k_oidx=None, k_oval=p["k_oval"],
                     v_main=p["v_main"], v_scale=p["v_scale"], v_zp=p["v_zp"],
                     k_tail=self.k_tail[:B], v_tail=self.v_tail[:B], b_tail_len=self.b_tail[:B],
-                    req_to_token=self._req_to_token[:B], req_to_group=self._req_to_group[:B], b_seq_len=self.b_seq[:B],
+                    req_to_token=self._req_to_token[:B] if self._sel is None else self._r2t_sel,
+                    req_to_group=self._req_to_group[:B] if self._sel is None else self._r2g_sel, b_seq_len=self.b_seq[:B],
                     k_obmp=p["k_obmp"], k_fp4_mapscale=p["k_fp4_mapscale"], k_fp4_mapcenter=p["k_fp4_mapcenter"],
                     max_seq_len=int(max_seq_len if max_seq_len is not None else self.window.packed_len(self.max_seq_len)),
                     max_tail_len=self.max_tail_len, page_size=self.ps, k_outliers_per_vector=self.k,

@@ -190,6 +190,41 @@ def test_decode_step_is_graph_capturable():
     del k_keep, v_keep, q_keep
 
 
+def test_selected_slots_remap_batch_rows():
+    """Batch rows can stand for any distinct request slots; the others are left untouched."""
+    H = 2
+    pool = _pool(4, 512, H)
+    hist = {}
+    for r, T in enumerate([50, 120, 75, 200]):
+        K, V = gaussian_kv(400 + r, T, H, 128)
+        pool.append_block(r, K.cuda().bfloat16(), V.cuda().bfloat16())
+        hist[r] = [K, V]
+    pool.select_slots([3, 1])
+    g = torch.Generator().manual_seed(2)
+    for _ in range(40):
+        Kn, Vn = torch.randn(2, H, 128, generator=g).bfloat16(), torch.randn(2, H, 128, generator=g).bfloat16()
+        pool.append_decode_device(Kn.cuda(), Vn.cuda(), 2)
+        for row, r in enumerate((3, 1)):
+            hist[r][0] = torch.cat([hist[r][0], Kn[row:row + 1].float()])
+            hist[r][1] = torch.cat([hist[r][1], Vn[row:row + 1].float()])
+    assert pool.seq_lens() == [50, 160, 75, 240]
+    d = pool.decode_inputs_device(2)
+    assert d["req_to_group"][0, 0].item() == 3 * pool.G_per_seq and d["req_to_group"][1, 0].item() == pool.G_per_seq
+    for row, r in enumerate((3, 1)):
+        T = hist[r][0].shape[0]
+        boundary = O.packed_boundary(T, SINK, RECENT)
+        assert int(pool.b_seq[row].item()) == boundary - SINK
+        want = O.pack_kv(hist[r][0][SINK:boundary].numpy(), hist[r][1][SINK:boundary].numpy(), outliers_per_vector=6)
+        assert_planes_equal(_seq_planes(pool, r, (boundary - SINK) // 32), want, ctx=f"slot {r}: ")
+        tail_idx = list(range(SINK)) + list(range(boundary, T))
+        assert torch.equal(pool.k_tail[row, :len(tail_idx)].cpu(), hist[r][0][tail_idx].bfloat16())
+    with pytest.raises(ValueError):
+        pool.select_slots([1, 1])
+    with pytest.raises(ValueError):
+        pool.append_decode_device(torch.zeros(3, H, 128, dtype=torch.bfloat16, device="cuda"),
+                                  torch.zeros(3, H, 128, dtype=torch.bfloat16, device="cuda"), 3)
+
+
 def test_single_request_store_mirrors_the_pool():
     from open_ommx_serve_b200.attention.kv_store import CanonicalKVStore
     from open_ommx_serve_b200.attention.kv_window import WindowSpec
