@@ -31,6 +31,13 @@ template <typename T> __device__ __forceinline__ float bits16_as_f32(uint32_t b)
 template <> __device__ __forceinline__ float bits16_as_f32<__nv_bfloat16>(uint32_t b) { return __uint_as_float(b << 16); }
 template <> __device__ __forceinline__ float bits16_as_f32<__half>(uint32_t b) { return __half2float(__ushort_as_half((unsigned short)b)); }
 
+// clamp(rint(x), 0, 3) as an integer without the conversion pipe: rint is monotone, so the clamp may come
+// first; adding 1.5 * 2^23 then rounds to nearest-even into the low mantissa bits (exact for |x| <= 3).
+__device__ __forceinline__ uint32_t code_0_3(float x) {
+    const float c = fminf(fmaxf(x, 0.f), 3.f);                  // NaN -> 0
+    return __float_as_uint(__fadd_rn(c, 12582912.f)) - 0x4B400000u;
+}
+
 // Monotone map fp32 -> uint32 (larger float <=> larger key); -0.0 is folded onto +0.0 first so
 // that equal values tie exactly as they do under the reference's float comparisons.
 __device__ __forceinline__ uint32_t f32_key(float x) {
@@ -327,10 +334,9 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_lane_kernel(PackKParam
 #pragma unroll
     for (int t = 0; t < 32; ++t) {
         const float d = __fsub_rn(x[t], zp);
-        float qv = rintf(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
-        qv = fminf(fmaxf(qv, 0.f), 3.f);
-        if (t < 16) cw0 |= (uint32_t)(int)qv << (2 * t);
-        else cw1 |= (uint32_t)(int)qv << (2 * (t - 16));
+        const uint32_t c = code_0_3(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
+        if (t < 16) cw0 = c * (1u << (2 * t)) + cw0;
+        else cw1 = c * (1u << (2 * (t - 16))) + cw1;
     }
     // ---- outlier values ----
     float ms = 0.f, mc = 0.f;
@@ -492,10 +498,8 @@ __global__ void __launch_bounds__(128) pack_v_kernel(PackVParams p) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         const float d = __fsub_rn(x[i], zp);
-        float qv = rintf(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
-        qv = fminf(fmaxf(qv, 0.f), 3.f);
-        uint32_t c = (uint32_t)(int)qv;
-        if (i < 16) w0 |= c << (2 * i); else w1 |= c << (2 * (i - 16));
+        const uint32_t c = code_0_3(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
+        if (i < 16) w0 = c * (1u << (2 * i)) + w0; else w1 = c * (1u << (2 * (i - 16))) + w1;
     }
     if (bad) or_status(p.status, OMMX_ST_NONFINITE);
     int page = t / p.page_size;
