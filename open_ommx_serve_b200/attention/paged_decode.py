@@ -207,8 +207,10 @@ def ommx_paged_decode_attention_canonical(
     if bitmap_read and k > 0 and k_obmp is None:
         raise ValueError("bitmap_read=True requires the k_obmp flat-bitmask plane (pack with "
                          "ommx_pack_kv_canonical_block(..., outlier_repr='bitmap')).")
-    if bitmap_read and k > 8:
-        raise ValueError(f"bitmap_read holds the k_oval stream in one 32-bit word, i.e. k <= 8; got k={k}.")
+    # The reference's bitmask read stops at k = 8 (its value stream must fit one 32-bit word,
+    # paged_decode.py:3055-3058); this kernel walks a 64-bit stream, so the 32-bit bitmask serves k <= 16.
+    if bitmap_read and k > 16:
+        raise ValueError(f"bitmap_read holds the k_oval stream in two 32-bit words, i.e. k <= 16; got k={k}.")
     if k > 0 and not bitmap_read:
         raise NotImplementedError(
             "this build reads the flat-bitmask outlier index only: pass bitmap_read=True with k_obmp "

@@ -250,6 +250,11 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     const int split = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     OMMX_TR(250);
+    // the first tensor-map copy otherwise pays for fetching its descriptor
+    if (threadIdx.x == S1_THREADS - 32 && p.swz != 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_v)) : "memory");
+    }
 
     // ---- split range (same rounding as the reference, paged_decode.py:1428-1432) ----
     const int seq = p.b_seq_len[b];
@@ -467,7 +472,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
                 uint32_t ms2 = 0, mc2 = 0;
                 uint2 bm2 = make_uint2(0, 0);
-                uint32_t st[2] = {0, 0};
+                uint32_t st[2] = {0, 0}, sth[2] = {0, 0};            // nibble stream of each channel: outliers 0..7, 8..15
                 if (splice) {
                     if (p.use_map) {
                         ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
@@ -487,6 +492,18 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     } else if (nb == 2) {
                         const uint32_t w = *reinterpret_cast<const uint32_t *>(ov);
                         st[0] = w & 0xFFFFu; st[1] = w >> 16;
+                    } else if (nb > 4) {
+                        // 9..16 outliers: the two channels' streams are 2*nb bytes back to back; read them as
+                        // 16-bit pieces into a 128-bit little-endian window and cut it at bit 8*nb
+                        uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (i < nb) w[i >> 1] |= (uint32_t) reinterpret_cast<const uint16_t *>(ov)[i] << (16 * (i & 1));
+                        const int sh = 8 * (nb - 4);                     // 8..32 bits of a stream lie above its first word
+                        const uint32_t hmask = sh == 32 ? 0xFFFFFFFFu : ((1u << sh) - 1u);
+                        st[0] = w[0]; sth[0] = w[1] & hmask;
+                        if (sh == 32) { st[1] = w[2]; sth[1] = w[3]; }
+                        else { st[1] = __funnelshift_r(w[1], w[2], sh); sth[1] = __funnelshift_r(w[2], w[3], sh) & hmask; }
                     } else {
                         const uint32_t w = *reinterpret_cast<const uint16_t *>(ov);
                         st[0] = w & 0xFFu; st[1] = w >> 8;
@@ -523,7 +540,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                             Bc = mc - zp;
                         }
                         uint32_t bits = bmv[c];
-                        const uint32_t stream = st[c];
+                        const uint32_t stream = st[c], stream_hi = sth[c];
+                        (void)stream_hi;
                         const int fsh = 2 * ((d0 & 3) + c);          // bit position of the channel's code in its byte
                         uint8_t *col = tile + 2 * d0 + 2 * c;
                         if (KOUT > 0) {
@@ -547,7 +565,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                             while (bits) {
                                 const int pz = 31 - __clz(bits);
                                 bits ^= 1u << pz;
-                                const uint32_t nib = (r < 8) ? ((stream >> (4 * r)) & 0xFu) : 0u;
+                                const uint32_t nib = ((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu;
                                 --r;
                                 const uint32_t row = (uint32_t)pz * (uint32_t)TS;
                                 const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
@@ -1125,8 +1143,8 @@ static int validate_decode(const ommx_decode_args *a) {
         return fail(OMMX_E_UNSUPPORTED, "decode: page_size=%d must be 8, 16 or 32", pl.page_size);
     if (pl.scale_kind != OMMX_SCALE_INT8_EXP)
         return fail(OMMX_E_UNSUPPORTED, "decode: only int8 power-of-two scale planes are served (pack with use_pow2)");
-    if (pl.outliers_per_vector < 0 || pl.outliers_per_vector > 8)
-        return fail(OMMX_E_UNSUPPORTED, "decode: outliers_per_vector=%d outside [0,8]", pl.outliers_per_vector);
+    if (pl.outliers_per_vector < 0 || pl.outliers_per_vector > 16)
+        return fail(OMMX_E_UNSUPPORTED, "decode: outliers_per_vector=%d outside [0,16]", pl.outliers_per_vector);
     if (a->packed_start_offset != 0) return fail(OMMX_E_UNSUPPORTED, "decode: packed_start_offset must be 0");
     if (a->seg_group_base < 0) return fail(OMMX_E_ARG, "decode: seg_group_base=%d", a->seg_group_base);
     if (a->num_kv_splits < 1) return fail(OMMX_E_ARG, "decode: num_kv_splits=%d", a->num_kv_splits);

@@ -1,7 +1,9 @@
 #!/usr/bin/env python3
 """Generate the golden fixtures in this folder by running the REFERENCE project's own CPU code.
 
-    python tests/golden/make_golden.py /path/to/open_ommx_serve
+    python tests/golden/make_golden.py /path/to/open_ommx_serve [case ...]
+
+(with case names given, only those files are rewritten)
 
 It imports, unmodified, from the reference checkout:
   * ommx_gpu_serve.attention.pack.ommx_pack_kv_canonical_block / dequant_kv_canonical
@@ -77,6 +79,8 @@ def pack_case(name, K, V, *, k=6, select="signed", use_pow2=True, omap=True, pag
 
 
 def _save(name, arrays):
+    if len(sys.argv) > 2 and name not in sys.argv[2:]:
+        return
     path = os.path.join(HERE, name + ".npz")
     np.savez_compressed(path, **arrays)
     h = hashlib.sha256(open(path, "rb").read()).hexdigest()[:16]
@@ -88,6 +92,8 @@ def main():
     pack_case("pack_default", *gaussian_kv(42, 64, 2, 128))
     pack_case("pack_fp32_inputs", *gaussian_kv(1, 64, 2, 128, bf16=False))
     for k in (0, 2, 4, 8):
+        pack_case(f"pack_k{k}", *gaussian_kv(3, 32, 1, 128), k=k)
+    for k in (9, 12, 16):       # value streams longer than one 32-bit word
         pack_case(f"pack_k{k}", *gaussian_kv(3, 32, 1, 128), k=k)
     pack_case("pack_abs_k3", *gaussian_kv(4, 32, 2, 128), k=3, select="abs")
     pack_case("pack_shared_map", *gaussian_kv(5, 32, 2, 128), omap=False)

@@ -80,7 +80,7 @@ def test_decode_head_geometries(H, Hq):
     _run_and_check(Case([1500], H=H, Hq=Hq, seed=H * 100 + Hq))
 
 
-@pytest.mark.parametrize("k", [0, 2, 4, 6, 8])
+@pytest.mark.parametrize("k", [0, 2, 3, 4, 6, 8, 9, 10, 12, 16])
 @pytest.mark.parametrize("mag", [4.0, 30.0])
 def test_decode_outlier_sweep(k, mag):
     _run_and_check(Case([2048], seed=k + 1, k=k, mag=mag), lse_atol=2e-2 if mag < 20 else 0.15,
