@@ -278,11 +278,12 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     uint8_t *s_tiles = s_stage + NS * p.stage_bytes;                    // NCW * DT_BYTES
     int32_t *s_tab = reinterpret_cast<int32_t *>(s_tiles + NCW * DT_BYTES);   // page ids, then group slots
     float *s_lut = reinterpret_cast<float *>(s_tab + MAX_SPLIT_PAGES + MAX_SPLIT_GROUPS);
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[], empty[], tile_full[NCW], tile_empty[NCW][]
-    int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * MAX_STAGES + (1 + MAX_STAGES) * NCW);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(s_lut + 16);         // full[], empty[], tile_full[NCW], tile_empty[NCW][], tile_rows[NCW]
+    int32_t *s_abort = reinterpret_cast<int32_t *>(s_bar + 2 * MAX_STAGES + (2 + MAX_STAGES) * NCW);
     CopyDesc *s_desc = reinterpret_cast<CopyDesc *>(s_abort + 4);
     const uint32_t bar_full = smem_u32(s_bar), bar_empty = smem_u32(s_bar + MAX_STAGES);
     const uint32_t bar_tfull = smem_u32(s_bar + 2 * MAX_STAGES), bar_tempty = smem_u32(s_bar + 2 * MAX_STAGES + NCW);
+    const uint32_t bar_trows = smem_u32(s_bar + 2 * MAX_STAGES + (1 + MAX_STAGES) * NCW);
 
     // ---- prologue: LUT, barriers, copy descriptors and the split's page / slot tables, spread over the
     //      whole CTA so that the producer can issue the first stage right after the barrier ----
@@ -298,7 +299,8 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             mbar_init(bar_empty + 8 * s, 3 * NCW);                  // 8 MMA warps + 16 tile halves
         }
         for (int u = 0; u < NCW; ++u) {
-            mbar_init(bar_tfull + 8 * u, 2);                        // the two halves of a tile
+            mbar_init(bar_tfull + 8 * u, 2);                        // the two halves of a tile: outlier deltas scattered
+            mbar_init(bar_trows + 8 * u, 2);                        // the two halves of a tile: factor / zero-point rows written
             for (int k2 = 0; k2 < MAX_STAGES; ++k2) mbar_init(bar_tempty + 8 * (MAX_STAGES * u + k2), 1);
         }
         *s_abort = 0;
@@ -435,6 +437,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         for (int n = dw; n < n_iters * NCW * 2; n += NDW) {
             const int it = n / (2 * NCW), unit = (n >> 1) % NCW, hf = n & 1;
             const int trk = 8 * ((n - dw) / NDW);
+            (void)trk;
             OMMX_TR(trk);
             const int h = unit & (H - 1), gsel = unit >> p.hshift;       // H is a power of two
             uint8_t *tile = s_tiles + unit * DT_BYTES;
@@ -461,120 +464,21 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 OMMX_TR(trk + 2);
                 bool clamped_any = false;
                 const bool splice = k_out > 0 && !no_outlier;
-                if (splice) {
-                    // clear this half's columns of token rows 0..31 (128 bytes per row)
-#pragma unroll
-                    for (int k2 = 0; k2 < 8; ++k2)
-                        *reinterpret_cast<uint4 *>(tile + (4 * k2 + (lane >> 3)) * DT_STRIDE + 128 * hf + 16 * (lane & 7)) = make_uint4(0, 0, 0, 0);
-                    __syncwarp();
-                }
+                // ---- first the rows the code and zero-point MMAs read (K factors, K zero-points, V factors and
+                //      zero-points): they are cheap, and the MMA warp starts on them while the deltas are scattered ----
                 const uint32_t e2 = *reinterpret_cast<const uint16_t *>(gb + p.o_ks + h * 128 + d0);
                 const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
-                uint32_t ms2 = 0, mc2 = 0;
-                uint2 bm2 = make_uint2(0, 0);
-                uint32_t st[2] = {0, 0}, sth[2] = {0, 0};            // nibble stream of each channel: outliers 0..7, 8..15
-                if (splice) {
-                    if (p.use_map) {
-                        ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
-                        mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
-                    }
-                    bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
-                    const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
-                    const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nb;          // 2*nb bytes, 2-byte aligned
-                    if (nb == 3) {
-                        const uint32_t w0 = reinterpret_cast<const uint16_t *>(ov)[0], w1 = reinterpret_cast<const uint16_t *>(ov)[1],
-                                       w2 = reinterpret_cast<const uint16_t *>(ov)[2];
-                        st[0] = w0 | ((w1 & 0xFFu) << 16);
-                        st[1] = (w1 >> 8) | (w2 << 8);
-                    } else if (nb == 4) {
-                        const uint2 w = *reinterpret_cast<const uint2 *>(ov);
-                        st[0] = w.x; st[1] = w.y;
-                    } else if (nb == 2) {
-                        const uint32_t w = *reinterpret_cast<const uint32_t *>(ov);
-                        st[0] = w & 0xFFFFu; st[1] = w >> 16;
-                    } else if (nb > 4) {
-                        // 9..16 outliers: the two channels' streams are 2*nb bytes back to back; read them as
-                        // 16-bit pieces into a 128-bit little-endian window and cut it at bit 8*nb
-                        uint32_t w[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            if (i < nb) w[i >> 1] |= (uint32_t) reinterpret_cast<const uint16_t *>(ov)[i] << (16 * (i & 1));
-                        const int sh = 8 * (nb - 4);                     // 8..32 bits of a stream lie above its first word
-                        const uint32_t hmask = sh == 32 ? 0xFFFFFFFFu : ((1u << sh) - 1u);
-                        st[0] = w[0]; sth[0] = w[1] & hmask;
-                        if (sh == 32) { st[1] = w[2]; sth[1] = w[3]; }
-                        else { st[1] = __funnelshift_r(w[1], w[2], sh); sth[1] = __funnelshift_r(w[2], w[3], sh) & hmask; }
-                    } else {
-                        const uint32_t w = *reinterpret_cast<const uint16_t *>(ov);
-                        st[0] = w & 0xFFu; st[1] = w >> 8;
-                    }
-                }
-                OMMX_TR(trk + 3);
-                const uint32_t bmv[2] = {bm2.x, bm2.y};
-                // The code byte holding this lane's channels, row pz: byte pz*TS + h*32 + d0/4 of the (1 KB aligned)
-                // k_base block, with the 16-byte chunk bits XOR-ed by the row's swizzle term.  h*32 + d0/4 splits
-                // into a part above bit 7 (added to the row) and a part below (the XOR operand).
-                const uint32_t k_hi_rel = (uint32_t)(h >> 2) * 128u;
-                const uint8_t *k_hi = gb + k_hi_rel;
-                const uint32_t k_lo = (uint32_t)((h & 3) * 32 + (d0 >> 2));
                 // this lane's entry in the fragment-ordered K factor row
                 const uint32_t kf_off = ROW_KF * DT_STRIDE + 64u * (2 * hf + (lane >> 4)) + 32u * ((lane >> 3) & 1) + 8u * (lane & 3) + 2u * ((lane >> 2) & 1);
                 uint32_t zph[2];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int e = max((int)(int8_t)(e2 >> (8 * c)), -126);
-                    const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
-                    const float zp = bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu));
-                    zph[c] = f16_bits_sat(zp);
+                    zph[c] = f16_bits_sat(bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu)));
                     bool cl;
                     const uint32_t fb = pow2_f16_bits(e, cl);
                     clamped_any |= cl;
                     *reinterpret_cast<uint16_t *>(tile + kf_off + 4 * c) = (uint16_t)fb;
-                    if (splice) {
-                        // delta between the outlier value and the base value it replaces, rounded once
-                        float A = sc, Bc = 0.f;                     // shared map: lvl*s + zp - (code*s + zp)
-                        if (p.use_map) {
-                            const float ms = bf16_bits_to_f32(c ? (ms2 >> 16) : (ms2 & 0xFFFFu));
-                            const float mc = bf16_bits_to_f32(c ? (mc2 >> 16) : (mc2 & 0xFFFFu));
-                            A = __fdividef(1.f, ms);
-                            Bc = mc - zp;
-                        }
-                        uint32_t bits = bmv[c];
-                        const uint32_t stream = st[c], stream_hi = sth[c];
-                        (void)stream_hi;
-                        const int fsh = 2 * ((d0 & 3) + c);          // bit position of the channel's code in its byte
-                        uint8_t *col = tile + 2 * d0 + 2 * c;
-                        if (KOUT > 0) {
-                            if (__popc(bits) == KOUT) {
-#pragma unroll
-                                for (int r = KOUT - 1; r >= 0; --r) {
-                                    const int pz = 31 - __clz(bits);
-                                    bits ^= 1u << pz;
-                                    const uint32_t nib = (stream >> (4 * r)) & 0xFu;
-                                    const uint32_t row = (uint32_t)pz * (uint32_t)TS;
-                                    const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
-                                    const float cf = (float)((cb >> fsh) & 3u);
-                                    const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
-                                    *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
-                                }
-                            } else {
-                                or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
-                            }
-                        } else {
-                            int r = __popc(bits) - 1;
-                            while (bits) {
-                                const int pz = 31 - __clz(bits);
-                                bits ^= 1u << pz;
-                                const uint32_t nib = ((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu;
-                                --r;
-                                const uint32_t row = (uint32_t)pz * (uint32_t)TS;
-                                const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
-                                const float cf = (float)((cb >> fsh) & 3u);
-                                const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
-                                *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
-                            }
-                        }
-                    }
                 }
                 *reinterpret_cast<uint32_t *>(tile + ROW_ZP * DT_STRIDE + 2 * d0) = zph[0] | (zph[1] << 16);
                 {   // V side: one token, two scale groups: power-of-two factor and zero-point of each
@@ -596,6 +500,145 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                         *reinterpret_cast<uint16_t *>(vfr + 16 * c) = (uint16_t)fb;
                         const float vz = bf16_bits_to_f32(c ? (vz2 >> 16) : (vz2 & 0xFFFFu));
                         *reinterpret_cast<uint16_t *>(ztr + 64 * c) = (uint16_t)f16_bits_sat(vz);
+                    }
+                }
+#ifdef OMMX_V_VFRAG
+                if (!(p.abl & ABL_NO_V)) {
+                    // V code bytes of this half (tokens 16hf .. 16hf+15 of head h) turned, in place, into the order the
+                    // P.V MMAs take them: MMA lane (g, j) needs byte 8cg + g of token rows 2j, 2j+1, 2j+8, 2j+9 for the four
+                    // scale groups cg - 16 scattered bytes.  Lane (g, j) of this warp gathers them into one 16-byte
+                    // word [cg][row] and stores it in 16-byte slot `lane` of the same 512 bytes (slot 2r + u = half u of token
+                    // row r), so the MMA warp fetches its operands with one 16-byte load per k-step.
+                    uint8_t *vreg_w = gb + p.o_vm;
+                    const int fg = lane >> 2, fj = lane & 3;
+                    const uint32_t v_hi_rel = (uint32_t)(h >> 2) * 128u, v_lo = (uint32_t)((h & 3) * 32 + fg);
+                    uint32_t fw[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int tt = 0; tt < 4; ++tt) {
+                        const uint32_t rowhi = (uint32_t)(16 * hf + 2 * fj + (tt & 1) + 8 * (tt >> 1)) * (uint32_t)TS + v_hi_rel;
+                        const uint32_t tm = (rowhi >> 3) & p.swz;
+                        const uint8_t *r0 = vreg_w + (rowhi + (v_lo ^ tm)), *r1 = vreg_w + (rowhi + ((v_lo ^ 16u) ^ tm));
+                        fw[0] |= (uint32_t)r0[0] << (8 * tt); fw[1] |= (uint32_t)r0[8] << (8 * tt);
+                        fw[2] |= (uint32_t)r1[0] << (8 * tt); fw[3] |= (uint32_t)r1[8] << (8 * tt);
+                    }
+                    __syncwarp();                                        // every lane holds its bytes before any slot is overwritten
+                    *reinterpret_cast<uint4 *>(vreg_w + swz128((uint32_t)((16 * hf + (lane >> 1)) * TS + h * 32 + 16 * (lane & 1)), p.swz)) =
+                        make_uint4(fw[0], fw[1], fw[2], fw[3]);
+                    // the next writer of these bytes is a bulk copy of the producer (async proxy)
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+#endif
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_trows + 8 * unit);
+                OMMX_TR(trk + 3);
+                // ---- then the outlier deltas of this half's columns ----
+                if (splice) {
+                    // clear this half's columns of token rows 0..31 (128 bytes per row)
+#pragma unroll
+                    for (int k2 = 0; k2 < 8; ++k2)
+                        *reinterpret_cast<uint4 *>(tile + (4 * k2 + (lane >> 3)) * DT_STRIDE + 128 * hf + 16 * (lane & 7)) = make_uint4(0, 0, 0, 0);
+                    uint32_t ms2 = 0, mc2 = 0;
+                    if (p.use_map) {
+                        ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
+                        mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
+                    }
+                    const uint2 bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
+                    uint32_t st[2] = {0, 0}, sth[2] = {0, 0};            // nibble stream of each channel: outliers 0..7, 8..15
+                    const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
+                    const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nb;          // 2*nb bytes, 2-byte aligned
+                    if (nb == 3) {
+                        const uint32_t w0 = reinterpret_cast<const uint16_t *>(ov)[0], w1 = reinterpret_cast<const uint16_t *>(ov)[1],
+                                       w2 = reinterpret_cast<const uint16_t *>(ov)[2];
+                        st[0] = w0 | ((w1 & 0xFFu) << 16);
+                        st[1] = (w1 >> 8) | (w2 << 8);
+                    } else if (nb == 4) {
+                        const uint2 w = *reinterpret_cast<const uint2 *>(ov);
+                        st[0] = w.x; st[1] = w.y;
+                    } else if (nb == 2) {
+                        const uint32_t w = *reinterpret_cast<const uint32_t *>(ov);
+                        st[0] = w & 0xFFFFu; st[1] = w >> 16;
+                    } else if (nb > 4) {
+                        // 9..16 outliers: the two channels' streams are 2*nb bytes back to back; read them as
+                        // 16-bit pieces into a 128-bit little-endian window and cut it at bit 8*nb
+                        uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (i < nb) w[i >> 1] |= (uint32_t) reinterpret_cast<const uint16_t *>(ov)[i] << (16 * (i & 1));
+                        const int sh = nb > 4 ? 8 * (nb - 4) : 8;        // 8..32 bits of a stream lie above its first word
+                        const uint32_t hmask = sh == 32 ? 0xFFFFFFFFu : ((1u << sh) - 1u);
+                        st[0] = w[0]; sth[0] = w[1] & hmask;
+                        if (sh == 32) { st[1] = w[2]; sth[1] = w[3]; }
+                        else { st[1] = __funnelshift_r(w[1], w[2], sh); sth[1] = __funnelshift_r(w[2], w[3], sh) & hmask; }
+                    } else {
+                        const uint32_t w = *reinterpret_cast<const uint16_t *>(ov);
+                        st[0] = w & 0xFFu; st[1] = w >> 8;
+                    }
+                    __syncwarp();                                        // the cleared rows before any delta lands in them
+                    const uint32_t bmv[2] = {bm2.x, bm2.y};
+                    // The code byte holding this lane's channels, row pz: byte pz*TS + h*32 + d0/4 of the (1 KB aligned)
+                    // k_base block, with the 16-byte chunk bits XOR-ed by the row's swizzle term.  h*32 + d0/4 splits
+                    // into a part above bit 7 (added to the row) and a part below (the XOR operand).
+                    const uint32_t k_hi_rel = (uint32_t)(h >> 2) * 128u;
+                    const uint8_t *k_hi = gb + k_hi_rel;
+                    const uint32_t k_lo = (uint32_t)((h & 3) * 32 + (d0 >> 2));
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int e = max((int)(int8_t)(e2 >> (8 * c)), -126);
+                        const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
+                        const float zp = bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu));
+                        // delta between the outlier value and the base value it replaces, rounded once
+                        float A = sc, Bc = 0.f;                     // shared map: lvl*s + zp - (code*s + zp)
+                        if (p.use_map) {
+                            const float ms = bf16_bits_to_f32(c ? (ms2 >> 16) : (ms2 & 0xFFFFu));
+                            const float mc = bf16_bits_to_f32(c ? (mc2 >> 16) : (mc2 & 0xFFFFu));
+                            A = __fdividef(1.f, ms);
+                            Bc = mc - zp;
+                        }
+                        uint32_t bits = bmv[c];
+                        const uint32_t stream = st[c], stream_hi = sth[c];
+                        (void)stream_hi;
+                        const int fsh = 2 * ((d0 & 3) + c);          // bit position of the channel's code in its byte
+                        uint8_t *col = tile + 2 * d0 + 2 * c;
+                        if (KOUT > 0) {
+                            if (__popc(bits) == KOUT) {
+                                // Two passes: all gathers (base-code byte, FP4 level) first, then the arithmetic and the
+                                // stores.  In one pass every load would have to follow the previous outlier's store in
+                                // program order (shared memory may alias), i.e. KOUT load round trips in a row.
+                                constexpr int KO = KOUT > 0 ? KOUT : 1;
+                                uint32_t pzs[KO], cbs[KO];
+                                float lvs[KO];
+#pragma unroll
+                                for (int r = KO - 1; r >= 0; --r) {
+                                    const int pz = 31 - __clz(bits);
+                                    bits ^= 1u << pz;
+                                    pzs[r] = (uint32_t)pz;
+                                    lvs[r] = s_lut[(stream >> (4 * r)) & 0xFu];
+                                    const uint32_t row = (uint32_t)pz * (uint32_t)TS;
+                                    cbs[r] = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
+                                }
+#pragma unroll
+                                for (int r = KO - 1; r >= 0; --r) {
+                                    const float cf = (float)((cbs[r] >> fsh) & 3u);
+                                    const float X = fmaf(cf, -sc, fmaf(lvs[r], A, Bc));
+                                    *reinterpret_cast<uint16_t *>(col + pzs[r] * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
+                                }
+                            } else {
+                                or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
+                            }
+                        } else {
+                            int r = __popc(bits) - 1;
+                            while (bits) {
+                                const int pz = 31 - __clz(bits);
+                                bits ^= 1u << pz;
+                                const uint32_t nib = ((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu;
+                                --r;
+                                const uint32_t row = (uint32_t)pz * (uint32_t)TS;
+                                const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
+                                const float cf = (float)((cb >> fsh) & 3u);
+                                const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
+                                *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
+                            }
+                        }
                     }
                 }
                 if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
@@ -706,7 +749,9 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 if (do_k) kw[nt] = *reinterpret_cast<const uint2 *>(gb + swz128((uint32_t)((8 * nt + g) * TS + h * 32 + 8 * j), p.swz));
             }
             OMMX_TR(8 * it + 2);
-            if (!mbar_wait(bar_tfull + 8 * unit, consumed & 1u)) {
+            // The unit's sidecar tile arrives in two steps: first the factor and zero-point rows, then the outlier
+            // deltas.  The code and zero-point MMAs run on the first, while the decode warps still scatter the deltas.
+            if (!mbar_wait(bar_trows + 8 * unit, consumed & 1u)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
                 break;
@@ -716,33 +761,45 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) { Sc[mt][0] = Sc[mt][1] = Sc[mt][2] = Sc[mt][3] = 0.f; Sd[mt][0] = Sd[mt][1] = Sd[mt][2] = Sd[mt][3] = 0.f; }
             Sz[0] = Sz[1] = Sz[2] = Sz[3] = 0.f;
-            // Five accumulators take turns, so that neighbours in the instruction stream never wait on each
-            // other, and every tile fragment is fetched two or three MMAs before the MMA that takes it
+            // Three accumulators take turns, so that neighbours in the instruction stream never wait on each
+            // other, and the zero-point fragment of the next k-step is fetched before the MMAs of this one
             // (the asm statements keep their order, so the order written here is the order issued).
-            uint32_t d0f[4], d1f[4], zf[2];                      // delta fragments of m-tile 0 / 1, zero-point fragment
-            if (has_delta) ldsm_x4(a_delta, d0f[0], d0f[1], d0f[2], d0f[3]);
-            ldsm_x2(a_zp, zf[0], zf[1]);
+            {
+                uint32_t zf[2];
+                ldsm_x2(a_zp, zf[0], zf[1]);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int wi = q >> 2, i0 = 2 * (q & 3);
-                const uint2 fq = reinterpret_cast<const uint2 *>(p_kf)[q];      // this k-step's two factor pairs
-                const uint32_t b0 = hmul2_f16(QS[2 * q], fq.x), b1 = hmul2_f16(QS[2 * q + 1], fq.y);
-                if (has_delta) ldsm_x4(a_delta + 16 * DT_STRIDE + 32 * q, d1f[0], d1f[1], d1f[2], d1f[3]);
-                {
-                    const uint32_t wlo = wi ? kw[0].y : kw[0].x, whi = wi ? kw[1].y : kw[1].x;
-                    mma_f16(Sc[0], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
+                for (int q = 0; q < 8; ++q) {
+                    const int wi = q >> 2, i0 = 2 * (q & 3);
+                    const uint2 fq = reinterpret_cast<const uint2 *>(p_kf)[q];      // this k-step's two factor pairs
+                    const uint32_t b0 = hmul2_f16(QS[2 * q], fq.x), b1 = hmul2_f16(QS[2 * q + 1], fq.y);
+                    {
+                        const uint32_t wlo = wi ? kw[0].y : kw[0].x, whi = wi ? kw[1].y : kw[1].x;
+                        mma_f16(Sc[0], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
+                    }
+                    mma_f16(Sz, zf[0], 0u, zf[1], 0u, QD[2 * q], QD[2 * q + 1]);
+                    if (q < 7) ldsm_x2(a_zp + 32 * (q + 1), zf[0], zf[1]);
+                    {
+                        const uint32_t wlo = wi ? kw[2].y : kw[2].x, whi = wi ? kw[3].y : kw[3].x;
+                        mma_f16(Sc[1], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
+                    }
                 }
-                if (has_delta) mma_f16(Sd[0], d0f[0], d0f[1], d0f[2], d0f[3], QD[2 * q], QD[2 * q + 1]);
-                mma_f16(Sz, zf[0], 0u, zf[1], 0u, QD[2 * q], QD[2 * q + 1]);
-                if (q < 7) {
-                    if (has_delta) ldsm_x4(a_delta + 32 * (q + 1), d0f[0], d0f[1], d0f[2], d0f[3]);
-                    ldsm_x2(a_zp + 32 * (q + 1), zf[0], zf[1]);
+            }
+            if (has_delta) {
+                if (!mbar_wait(bar_tfull + 8 * unit, consumed & 1u)) {
+                    if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+                    m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
+                    break;
                 }
-                {
-                    const uint32_t wlo = wi ? kw[2].y : kw[2].x, whi = wi ? kw[3].y : kw[3].x;
-                    mma_f16(Sc[1], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
+                OMMX_TR(8 * it + 7);
+                uint32_t d0f[4], d1f[4];                         // delta fragments of m-tile 0 / 1
+                ldsm_x4(a_delta, d0f[0], d0f[1], d0f[2], d0f[3]);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    ldsm_x4(a_delta + 16 * DT_STRIDE + 32 * q, d1f[0], d1f[1], d1f[2], d1f[3]);
+                    mma_f16(Sd[0], d0f[0], d0f[1], d0f[2], d0f[3], QD[2 * q], QD[2 * q + 1]);
+                    if (q < 7) ldsm_x4(a_delta + 32 * (q + 1), d0f[0], d0f[1], d0f[2], d0f[3]);
+                    mma_f16(Sd[1], d1f[0], d1f[1], d1f[2], d1f[3], QD[2 * q], QD[2 * q + 1]);
                 }
-                if (has_delta) mma_f16(Sd[1], d1f[0], d1f[1], d1f[2], d1f[3], QD[2 * q], QD[2 * q + 1]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot((int)consumed, NS)));   // the next tile may be built
@@ -825,6 +882,13 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     // Byte 8cg + g of a token row's 32-byte head slice, four scale groups per row.  The swizzle term
                     // of a row only touches bits 4..6, so two XORs give the addresses of groups 0 and 2 and the
                     // other two are 8 bytes on.
+#ifdef OMMX_V_VFRAG
+                    // the decode warps left this lane's 16 code bytes of the k-step in slot `lane` of the half: word cg holds
+                    // byte 8cg + g of token rows tA, tA+1, tA+8, tA+9
+                    const uint4 fv = *reinterpret_cast<const uint4 *>(vreg + swz128((uint32_t)((16 * ks + (lane >> 1)) * TS + h * 32 + 16 * (lane & 1)), p.swz));
+                    const uint32_t fw[4] = {fv.x, fv.y, fv.z, fv.w};
+                    (void)tA; (void)v_hi_rel; (void)v_lo;
+#else
                     uint32_t vb[4][4];                               // [token of (tA, tA+1, tA+8, tA+9)][scale group]
 #pragma unroll
                     for (int tt = 0; tt < 4; ++tt) {
@@ -834,11 +898,16 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                         vb[tt][0] = r0[0]; vb[tt][1] = r0[8];
                         vb[tt][2] = r1[0]; vb[tt][3] = r1[8];
                     }
+#endif
 #pragma unroll
                     for (int cg = 0; cg < 4; ++cg) {
                         // channels 32cg + 4g .. + 3 of four tokens: one byte each
+#ifdef OMMX_V_VFRAG
+                        const uint32_t w01 = __byte_perm(fw[cg], 0u, 0x4140), w89 = __byte_perm(fw[cg], 0u, 0x4342);
+#else
                         const uint32_t bA = vb[0][cg], bA1 = vb[1][cg], bB = vb[2][cg], bB1 = vb[3][cg];
                         const uint32_t w01 = bA | (bA1 << 16), w89 = bB | (bB1 << 16);
+#endif
                         const uint32_t pb0 = hmul2_f16(T[ks][0], VF[4 * cg + 2 * ks]), pb1 = hmul2_f16(T[ks][1], VF[4 * cg + 2 * ks + 1]);
 #pragma unroll
                         for (int u = 0; u < 2; ++u)
@@ -1226,7 +1295,7 @@ static bool make_code_map(CUtensorMap *m, const void *base, int64_t total_bytes,
 
 static size_t stage1_smem(const S1Params &p) {
     return 1024 + (size_t)p.nstages * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
-           + (2 * MAX_STAGES + (1 + MAX_STAGES) * NCW) * 8 + 16 + MAX_STAGE_COPIES * sizeof(CopyDesc);
+           + (2 * MAX_STAGES + (2 + MAX_STAGES) * NCW) * 8 + 16 + MAX_STAGE_COPIES * sizeof(CopyDesc);
 }
 
 template <int KOUT>
