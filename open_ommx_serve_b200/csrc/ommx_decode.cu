@@ -502,32 +502,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                         *reinterpret_cast<uint16_t *>(ztr + 64 * c) = (uint16_t)f16_bits_sat(vz);
                     }
                 }
-#ifdef OMMX_V_VFRAG
-                if (!(p.abl & ABL_NO_V)) {
-                    // V code bytes of this half (tokens 16hf .. 16hf+15 of head h) turned, in place, into the order the
-                    // P.V MMAs take them: MMA lane (g, j) needs byte 8cg + g of token rows 2j, 2j+1, 2j+8, 2j+9 for the four
-                    // scale groups cg - 16 scattered bytes.  Lane (g, j) of this warp gathers them into one 16-byte
-                    // word [cg][row] and stores it in 16-byte slot `lane` of the same 512 bytes (slot 2r + u = half u of token
-                    // row r), so the MMA warp fetches its operands with one 16-byte load per k-step.
-                    uint8_t *vreg_w = gb + p.o_vm;
-                    const int fg = lane >> 2, fj = lane & 3;
-                    const uint32_t v_hi_rel = (uint32_t)(h >> 2) * 128u, v_lo = (uint32_t)((h & 3) * 32 + fg);
-                    uint32_t fw[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                    for (int tt = 0; tt < 4; ++tt) {
-                        const uint32_t rowhi = (uint32_t)(16 * hf + 2 * fj + (tt & 1) + 8 * (tt >> 1)) * (uint32_t)TS + v_hi_rel;
-                        const uint32_t tm = (rowhi >> 3) & p.swz;
-                        const uint8_t *r0 = vreg_w + (rowhi + (v_lo ^ tm)), *r1 = vreg_w + (rowhi + ((v_lo ^ 16u) ^ tm));
-                        fw[0] |= (uint32_t)r0[0] << (8 * tt); fw[1] |= (uint32_t)r0[8] << (8 * tt);
-                        fw[2] |= (uint32_t)r1[0] << (8 * tt); fw[3] |= (uint32_t)r1[8] << (8 * tt);
-                    }
-                    __syncwarp();                                        // every lane holds its bytes before any slot is overwritten
-                    *reinterpret_cast<uint4 *>(vreg_w + swz128((uint32_t)((16 * hf + (lane >> 1)) * TS + h * 32 + 16 * (lane & 1)), p.swz)) =
-                        make_uint4(fw[0], fw[1], fw[2], fw[3]);
-                    // the next writer of these bytes is a bulk copy of the producer (async proxy)
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                }
-#endif
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_trows + 8 * unit);
                 OMMX_TR(trk + 3);
@@ -729,14 +703,15 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         const int s = ring_slot(it, NS);
         const uint32_t ph = ring_phase(it, NS);
         OMMX_TR(8 * it);
+        const int lg = it * GS + gsel;                               // local group of this warp
+        const bool active = lg < ngroups && !(p.abl & ABL_NO_COMPUTE);
         if (!mbar_wait(bar_full + 8 * s, ph)) {
             if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
             m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
             break;
         }
         OMMX_TR(8 * it + 1);
-        const int lg = it * GS + gsel;                               // local group of this warp
-        if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
+        if (active) {
             uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
             const uint8_t *vreg = gb + p.o_vm;                      // v_main region of the group (1 KB aligned)
 
@@ -882,13 +857,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     // Byte 8cg + g of a token row's 32-byte head slice, four scale groups per row.  The swizzle term
                     // of a row only touches bits 4..6, so two XORs give the addresses of groups 0 and 2 and the
                     // other two are 8 bytes on.
-#ifdef OMMX_V_VFRAG
-                    // the decode warps left this lane's 16 code bytes of the k-step in slot `lane` of the half: word cg holds
-                    // byte 8cg + g of token rows tA, tA+1, tA+8, tA+9
-                    const uint4 fv = *reinterpret_cast<const uint4 *>(vreg + swz128((uint32_t)((16 * ks + (lane >> 1)) * TS + h * 32 + 16 * (lane & 1)), p.swz));
-                    const uint32_t fw[4] = {fv.x, fv.y, fv.z, fv.w};
-                    (void)tA; (void)v_hi_rel; (void)v_lo;
-#else
                     uint32_t vb[4][4];                               // [token of (tA, tA+1, tA+8, tA+9)][scale group]
 #pragma unroll
                     for (int tt = 0; tt < 4; ++tt) {
@@ -898,16 +866,11 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                         vb[tt][0] = r0[0]; vb[tt][1] = r0[8];
                         vb[tt][2] = r1[0]; vb[tt][3] = r1[8];
                     }
-#endif
 #pragma unroll
                     for (int cg = 0; cg < 4; ++cg) {
                         // channels 32cg + 4g .. + 3 of four tokens: one byte each
-#ifdef OMMX_V_VFRAG
-                        const uint32_t w01 = __byte_perm(fw[cg], 0u, 0x4140), w89 = __byte_perm(fw[cg], 0u, 0x4342);
-#else
                         const uint32_t bA = vb[0][cg], bA1 = vb[1][cg], bB = vb[2][cg], bB1 = vb[3][cg];
                         const uint32_t w01 = bA | (bA1 << 16), w89 = bB | (bB1 << 16);
-#endif
                         const uint32_t pb0 = hmul2_f16(T[ks][0], VF[4 * cg + 2 * ks]), pb1 = hmul2_f16(T[ks][1], VF[4 * cg + 2 * ks + 1]);
 #pragma unroll
                         for (int u = 0; u < 2; ++u)
