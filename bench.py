@@ -38,6 +38,7 @@ sys.path.insert(0, ROOT)
 
 LAYERS, HQ, HKV, D, PAGE = 32, 32, 8, 128, 16
 SINK, RECENT, K_OUT = 8, 32, 6
+MAG = 12.0                # factor on the 4 outlier channels of every K head
 CONTEXTS = (1024, 4096, 16384, 32768, 65536)
 HEADLINE_CTX = 65536
 H200_PUBLISHED_US = {65536: 563.2, 32768: 284.1, 16384: 162.3, 4096: 147.3, 1024: 469.6}
@@ -52,10 +53,16 @@ def packed_len(ctx):
 NCU_TRAFFIC_RATIO = 70.33e6 / 69138432.0
 
 
+def unit_bytes(k):
+    """Packed bytes per (token, kv head): codes 32 + K scale 4 + K zero-point 8 (+ map scale 8, map centre 8, bitmask
+    16 and 4 bytes per pair of outliers when k > 0) + V 44; 132 at k = 6."""
+    return 32 + 4 + 8 + ((8 + 8 + 16 + 4 * ((k + 1) // 2)) if k > 0 else 0) + 44
+
+
 def algorithmic_bytes(ctx, batch, hkv):
     """Bytes the path must read per layer: every plane handed to the kernel + the bf16 rows."""
     p = packed_len(ctx)
-    return batch * (p * hkv * 132 + (ctx - p) * hkv * D * 2 * 2)
+    return batch * (p * hkv * unit_bytes(K_OUT) + (ctx - p) * hkv * D * 2 * 2)
 
 
 def measured_peak_gbs():
@@ -133,7 +140,7 @@ def cpu_reference_layer(ctx, threads=None, steps=3, warmup=1, seed=42):
     V = torch.randn(ctx, HKV, D, generator=g)
     for h in range(HKV):
         idx = torch.randperm(D, generator=torch.Generator().manual_seed(seed + 1 + h))[:4]
-        K[:, h, idx] *= 12.0
+        K[:, h, idx] *= MAG
     Kh, Vh = K.permute(1, 0, 2).contiguous(), V.permute(1, 0, 2).contiguous()
     times, qt, at = [], [], []
     for i in range(warmup + steps):
@@ -218,7 +225,7 @@ class LayerStack:
                     V = torch.randn(n, hkv, D, generator=cg, device=device)
                     for h in range(hkv):
                         idx = torch.randperm(D, generator=torch.Generator().manual_seed(seed + 1 + h))[:4].to(device)
-                        K[:, h, idx] *= 12.0
+                        K[:, h, idx] *= MAG
                     ommx_pack_kv_into(K.bfloat16(), V.bfloat16(), pl,
                                       dst_pages=self.req_to_token[b, t0 // PAGE:(t0 + n) // PAGE].contiguous(),
                                       dst_groups=self.req_to_group[b, t0 // 32:(t0 + n) // 32].contiguous(),
@@ -423,7 +430,7 @@ def run_ours(args, rank, world, local_rank):
         "vs_baseline": us_layer / H200_PUBLISHED_US[args.ctx] if args.ctx in H200_PUBLISHED_US else None,
         "vs_baseline_note": "value / the reference's published H200-NVL microbench time for the same context (other hardware, page 32)",
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"llama3.1-8b geometry, {LAYERS}-layer stack, batch 1, ctx {args.ctx}, OMMX k=6 sink 8 "
+        "config": {"workload": f"llama3.1-8b geometry, {LAYERS}-layer stack, batch 1, ctx {args.ctx}, OMMX k={K_OUT} (outlier channels x{MAG:g}) sink 8 "
                                f"recent 32, {PAGE}-token pages, random page table",
                    "ctx": args.ctx, "batch": 1, "kv_heads_per_gpu": hkv, "splits": per_ctx[str(args.ctx)]["splits"],
                    "l2": "flushed between timed steps (256 MiB memset); one step reads 32 distinct plane sets",
@@ -536,8 +543,12 @@ def main():
     ap.add_argument("--profile", action="store_true", help="eager launches only, for ncu (use a small --layers)")
     ap.add_argument("--workload", default="b1", choices=("b1", "batch32"),
                     help="b1 = the headline line; batch32 = ragged batch with the per-step store (own JSON line)")
+    ap.add_argument("--k", type=int, default=K_OUT, help="outliers per K vector (the headline recipe has 6)")
+    ap.add_argument("--mag", type=float, default=MAG, help="factor on the 4 outlier channels of every K head")
     args = ap.parse_args()
     globals()["LAYERS"] = args.layers
+    globals()["K_OUT"] = args.k
+    globals()["MAG"] = args.mag
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -87,7 +87,7 @@ struct __align__(16) CopyDesc {
     uint32_t unit, dst;
     int32_t tbase, tmul, gi, tok0;       // gi: group in stage (bits 0..7) | kind << 8
 };                                       // kind 0 bulk copy, 1 k_base through tmap_k, 2 v_main through tmap_v
-constexpr int MAX_STAGE_COPIES = 8 * (4 * 4 + 6);                    // 8 groups per stage, 8-token pages
+// a stage holds at most 8 groups x (4 planes x 4 pages + 6 group planes) = 176 copies (1 kv head, 8-token pages)
 
 // Development builds (-DOMMX_TRACE) stamp the SM clock at fixed points of one CTA's warps into a
 // device array that ommx_b200_debug_read_trace copies out; service builds compile the probes away.
@@ -586,7 +586,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                                     const int pz = 31 - __clz(bits);
                                     bits ^= 1u << pz;
                                     pzs[r] = (uint32_t)pz;
-                                    lvs[r] = s_lut[(stream >> (4 * r)) & 0xFu];
+                                    lvs[r] = s_lut[((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu];
                                     const uint32_t row = (uint32_t)pz * (uint32_t)TS;
                                     cbs[r] = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
                                 }
@@ -600,6 +600,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                                 or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
                             }
                         } else {
+                            // any other k: one pass at run time
                             int r = __popc(bits) - 1;
                             while (bits) {
                                 const int pz = 31 - __clz(bits);
@@ -1258,7 +1259,8 @@ static bool make_code_map(CUtensorMap *m, const void *base, int64_t total_bytes,
 
 static size_t stage1_smem(const S1Params &p) {
     return 1024 + (size_t)p.nstages * p.stage_bytes + (size_t)NCW * DT_BYTES + (MAX_SPLIT_GROUPS + MAX_SPLIT_PAGES) * 4 + 64
-           + (2 * MAX_STAGES + (2 + MAX_STAGES) * NCW) * 8 + 16 + MAX_STAGE_COPIES * sizeof(CopyDesc);
+           + (2 * MAX_STAGES + (2 + MAX_STAGES) * NCW) * 8 + 16
+           + (size_t)p.GS * (4 * p.ppg + 6) * sizeof(CopyDesc);       // the copy roles of one stage come last
 }
 
 template <int KOUT>
@@ -1329,9 +1331,15 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     const size_t smem = stage1_smem(p);
     if (smem > 232448) return fail(OMMX_E_UNSUPPORTED, "stage 1 planes of one group do not fit shared memory");
     dim3 grid(a->num_kv_splits, a->batch);
-    if (p.k_out == 6) return launch_s1<6>(p, grid, smem, st);
-    if (p.k_out == 0) return launch_s1<0>(p, grid, smem, st);
-    return launch_s1<-1>(p, grid, smem, st);
+    switch (p.k_out) {                       // the serving recipes get the unrolled two-pass splice
+        case 0: return launch_s1<0>(p, grid, smem, st);
+        case 2: return launch_s1<2>(p, grid, smem, st);
+        case 4: return launch_s1<4>(p, grid, smem, st);
+        case 6: return launch_s1<6>(p, grid, smem, st);
+        case 8: return launch_s1<8>(p, grid, smem, st);
+        case 12: return launch_s1<12>(p, grid, smem, st);
+        default: return launch_s1<-1>(p, grid, smem, st);
+    }
 }
 
 // `after_stage1`: the previous kernel in the stream is this call's own stage 1, so stage 2 may be
