@@ -66,7 +66,7 @@ typedef struct ommx_kv_planes {
     int32_t page_size;            /* tokens per page: 8, 16 or 32 */
     int32_t num_pages;
     int32_t num_group_slots;
-    int32_t outliers_per_vector;  /* k: FP4 outliers per 32-token K vector (0..8) */
+    int32_t outliers_per_vector;  /* k: FP4 outliers per 32-token K vector (pack and decode: 0..16; the decode-step store: 0, 2, 4, 6, 8) */
     int32_t kv_outlier_map;       /* 1: outliers use k_mapscale/k_mapcenter, 0: share scale/zp */
     int32_t scale_kind;           /* OMMX_SCALE_* (zp and map planes are f32 iff OMMX_SCALE_F32) */
     void *k_base, *k_scale, *k_zp, *k_obmp, *k_oval, *k_mapscale, *k_mapcenter;
