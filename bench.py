@@ -8,16 +8,21 @@ Llama-3.1-8B geometry (32 query heads, 8 KV heads, head_dim 128), batch 1, conte
 recipe k=6 / sink 8 / recent 32, 16-token pages behind a seeded random page table.  Each layer
 has its own packed planes, so one step streams 32 x 69 MB - far more than the 126 MB L2; L2
 is flushed between timed steps as well.  Metric: microseconds per layer (lower is better); the
-achieved HBM GB/s (packed-KV bytes / time) and the other contexts are reported beside it.
+achieved HBM GB/s (packed-KV bytes / time) and the contexts 1K..128K are reported beside it.
 
   value      device-resident inputs, the whole step replayed as one CUDA graph
   roofline   stage-1 kernel alone: algorithmic bytes per launch / its average duration
              (CUDA events on the launching stream), against the measured copy bandwidth
-  e2e        the public Python entry with HOST buffers: per layer the step's q and new K/V
-             rows are copied from pinned memory and the output row is copied back
+  e2e        the public Python entry with HOST buffers: per step the q and new K/V rows of
+             every layer are copied from pinned memory and the outputs are copied back
+  contexts   per context: whole step, stage 1, stage 2, the all-gather (N > 1), and the
+             reference's own Triton kernels timed on the same planes of the same GPU
+             (baseline/_ref, the reference's microbenchmark protocol: graph replay, 3 + 20, median)
+  workloads  the other configurations as sub-records: batch 32 ragged with the per-step store,
+             Llama-70B head geometry (batch 8 x 32K), the prefill-time bulk pack of 8 192 tokens
   cpu_baseline / --impl reference
-             the reference's CPU path (fake-quantize K and V, then dense attention) restated in
-             oracle/, timed on the host cores on ONE layer of the same context
+             the reference's CPU path - its own fake quantizer (oracle/_ref, unmodified) on K and V,
+             then dense attention - timed on the host cores on ONE layer of the same context
 
 With N > 1 (torchrun) the 8 KV heads are sharded over the ranks, there is no collective inside
 attention, and one NCCL all-gather per layer reassembles the head outputs (timed inside the step).
@@ -26,7 +31,9 @@ Synthetic data throughout: seeded N(0,1) K/V with 4 K channels per head scaled x
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
+import math
 import os
 import subprocess
 import sys
@@ -39,17 +46,18 @@ sys.path.insert(0, ROOT)
 LAYERS, HQ, HKV, D, PAGE = 32, 32, 8, 128, 16
 SINK, RECENT, K_OUT = 8, 32, 6
 MAG = 12.0                # factor on the 4 outlier channels of every K head
-CONTEXTS = (1024, 4096, 16384, 32768, 65536)
+CONTEXTS = (1024, 4096, 16384, 32768, 65536, 131072)
 HEADLINE_CTX = 65536
 H200_PUBLISHED_US = {65536: 563.2, 32768: 284.1, 16384: 162.3, 4096: 147.3, 1024: 469.6}
+TRITON_BUDGET_S = 240.0   # wall-clock cap on the Triton legs of one run (JIT compiles dominate)
 
 
 def packed_len(ctx):
     return max(0, (ctx - SINK - RECENT) // 32 * 32)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch (ncu, ctx 65536, 8 kv heads: 69.25 MB + 1.08 MB)
-# over its algorithmic bytes (69 138 432): the planes are read once, nothing is re-read
+# dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch under ncu over its algorithmic
+# bytes (profiles/decode_stage1_64k_b1.md): the planes are read once, nothing is re-read
 NCU_TRAFFIC_RATIO = 70.33e6 / 69138432.0
 
 
@@ -70,6 +78,13 @@ def measured_peak_gbs():
         return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
 
 
 class ClockSampler:
@@ -125,15 +140,27 @@ class ClockSampler:
 
 # ───────────────────────────── reference arm / CPU baseline ─────────────────────────────
 
-def cpu_reference_layer(ctx, threads=None, steps=3, warmup=1, seed=42):
-    """The reference's CPU path on one layer: fake-quantize K (outliers kept as FP4) and V, then
-    dense attention of one query row over the result (ommx_fakequant/quant_function.py:152,
-    ommx_fakequant/quant_attention.py:688,957 restated in oracle/ommx_oracle.py)."""
+def _reference_fakequant():
+    """The reference's own fake quantizer, loaded by path from oracle/_ref (None when not built)."""
+    path = os.path.join(ROOT, "oracle", "_ref", "ommx_fakequant", "quant_function.py")
+    if not os.path.isfile(path):
+        return None
+    spec = importlib.util.spec_from_file_location("ref_quant_function", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod._apply_group_quantization_vectorized
+
+
+def cpu_reference_layer(ctx, steps=3, warmup=1, seed=42):
+    """The reference's CPU path on one layer: fake-quantize K (outliers kept as FP4) and V
+    (ommx_fakequant/quant_function.py:152, run unmodified from oracle/_ref when it is there, else
+    the restatement in oracle/ommx_oracle.py), then dense attention of one query row over the
+    result (ommx_fakequant/quant_attention.py:688,957).  All host cores."""
     import numpy as np
     import torch
     from oracle import ommx_oracle as O
-    if threads:
-        torch.set_num_threads(threads)
+    torch.set_num_threads(host_cores())          # torchrun exports OMP_NUM_THREADS=1; undo that here
+    ref_fq = _reference_fakequant()
     g = torch.Generator().manual_seed(seed)
     q = torch.randn(HQ, D, generator=g)
     K = torch.randn(ctx, HKV, D, generator=g)
@@ -142,11 +169,21 @@ def cpu_reference_layer(ctx, threads=None, steps=3, warmup=1, seed=42):
         idx = torch.randperm(D, generator=torch.Generator().manual_seed(seed + 1 + h))[:4]
         K[:, h, idx] *= MAG
     Kh, Vh = K.permute(1, 0, 2).contiguous(), V.permute(1, 0, 2).contiguous()
+    kw = dict(group_size=32, bits=2, use_pow2=True, attention_sink_num=RECENT, attention_sink_num_front=SINK,
+              debug_mode=False, outlier_method="fp4", outliers_per_group=0, is_prefill=False)
+
+    def quantize():
+        if ref_fq is not None:
+            Kq = ref_fq(Kh[None], is_key=True, outlier_percent_topk=3 / 32, outlier_percent_bottomk=3 / 32, **kw)[0]
+            Vq = ref_fq(Vh[None], is_key=False, outlier_percent_topk=0.0, outlier_percent_bottomk=0.0, **kw)[0]
+            return Kq, Vq
+        return (O.fakequant_group_torch(Kh, is_key=True),
+                O.fakequant_group_torch(Vh, is_key=False, top=0, bottom=0))
+
     times, qt, at = [], [], []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        Kq = O.fakequant_group_torch(Kh, is_key=True)
-        Vq = O.fakequant_group_torch(Vh, is_key=False, top=0, bottom=0)
+        Kq, Vq = quantize()
         t1 = time.perf_counter()
         Kr = Kq.repeat_interleave(HQ // HKV, dim=0)[None]
         Vr = Vq.repeat_interleave(HQ // HKV, dim=0)[None]
@@ -159,13 +196,25 @@ def cpu_reference_layer(ctx, threads=None, steps=3, warmup=1, seed=42):
     # correctness of what was timed: dense fp64 attention over the same fake-quantized cache
     want, _ = O.attention_fp32(q.numpy(), Kq.permute(1, 0, 2).numpy(), Vq.permute(1, 0, 2).numpy(), D ** -0.5)
     err = float(np.abs(out[0, :, 0].numpy() - want).max())
-    times.sort()
-    return {"us_per_layer": times[len(times) // 2] * 1e6, "quant_ms": sorted(qt)[len(qt) // 2] * 1e3,
-            "attn_ms": sorted(at)[len(at) // 2] * 1e3, "max_abs_vs_dense": err,
-            "threads": torch.get_num_threads(), "cpu_count": os.cpu_count()}
+    mean = sum(times) / len(times)
+    return {"us_per_layer": mean * 1e6, "median_us": sorted(times)[len(times) // 2] * 1e6,
+            "quant_ms": sorted(qt)[len(qt) // 2] * 1e3, "attn_ms": sorted(at)[len(at) // 2] * 1e3,
+            "max_abs_vs_dense": err, "threads": torch.get_num_threads(), "cpu_count": os.cpu_count(),
+            "kind": "reference" if ref_fq is not None else "port"}
+
+
+def cpu_baseline_record(res, ctx, steps):
+    what = ("the reference's ommx_fakequant/quant_function.py run unmodified" if res["kind"] == "reference"
+            else "the restatement of ommx_fakequant/quant_function.py in oracle/")
+    return {"value": res["us_per_layer"], "unit": "us", "cores": res["threads"], "kind": res["kind"],
+            "sample": f"1 of {LAYERS} layers at ctx {ctx} per step ({what}): fake-quantize K+V ({res['quant_ms']:.0f} ms) + "
+                      f"dense attention ({res['attn_ms']:.1f} ms), mean of {steps}; host has {res['cpu_count']} cpus",
+            "max_abs_vs_dense_attention": res["max_abs_vs_dense"]}
 
 
 def run_reference(args, rank, world):
+    """`--impl reference`: rank 0 alone times the reference's CPU path; a step is ONE layer of the
+    configured context (the layers of a stack are independent and identical in cost)."""
     if rank != 0:
         return
     ctx = args.ctx
@@ -174,14 +223,15 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": "ommx_decode_attn_us_per_layer", "value": us, "unit": "us",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": us * LAYERS / 1e3, "higher_is_better": False, "scaling": "strong",
+        "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"llama3.1-8b geometry, {LAYERS} layers, batch 1, ctx {ctx}, OMMX k=6 sink 8 recent 32",
-                   "ctx": ctx, "batch": 1},
-        "cpu_baseline": {"value": us, "unit": "us", "cores": res["threads"], "kind": "port",
-                         "sample": f"1 of {LAYERS} layers at ctx {ctx}: fake-quantize K+V ({res['quant_ms']:.0f} ms) + "
-                                   f"dense attention ({res['attn_ms']:.1f} ms); host has {res['cpu_count']} cpus",
-                         "max_abs_vs_dense_attention": res["max_abs_vs_dense"]},
+        "config": {"workload": f"llama3.1-8b geometry, {LAYERS}-layer stack, batch 1, ctx {ctx}, OMMX k={K_OUT} (outlier channels x{MAG:g}) sink 8 "
+                               f"recent 32, {PAGE}-token pages, random page table",
+                   "ctx": ctx, "batch": 1,
+                   "step": "one timed step = ONE layer of the stack on the host cores (a bounded sample: the layers are "
+                           "independent and cost the same); value is per layer, like the GPU arm's"},
+        "extrapolated_stack_ms": us * LAYERS / 1e3,
+        "cpu_baseline": cpu_baseline_record(res, ctx, max(1, args.steps)),
         "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "hbm_gbs": algorithmic_bytes(ctx, 1, HKV) / us / 1e3, "gpu_launches": 0,
     }
@@ -191,11 +241,12 @@ def run_reference(args, rank, world):
 # ───────────────────────────── our arm ─────────────────────────────
 
 class LayerStack:
-    """32 layers of pooled planes for one rank's share of the KV heads."""
+    """`layers` layers of pooled planes for one rank's share of the KV heads."""
 
-    def __init__(self, ctx, batch, hkv, hq, device, seed=42):
+    def __init__(self, ctx, batch, hkv, hq, device, seed=42, layers=None):
         import torch
         from open_ommx_serve_b200.attention.pack import alloc_planes, ommx_pack_kv_into
+        self.n_layers = LAYERS if layers is None else layers
         self.ctx, self.batch, self.hkv, self.hq, self.device = ctx, batch, hkv, hq, device
         P = packed_len(ctx)
         self.max_packed, self.max_tail = P, ctx - P
@@ -211,9 +262,10 @@ class LayerStack:
         cg = torch.Generator(device=device)
         chunk = 16384
         # residual rows of all layers in one tensor each, so that a step's new rows land with one copy
-        self.k_tail_all = torch.empty(LAYERS, batch, 72, hkv, D, dtype=torch.bfloat16, device=device)
+        self.k_tail_all = torch.empty(self.n_layers, batch, 72, hkv, D, dtype=torch.bfloat16, device=device)
         self.v_tail_all = torch.empty_like(self.k_tail_all)
-        for layer in range(LAYERS):
+        ch_idx = [torch.randperm(D, generator=torch.Generator().manual_seed(seed + 1 + h))[:4].to(device) for h in range(hkv)]
+        for layer in range(self.n_layers):
             pl = alloc_planes(n_pages, n_groups, hkv, D, page_size=PAGE, outliers_per_vector=K_OUT,
                               kv_outlier_map=True, device=device)
             cg.manual_seed(seed + layer)
@@ -224,8 +276,7 @@ class LayerStack:
                     K = torch.randn(n, hkv, D, generator=cg, device=device)
                     V = torch.randn(n, hkv, D, generator=cg, device=device)
                     for h in range(hkv):
-                        idx = torch.randperm(D, generator=torch.Generator().manual_seed(seed + 1 + h))[:4].to(device)
-                        K[:, h, idx] *= MAG
+                        K[:, h, ch_idx[h]] *= MAG
                     ommx_pack_kv_into(K.bfloat16(), V.bfloat16(), pl,
                                       dst_pages=self.req_to_token[b, t0 // PAGE:(t0 + n) // PAGE].contiguous(),
                                       dst_groups=self.req_to_group[b, t0 // 32:(t0 + n) // 32].contiguous(),
@@ -236,8 +287,8 @@ class LayerStack:
             self.layers.append({"planes": pl, "k_tail": tails_k, "v_tail": tails_v, "q": q})
         self.b_seq_len = torch.full((batch,), P, dtype=torch.int32, device=device)
         self.b_tail_len = torch.full((batch,), ctx - P, dtype=torch.int32, device=device)
-        self.o = torch.zeros(LAYERS, batch, hq, D, dtype=torch.float32, device=device)
-        self.lse = torch.zeros(LAYERS, batch, hq, dtype=torch.float32, device=device)
+        self.o = torch.zeros(self.n_layers, batch, hq, D, dtype=torch.float32, device=device)
+        self.lse = torch.zeros(self.n_layers, batch, hq, dtype=torch.float32, device=device)
         self.ws = None
         self.splits = 0
 
@@ -252,18 +303,23 @@ class LayerStack:
         self.splits = _auto_num_kv_splits(max(P, 1), self.batch, device=self.device, kv_heads=self.hkv)
         self.ws = torch.empty(self.batch, self.hq, self.splits + 1, D + 1, dtype=torch.float32, device=self.device)
 
-    def decode_layer(self, i, q=None, stage=0):
-        from open_ommx_serve_b200.attention.paged_decode import ommx_paged_decode_attention_canonical
+    def decode_layer(self, i, q=None, stage=0, fn=None, o=None, lse=None):
+        """One decode call on layer i through this package's entry, or through `fn` (the reference's
+        Triton launcher, which takes the same arguments)."""
         L = self.layers[i]
         p = L["planes"]
-        ommx_paged_decode_attention_canonical(
-            L["q"] if q is None else q, p["k_base"], p["k_scale"], p["k_zp"], None, p["k_oval"],
-            p["v_main"], p["v_scale"], p["v_zp"], L["k_tail"], L["v_tail"], self.b_tail_len,
-            self.o[i], self.lse[i], self.req_to_token, self.req_to_group, self.b_seq_len,
-            sm_scale=D ** -0.5, page_size=PAGE, k_outliers_per_vector=K_OUT, bitmap_read=True,
-            k_obmp=p["k_obmp"], k_fp4_mapscale=p["k_fp4_mapscale"], k_fp4_mapcenter=p["k_fp4_mapcenter"],
-            kv_outlier_map=True, kv_int8_scale=True, num_kv_splits=self.splits,
-            max_seq_len=self.cur_packed, max_tail_len=self.cur_tail, attn_logits=self.ws, _stage=stage)
+        kw = {}
+        if fn is None:
+            from open_ommx_serve_b200.attention.paged_decode import ommx_paged_decode_attention_canonical as fn
+            kw = dict(num_kv_splits=self.splits, attn_logits=self.ws, _stage=stage)
+        fn(L["q"] if q is None else q, p["k_base"], p["k_scale"], p["k_zp"], None, p["k_oval"],
+           p["v_main"], p["v_scale"], p["v_zp"], L["k_tail"], L["v_tail"], self.b_tail_len,
+           self.o[i] if o is None else o, self.lse[i] if lse is None else lse,
+           self.req_to_token, self.req_to_group, self.b_seq_len,
+           sm_scale=D ** -0.5, page_size=PAGE, k_outliers_per_vector=K_OUT, bitmap_read=True,
+           k_obmp=p["k_obmp"], k_fp4_mapscale=p["k_fp4_mapscale"], k_fp4_mapcenter=p["k_fp4_mapcenter"],
+           kv_outlier_map=True, kv_int8_scale=True,
+           max_seq_len=self.cur_packed, max_tail_len=self.cur_tail, **kw)
 
 
 def timed_graph(fn, steps, warmup, flush, torch):
@@ -292,6 +348,56 @@ def timed_graph(fn, steps, warmup, flush, torch):
     return times
 
 
+class TritonReference:
+    """The reference's own Triton launcher (baseline/_ref, unmodified) on this GPU, same planes."""
+
+    def __init__(self):
+        self.fn, self.why, self.spent = None, None, 0.0
+        ref = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isfile(os.path.join(ref, "ommx_gpu_serve", "attention", "paged_decode.py")):
+            self.why = "baseline/_ref not built"
+            return
+        try:
+            if ref not in sys.path:
+                sys.path.insert(0, ref)
+            import triton  # noqa: F401
+            from ommx_gpu_serve.attention import paged_decode as rdec
+            if not rdec.is_available():
+                raise RuntimeError("reference reports its Triton backend unavailable")
+            self.fn = rdec.ommx_paged_decode_attention_canonical
+        except Exception as exc:
+            self.why = f"{type(exc).__name__}: {str(exc)[:160]}"
+
+    def time_layer(self, stack, flush, torch, layer=0):
+        """Median µs of one layer's decode by the reference's protocol (bench/bench_decode_kernel.py:233-256:
+        CUDA-graph replay, 3 warm-up + 20 measured, median) with L2 flushed before every replay; also
+        returns max-abs / cosine of this package's output against the Triton output on that layer."""
+        if self.fn is None or self.spent > TRITON_BUDGET_S:
+            return None
+        t_wall = time.time()
+        try:
+            o = torch.zeros_like(stack.o[layer])
+            lse = torch.zeros_like(stack.lse[layer])
+
+            def launch():
+                stack.decode_layer(layer, fn=self.fn, o=o, lse=lse)
+
+            launch()                                   # JIT compile + autotune outside the capture
+            torch.cuda.synchronize()
+            ms = sorted(timed_graph(launch, 20, 3, flush, torch))
+            stack.decode_layer(layer)
+            torch.cuda.synchronize()
+            diff = float((stack.o[layer] - o).abs().max().item())
+            cos = float(torch.nn.functional.cosine_similarity(stack.o[layer].flatten().double(), o.flatten().double(), dim=0).item())
+            return {"us": 0.5 * (ms[9] + ms[10]) * 1e3, "max_abs_ours_vs_triton": diff, "cos_ours_vs_triton": cos}
+        except Exception as exc:
+            self.why = f"{type(exc).__name__}: {str(exc)[:160]}"
+            self.fn = None
+            return None
+        finally:
+            self.spent += time.time() - t_wall
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -302,7 +408,8 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     hkv, hq = HKV // world, HQ // world
-    stack = LayerStack(args.ctx, 1, hkv, hq, device)
+    contexts = [c for c in CONTEXTS if c <= max(args.ctx, args.max_ctx)] if args.all_contexts else [args.ctx]
+    stack = LayerStack(max(contexts), 1, hkv, hq, device)
     if args.profile:
         # plain eager launches for a profiler: no graph, no timing, no JSON line
         stack.set_context(args.ctx)
@@ -315,6 +422,7 @@ def run_ours(args, rank, world, local_rank):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     gathered = torch.zeros(LAYERS, world, 1, hq, D, dtype=torch.float32, device=device) if world > 1 else None
     lib = _lib.load()
+    triton_ref = TritonReference() if (rank == 0 and not args.no_triton) else None
 
     def step_full():
         for i in range(LAYERS):
@@ -325,6 +433,14 @@ def run_ours(args, rank, world, local_rank):
     def step_stage1():
         for i in range(LAYERS):
             stack.decode_layer(i, stage=1)
+
+    def step_stage2():
+        for i in range(LAYERS):
+            stack.decode_layer(i, stage=2)
+
+    def step_gather():
+        for i in range(LAYERS):
+            sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
 
     def barrier():
         torch.cuda.synchronize()
@@ -341,7 +457,6 @@ def run_ours(args, rank, world, local_rank):
 
     per_ctx = {}
     results = {}
-    contexts = [c for c in CONTEXTS if c <= args.ctx] if args.all_contexts else [args.ctx]
     sampler = ClockSampler(local_rank)
     for ctx in contexts:
         stack.set_context(ctx)
@@ -353,25 +468,38 @@ def run_ours(args, rank, world, local_rank):
             sampler.__enter__()
         t_full = timed_graph(step_full, k_steps, args.warmup, flush, torch)
         barrier()
-        launches_step = int(lib.ommx_b200_launch_count()) // (2 + 0)   # eager warm-up + capture each ran the step once
+        launches_step = int(lib.ommx_b200_launch_count()) // 2   # eager warm-up + capture each ran the step once
         t_s1 = timed_graph(step_stage1, k_steps, args.warmup, flush, torch)
         barrier()
         if head:
             sampler.__exit__()
+        t_s2 = timed_graph(step_stage2, max(3, k_steps // 2), args.warmup, flush, torch)
+        barrier()
+        ms_ag = None
+        if world > 1:
+            t_ag = timed_graph(step_gather, max(3, k_steps // 2), args.warmup, flush, torch)
+            barrier()
+            ms_ag = reduce_max(sum(t_ag) / len(t_ag))
         ms_step = reduce_max(sum(t_full) / len(t_full))
         ms_s1 = reduce_max(sum(t_s1) / len(t_s1))
+        ms_s2 = reduce_max(sum(t_s2) / len(t_s2))
         bytes_layer = algorithmic_bytes(ctx, 1, HKV)             # whole job (all ranks)
         bytes_launch = algorithmic_bytes(ctx, 1, hkv) - (ctx - packed_len(ctx)) * hkv * D * 4   # stage 1 reads planes only
+        tri = triton_ref.time_layer(stack, flush, torch) if (triton_ref is not None and world == 1) else None
         per_ctx[str(ctx)] = {
             "us_per_layer": ms_step * 1e3 / LAYERS, "hbm_gbs": bytes_layer / (ms_step / LAYERS) / 1e6,
             "stage1_us": ms_s1 * 1e3 / LAYERS, "stage1_gbs": bytes_launch / (ms_s1 / LAYERS) / 1e6,
+            "stage2_us": ms_s2 * 1e3 / LAYERS,
+            "allgather_us": None if ms_ag is None else ms_ag * 1e3 / LAYERS,
             "splits": stack.splits, "bytes_per_layer": bytes_layer,
+            "triton_b200_us": None if tri is None else tri["us"],
+            "triton_b200": tri,
             "h200_published_us": H200_PUBLISHED_US.get(ctx)}
         if head:
             results = {"ms_step": ms_step, "ms_s1": ms_s1, "bytes_layer": bytes_layer,
                        "bytes_launch": bytes_launch, "launches_step": launches_step}
 
-    # ---- end to end through the public Python entry with host buffers (no graph) ----
+    # ---- end to end through the public Python entry with host buffers ----
     stack.set_context(args.ctx)
     # the step's inputs (q and the new K/V row of every layer) in one pinned buffer, its outputs in another
     n_q, n_kv = hq * D, hkv * D
@@ -410,6 +538,17 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms_e2e = reduce_max(sum(e2e_graph_times) / len(e2e_graph_times))
 
+    # ---- the other configurations, as sub-records of the same line ----
+    workloads = {}
+    del stack
+    torch.cuda.empty_cache()
+    if not args.no_workloads:
+        peak, _ = measured_peak_gbs()
+        workloads["llama70b_b8_32k"] = workload_llama70b(args, device, world, flush, reduce_max, barrier, peak, gathered_world=world)
+        if world == 1:
+            workloads["batch32_store_decode"] = workload_batch32(args, device, flush, peak)
+            workloads["prefill_pack_8k"] = workload_prefill_pack(args, device, flush, peak)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -419,10 +558,7 @@ def run_ours(args, rank, world, local_rank):
     ach = results["bytes_launch"] / (results["ms_s1"] / LAYERS) / 1e6
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        r = cpu_reference_layer(args.ctx, steps=2, warmup=1)
-        cpu = {"value": r["us_per_layer"], "unit": "us", "cores": r["threads"], "kind": "port",
-               "sample": f"1 of {LAYERS} layers at ctx {args.ctx}: fake-quantize K+V ({r['quant_ms']:.0f} ms) + dense "
-                         f"attention ({r['attn_ms']:.1f} ms), median of 2; host has {r['cpu_count']} cpus"}
+        cpu = cpu_baseline_record(cpu_reference_layer(args.ctx, steps=2, warmup=1), args.ctx, 2)
     line = {
         "metric": "ommx_decode_attn_us_per_layer", "value": us_layer, "unit": "us", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": results["ms_step"],
@@ -441,7 +577,7 @@ def run_ours(args, rank, world, local_rank):
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                      "traffic": results["bytes_launch"] * NCU_TRAFFIC_RATIO, "peak_kind": peak_kind,
                      "traffic_note": "dram__bytes_read+write of one stage-1 launch under ncu at ctx 65536, 8 kv heads "
-                                     "(70.33 MB against 69.14 MB algorithmic), scaled by algorithmic bytes for other shapes",
+                                     "over its algorithmic bytes (profiles/decode_stage1_64k_b1.md), scaled by algorithmic bytes for other shapes",
                      "kernel": "decode_stage1_kernel",
                      "algorithmic_bytes_per_launch": results["bytes_launch"],
                      "us_per_launch": results["ms_s1"] * 1e3 / LAYERS,
@@ -456,6 +592,9 @@ def run_ours(args, rank, world, local_rank):
                         "eager_value is the same step launched from Python"},
         "gpu_launches": results["launches_step"] * args.steps,
         "contexts": per_ctx,
+        "triton_reference": None if triton_ref is None else {"available": triton_ref.fn is not None, "note": triton_ref.why,
+                                                             "seconds_spent": round(triton_ref.spent, 1)},
+        "workloads": workloads,
         "clocks": sampler.summary(),
     }
     print(json.dumps(line))
@@ -463,22 +602,65 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def run_batch32(args, local_rank):
-    """Secondary workload (not the headline line): batch 32, ragged contexts 1K..32K, split partition 512,
-    every step stores one new token per sequence through the device-resident pool and decodes, per layer."""
+# ───────────────────────────── sub-record workloads ─────────────────────────────
+
+def workload_llama70b(args, device, world, flush, reduce_max, barrier, peak, gathered_world=1):
+    """Llama-3.1-70B head geometry (64 query heads, 8 kv heads, GQA 8), batch 8 at 32K context, the kv heads
+    sharded over the ranks (all 8 on one GPU at N=1, one per GPU at N=8).  A 4-layer stack stands for the
+    80 layers (each layer's planes exceed L2 many times over at N=1; L2 is flushed between steps)."""
+    import torch
+    from open_ommx_serve_b200 import sharding
+    layers, B, ctx = (4 if world == 1 else 8), 8, 32768
+    hkv, hq = HKV // world, 64 // world
+    stack = LayerStack(ctx, B, hkv, hq, device, seed=7, layers=layers)
+    stack.set_context(ctx)
+    gathered = torch.zeros(layers, world, B, hq, D, dtype=torch.float32, device=device) if world > 1 else None
+
+    def step():
+        for i in range(layers):
+            stack.decode_layer(i)
+            if world > 1:
+                sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
+
+    def step_s1():
+        for i in range(layers):
+            stack.decode_layer(i, stage=1)
+
+    steps = max(3, min(args.steps, 10))
+    barrier()
+    ms = reduce_max(sum(t := timed_graph(step, steps, args.warmup, flush, torch)) / len(t))
+    barrier()
+    ms1 = reduce_max(sum(t := timed_graph(step_s1, steps, args.warmup, flush, torch)) / len(t))
+    barrier()
+    p = packed_len(ctx)
+    bytes_layer = B * (p * HKV * unit_bytes(K_OUT) + (ctx - p) * HKV * D * 4)
+    bytes_launch = B * p * hkv * unit_bytes(K_OUT)
+    ach = bytes_launch / (ms1 / layers) / 1e6
+    rec = {"config": {"workload": f"llama3.1-70b head geometry (64 q heads, 8 kv heads), batch {B}, ctx {ctx}, {layers}-layer stack "
+                                  f"standing for 80 layers, {hkv} kv head(s) per GPU", "splits": stack.splits},
+           "us_per_layer": ms * 1e3 / layers, "hbm_gbs": bytes_layer / (ms / layers) / 1e6,
+           "tokens_per_s_80_layers": B / (ms / layers * 80 * 1e-3),
+           "roofline": {"bound": "hbm", "kernel": "decode_stage1_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
+                        "frac": ach / peak, "us_per_launch": ms1 * 1e3 / layers, "algorithmic_bytes_per_launch": bytes_launch}}
+    del stack
+    torch.cuda.empty_cache()
+    return rec
+
+
+def workload_batch32(args, device, flush, peak, layers=8):
+    """Batch 32, ragged contexts 1K..32K (seed 42), split partition 512; every step stores one new token per
+    sequence through the device-resident pool and decodes, per layer."""
     import torch
     from open_ommx_serve_b200 import _lib, ommx_paged_decode_attention_canonical
     from open_ommx_serve_b200.attention.kv_pool import MultiSeqKVPool
     from open_ommx_serve_b200.attention.kv_window import WindowSpec
 
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
     B, max_len, part = 32, 32768 + 256, 512
     lens = torch.randint(1024, 32769, (B,), generator=torch.Generator().manual_seed(42)).tolist()
     win = WindowSpec(8, 32, 32, PAGE)
     pools = []
     cg = torch.Generator(device=device)
-    for layer in range(LAYERS):
+    for layer in range(layers):
         pool = MultiSeqKVPool(D, HKV, B, max_len, outliers_per_vector=K_OUT, window=win, device=device)
         cg.manual_seed(1000 + layer)
         for r, T in enumerate(lens):
@@ -490,11 +672,11 @@ def run_batch32(args, local_rank):
     max_packed = win.packed_len(max_len)
     splits = (max_packed + part - 1) // part
     ws = torch.empty(B, HQ, splits + 1, D + 1, dtype=torch.float32, device=device)
-    q = torch.randn(LAYERS, B, HQ, D, generator=cg, device=device).bfloat16()
-    kn = torch.randn(LAYERS, B, HKV, D, generator=cg, device=device).bfloat16()
-    vn = torch.randn(LAYERS, B, HKV, D, generator=cg, device=device).bfloat16()
-    o = torch.zeros(LAYERS, B, HQ, D, dtype=torch.float32, device=device)
-    lse = torch.zeros(LAYERS, B, HQ, dtype=torch.float32, device=device)
+    q = torch.randn(layers, B, HQ, D, generator=cg, device=device).bfloat16()
+    kn = torch.randn(layers, B, HKV, D, generator=cg, device=device).bfloat16()
+    vn = torch.randn(layers, B, HKV, D, generator=cg, device=device).bfloat16()
+    o = torch.zeros(layers, B, HQ, D, dtype=torch.float32, device=device)
+    lse = torch.zeros(layers, B, HQ, dtype=torch.float32, device=device)
 
     def step():
         for i, pool in enumerate(pools):
@@ -508,26 +690,58 @@ def run_batch32(args, local_rank):
                 kv_outlier_map=True, kv_int8_scale=True, num_kv_splits=splits, max_seq_len=max_packed,
                 max_tail_len=d["max_tail_len"], attn_logits=ws)
 
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     lib = _lib.load()
     lib.ommx_b200_reset_launch_count()
-    sampler = ClockSampler(local_rank)
-    with sampler:
-        times = timed_graph(step, args.steps, args.warmup, flush, torch)
+    steps = max(3, min(args.steps, 10))
+    times = timed_graph(step, steps, args.warmup, flush, torch)
     ms = sum(times) / len(times)
-    packed = sum(win.packed_len(T + args.warmup + args.steps // 2) for T in lens)
-    bytes_layer = packed * HKV * 132 + sum(T - win.packed_len(T) for T in lens) * HKV * D * 4
+    packed = sum(win.packed_len(T + args.warmup + steps // 2) for T in lens)
+    bytes_layer = packed * HKV * unit_bytes(K_OUT) + sum(T - win.packed_len(T) for T in lens) * HKV * D * 4
     status = max(int(p.status.item()) for p in pools)
-    print(json.dumps({
-        "metric": "ommx_store_plus_decode_us_per_layer", "value": ms * 1e3 / LAYERS, "unit": "us", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": f"llama3.1-8b geometry, {LAYERS} layers, batch 32, contexts uniform 1K..32K (seed 42), "
-                               f"split partition 512 ({splits} splits), one new token stored per sequence per step "
-                               "(device-resident pool), then decode; CUDA-graph replay, L2 flushed between steps",
-                   "sum_ctx": sum(lens), "splits": splits},
-        "hbm_gbs": bytes_layer / (ms / LAYERS) / 1e6, "tokens_per_s": B / (ms * 1e-3),
-        "gpu_launches": int(lib.ommx_b200_launch_count()), "device_status": status, "clocks": sampler.summary()}))
+    ach = bytes_layer / (ms / layers) / 1e6
+    rec = {"config": {"workload": f"llama3.1-8b geometry, {layers}-layer stack, batch 32, contexts uniform 1K..32K (seed 42), "
+                                  f"split partition 512 ({splits} splits), one new token stored per sequence per step "
+                                  "(device-resident pool), then decode; CUDA-graph replay, L2 flushed between steps",
+                      "sum_ctx": sum(lens), "splits": splits},
+           "us_per_layer": ms * 1e3 / layers, "hbm_gbs": ach, "tokens_per_s_32_layers": B / (ms / layers * 32 * 1e-3),
+           "roofline": {"bound": "hbm", "kernel": "store + stage 1 + stage 2 of one layer", "achieved": ach, "peak": peak,
+                        "unit": "GB/s", "frac": ach / peak, "algorithmic_bytes_per_layer": bytes_layer},
+           "gpu_launches": int(lib.ommx_b200_launch_count()), "device_status": status}
+    del pools
+    torch.cuda.empty_cache()
+    return rec
+
+
+def workload_prefill_pack(args, device, flush, peak, tokens=8192):
+    """Prefill-time bulk quantize + pack of one 8 192-token K/V chunk (8 kv heads) straight into 16-token pages."""
+    import torch
+    from open_ommx_serve_b200.attention.pack import alloc_planes, ommx_pack_kv_into
+    n_sets = 4
+    g = torch.Generator(device=device).manual_seed(5)
+    Ks = [torch.randn(tokens, HKV, D, generator=g, device=device) for _ in range(n_sets)]
+    for K in Ks:
+        K[:, :, :4] *= MAG
+    Ks = [K.bfloat16() for K in Ks]
+    Vs = [torch.randn(tokens, HKV, D, generator=g, device=device).bfloat16() for _ in range(n_sets)]
+    pls = [alloc_planes(tokens // PAGE, tokens // 32, HKV, D, page_size=PAGE, outliers_per_vector=K_OUT,
+                        kv_outlier_map=True, device=device) for _ in range(n_sets)]
+    pages = torch.randperm(tokens // PAGE, generator=torch.Generator().manual_seed(1)).to(torch.int32).to(device)
+    groups = torch.randperm(tokens // 32, generator=torch.Generator().manual_seed(2)).to(torch.int32).to(device)
+
+    def step():
+        for K, V, pl in zip(Ks, Vs, pls):
+            ommx_pack_kv_into(K, V, pl, dst_pages=pages, dst_groups=groups, outliers_per_vector=K_OUT)
+
+    steps = max(3, min(args.steps, 10))
+    times = timed_graph(step, steps, args.warmup, flush, torch)
+    us = sum(times) / len(times) * 1e3 / n_sets
+    nbytes = tokens * HKV * D * 4 + tokens * HKV * unit_bytes(K_OUT)
+    ach = nbytes / us / 1e3
+    return {"config": {"workload": f"bulk quantize + pack of {tokens} tokens x {HKV} kv heads (bf16 K and V in, packed planes out, "
+                                   f"{PAGE}-token pages through a random page table); {n_sets} chunks per step, L2 flushed between steps"},
+            "us_per_chunk": us, "hbm_gbs": ach,
+            "roofline": {"bound": "hbm", "kernel": "pack_k_lane_kernel + pack_v_kernel", "achieved": ach, "peak": peak,
+                         "unit": "GB/s", "frac": ach / peak, "algorithmic_bytes_per_chunk": nbytes}}
 
 
 def main():
@@ -536,13 +750,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--ctx", type=int, default=HEADLINE_CTX)
+    ap.add_argument("--ctx", type=int, default=HEADLINE_CTX, help="context of the headline value")
+    ap.add_argument("--max-ctx", type=int, default=max(CONTEXTS), help="longest context of the per-context table")
     ap.add_argument("--no-all-contexts", dest="all_contexts", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-triton", action="store_true", help="skip timing the reference's Triton kernels")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the sub-record workloads")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers in the stack (32 = the benchmark)")
     ap.add_argument("--profile", action="store_true", help="eager launches only, for ncu (use a small --layers)")
-    ap.add_argument("--workload", default="b1", choices=("b1", "batch32"),
-                    help="b1 = the headline line; batch32 = ragged batch with the per-step store (own JSON line)")
     ap.add_argument("--k", type=int, default=K_OUT, help="outliers per K vector (the headline recipe has 6)")
     ap.add_argument("--mag", type=float, default=MAG, help="factor on the 4 outlier channels of every K head")
     args = ap.parse_args()
@@ -553,15 +768,11 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        if args.steps > 5:
-            args.steps = 5                      # each step is seconds of CPU work
         run_reference(args, rank, world)
         return
     args.warmup = max(3, args.warmup)
-    if args.workload == "batch32":
-        if world == 1:
-            run_batch32(args, local_rank)
-        return
+    if args.profile:
+        args.all_contexts = False
     run_ours(args, rank, world, local_rank)
 
 

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define OMMX_B200_ABI_VERSION 1
+#define OMMX_B200_ABI_VERSION 2
 
 /* host-side argument errors (return values) */
 #define OMMX_E_ARG          (-1)   /* null pointer, bad size, misaligned plane */
@@ -188,17 +188,38 @@ typedef struct ommx_kv_append_args {
     ommx_kv_pool pool;
     const void *k_new, *v_new;        /* bf16 [batch, n_kv_heads, head_dim]; NULL with advance = 0 */
     int64_t new_stride_b, new_stride_h;
-    const int32_t *slots;             /* device int32 [batch]: pool slot of each row, NULL = 0..batch-1 */
+    const void *slots;                /* device [batch]: pool slot of each row, NULL = 0..batch-1 */
     int32_t batch;
-    int32_t advance;                  /* 1: append + pack + advance; 0: only (re)build the decode inputs */
+    int32_t advance;                  /* 1: append + pack + advance; 0: only (re)build the decode inputs;
+                                         2: append + pack, pool.seq_len left alone (the caller advances it) */
     int32_t outlier_select, use_pow2; /* as in ommx_pack_args; outlier_select must be 1 (signed) */
     void *k_tail, *v_tail;            /* out, optional: bf16 [batch, max_tail, n_kv_heads, head_dim] */
     int32_t max_tail;
     int32_t *b_seq_len, *b_tail_len;  /* out, optional: device int32 [batch] */
     int32_t *status;                  /* optional */
+    const void *write_pos;            /* optional, device [batch]: tokens each row's sequence holds before this
+                                         step (the absolute position the new row is written at), instead of
+                                         pool.seq_len[slot]; with advance = 1 seq_len[slot] becomes write_pos + 1.
+                                         This is the (rows, cols) form of MultiSeqKVPool.append_decode_captured
+                                         (attention/kv_pool.py:490-524) and CanonicalKVStore.write_token
+                                         (attention/kv_store.py:361-385). */
+    int32_t index_is_int64;           /* slots and write_pos hold int64 (else int32) */
 } ommx_kv_append_args;
 
 int ommx_b200_kv_append_decode(const ommx_kv_append_args *args, void *stream);
+
+/*
+ * Residual rows by absolute token position: k_tail/v_tail[i, y] = ring row of token tail_idx[i, y] of
+ * sequence slot sel[i] (NULL: slot i).  Replaces _kv_gather_tail (attention/kv_store_ops.py:42-57) as
+ * called by CanonicalKVStore.gather_tail_into (attention/kv_store.py:397-427) and
+ * MultiSeqKVPool.decode_inputs_captured (attention/kv_pool.py:886-936).  sel and tail_idx are device
+ * int32 or int64; k_tail/v_tail are bf16 [batch, rows, n_kv_heads, head_dim], contiguous.  Only
+ * pool->k_hist, v_hist, ring_cap, sink_tokens, num_seqs and the head geometry are read.  A negative
+ * position or a slot outside the pool zero-fills the row and sets a status bit.
+ */
+int ommx_b200_kv_gather_tail(const ommx_kv_pool *pool, const void *sel, const void *tail_idx,
+                             int32_t index_is_int64, int32_t batch, int32_t rows,
+                             void *k_tail, void *v_tail, int32_t *status, void *stream);
 
 /*
  * Split count this library prefers for (max context, batch, local kv heads) on the current

@@ -72,7 +72,8 @@ class KVAppendArgs(C.Structure):
                 ("slots", C.c_void_p), ("batch", C.c_int32), ("advance", C.c_int32),
                 ("outlier_select", C.c_int32), ("use_pow2", C.c_int32),
                 ("k_tail", C.c_void_p), ("v_tail", C.c_void_p), ("max_tail", C.c_int32),
-                ("b_seq_len", C.c_void_p), ("b_tail_len", C.c_void_p), ("status", C.c_void_p)]
+                ("b_seq_len", C.c_void_p), ("b_tail_len", C.c_void_p), ("status", C.c_void_p),
+                ("write_pos", C.c_void_p), ("index_is_int64", C.c_int32)]
 
 
 #: every symbol include/ommx_b200.h declares: name -> (restype, argtypes)
@@ -83,6 +84,8 @@ SYMBOLS = {
     "ommx_b200_decode_stage2": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_decode_static_ws": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_kv_append_decode": (C.c_int, [C.POINTER(KVAppendArgs), C.c_void_p]),
+    "ommx_b200_kv_gather_tail": (C.c_int, [C.POINTER(KVPool), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                           C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "ommx_b200_auto_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
     "ommx_b200_min_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32]),
     "ommx_b200_merge_states": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,

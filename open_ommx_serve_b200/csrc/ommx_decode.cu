@@ -11,19 +11,20 @@
 //                   slots and the copy roles of a stage are tabulated in shared memory once.
 //   15 decode warps build, two per (group, kv head) unit, the unit's sidecar tile: outlier
 //                   deltas (bit walk with clz, FP4 nibble, base code byte) as fp16
-//                   [token][channel], zero-points, and the power-of-two K and V scale factors
-//                   laid out in MMA-fragment order.
+//                   [token][channel], the fp32 q.zp dot products of the unit's query heads, and the
+//                   power-of-two K and V scale factors laid out in MMA-fragment order.
 //   8 MMA warps     own one unit per stage and a private online-softmax state.  All MMAs are
 //                   m16n8k16 fp16 with the 2-bit codes as the A operand - a code field masked in
 //                   place is the fp16 subnormal code * 4^slot * 2^-24, exact and offset-free - and
-//                   the query heads as the 8 columns: logits = codes.(q*2^e) + delta.q + zp.q,
+//                   the query heads as the 8 columns: logits = codes.(q*2^e) + delta.q + (q.zp from the sidecar),
 //                   softmax over token rows, P transposed with movmatrix, output =
 //                   codes^T.(P*2^e_v) + vz^T.P.
 //
 // Numerics follow the reference kernel's rounding points: q*sm_scale rounded to bf16, exact
-// code*2^e products, the outlier delta rounded to bf16, fp32 accumulation, V as exact code*2^e
-// products with the zero-point bias summed apart.  Two points differ inside the gate: q.zp uses
-// the bf16 q*sm_scale instead of fp32 q, and P is rounded to fp16 (11 bits) instead of bf16.
+// code*2^e products, the outlier delta rounded to bf16, q.zp as an fp32 dot product of the raw
+// query with the zero-points (paged_decode.py:1754-1770), fp32 accumulation, V as exact code*2^e
+// products with the zero-point bias summed apart.  One point differs inside the gate: P is rounded
+// to fp16 (11 bits) instead of bf16.
 #include "ommx_common.cuh"
 #include <cuda.h>                       // CUtensorMap (types only; the encoder is looked up at run time)
 #include <mutex>
@@ -44,7 +45,7 @@ constexpr int S1_THREADS = (NCW + NDW + 1) * 32;
 constexpr int REGS_MMA = 128, REGS_DECODE = 56;
 constexpr int MAX_STAGES = 4;           // ring depth (3 when the planes of a stage are large)
 constexpr int DT_STRIDE = 272;          // bytes per sidecar-tile row (256 data + 16 pad)
-constexpr int ROW_ZP = 32;              // K zero-points, fp16, channel order
+constexpr int ROW_ZP = 32;              // q.zp partial sums, fp32: [channel half][8 query heads of the kv head]
 constexpr int ROW_KF = 33;              // K scale factors 2^(e+4), fp16, in code-fragment order
 constexpr int ROW_VF = 34;              // V scale factors, fp16, fragment order (rows 34, 35: two copies)
 constexpr int ROW_ZT = 36;              // V zero-points [scale group][token], fp16 (rows 36, 37: two copies)
@@ -57,7 +58,7 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // about a second of SM 
 struct S1Params {
     const __nv_bfloat16 *q;
     int64_t q_sb, q_sh;
-    int32_t B, Hq, H, gqa;
+    int32_t B, Hq, H, gqa, q_pair_ok;    // q_pair_ok: two adjacent q elements may be fetched as one 32-bit word
     const uint8_t *k_base, *v_main, *v_scale, *v_zp, *k_scale, *k_zp, *k_ms, *k_mc, *k_obmp, *k_oval;
     int32_t ps, ppg, num_pages, num_slots, k_out, nb, use_map;
     const int32_t *b_seq_len;
@@ -464,23 +465,61 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 OMMX_TR(trk + 2);
                 bool clamped_any = false;
                 const bool splice = k_out > 0 && !no_outlier;
-                // ---- first the rows the code and zero-point MMAs read (K factors, K zero-points, V factors and
+                // ---- first the rows the code MMAs and the softmax read (K factors, q.zp sums, V factors and
                 //      zero-points): they are cheap, and the MMA warp starts on them while the deltas are scattered ----
                 const uint32_t e2 = *reinterpret_cast<const uint16_t *>(gb + p.o_ks + h * 128 + d0);
                 const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
                 // this lane's entry in the fragment-ordered K factor row
                 const uint32_t kf_off = ROW_KF * DT_STRIDE + 64u * (2 * hf + (lane >> 4)) + 32u * ((lane >> 3) & 1) + 8u * (lane & 3) + 2u * ((lane >> 2) & 1);
-                uint32_t zph[2];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int e = max((int)(int8_t)(e2 >> (8 * c)), -126);
-                    zph[c] = f16_bits_sat(bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu)));
                     bool cl;
                     const uint32_t fb = pow2_f16_bits(e, cl);
                     clamped_any |= cl;
                     *reinterpret_cast<uint16_t *>(tile + kf_off + 4 * c) = (uint16_t)fb;
                 }
-                *reinterpret_cast<uint32_t *>(tile + ROW_ZP * DT_STRIDE + 2 * d0) = zph[0] | (zph[1] << 16);
+                {   // q.zp of this half's 64 channels for the (up to 8) query heads of the kv head, in fp32 from the
+                    // raw bf16 query, as the reference forms it.  The 8 per-lane partials are summed over the warp by a
+                    // halving exchange (lane bits 4, 3, 2 select the head, then two plain steps): 9 shuffles.
+                    const float zp0 = bf16_bits_to_f32(z2 & 0xFFFFu), zp1 = bf16_bits_to_f32(z2 >> 16);
+                    const __nv_bfloat16 *qh = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa) * p.q_sh + d0;
+                    float v[8];
+#pragma unroll
+                    for (int hd = 0; hd < 8; ++hd) {
+                        v[hd] = 0.f;
+                        if (hd < p.gqa) {
+                            const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qh + (int64_t)hd * p.q_sh);
+                            uint32_t qa, qb;
+                            if (p.q_pair_ok) { const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(q16)); qa = w & 0xFFFFu; qb = w >> 16; }
+                            else { qa = __ldg(q16); qb = __ldg(q16 + 1); }
+                            v[hd] = fmaf(bf16_bits_to_f32(qa), zp0, bf16_bits_to_f32(qb) * zp1);
+                        }
+                    }
+                    float w4[4], w2[2];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const bool up = (lane & 16) != 0;
+                        const float give = up ? v[i] : v[i + 4], keep = up ? v[i + 4] : v[i];
+                        w4[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, give, 16);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const bool up = (lane & 8) != 0;
+                        const float give = up ? w4[i] : w4[i + 2], keep = up ? w4[i + 2] : w4[i];
+                        w2[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, give, 8);
+                    }
+                    float w1;
+                    {
+                        const bool up = (lane & 4) != 0;
+                        const float give = up ? w2[0] : w2[1], keep = up ? w2[1] : w2[0];
+                        w1 = keep + __shfl_xor_sync(0xFFFFFFFFu, give, 4);
+                    }
+                    w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 2);
+                    w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 1);
+                    if ((lane & 3) == 0)                             // lane bits 4,3,2 = head bits 2,1,0
+                        reinterpret_cast<float *>(tile + ROW_ZP * DT_STRIDE)[8 * hf + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = w1;
+                }
                 {   // V side: one token, two scale groups: power-of-two factor and zero-point of each
                     const int copy = it & 1;
                     const int tk = 16 * hf + (lane & 15), cg0 = 2 * (lane >> 4);
@@ -639,7 +678,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     const bool head_ok = g < p.gqa;
     // B fragments of q, fp16.  QS: bf16(q*sm_scale) * 4^-slot for the code MMAs, register r = 8*wi + i holds
     // channels (32j + 16wi + i, + 8), the pair a code word yields in one AND.  QD: plain bf16(q*sm_scale) for
-    // the delta / zero-point MMAs, whose tile columns are channels in natural order.
+    // the delta MMAs, whose tile columns are channels in natural order.
     uint32_t QS[16], QD[16];
     {
         const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (head_ok ? g : 0)) * p.q_sh;
@@ -686,7 +725,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     }
     // per-lane fragment addresses inside the sidecar tile
     const uint32_t a_delta = tile_s + ((lane & 7) + 8 * ((lane >> 3) & 1)) * DT_STRIDE + 16 * (lane >> 4);
-    const uint32_t a_zp = tile_s + ROW_ZP * DT_STRIDE + 16 * ((lane >> 3) & 1);
     const uint8_t *p_kf = tile + ROW_KF * DT_STRIDE + 64 * j;
     // ---- online softmax state of heads 2j and 2j+1 (the two columns this lane holds) ----
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
@@ -726,23 +764,24 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             }
             OMMX_TR(8 * it + 2);
             // The unit's sidecar tile arrives in two steps: first the factor and zero-point rows, then the outlier
-            // deltas.  The code and zero-point MMAs run on the first, while the decode warps still scatter the deltas.
+            // deltas.  The code MMAs run on the first, while the decode warps still scatter the deltas.
             if (!mbar_wait(bar_trows + 8 * unit, consumed & 1u)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
                 break;
             }
             OMMX_TR(8 * it + 3);
-            float Sc[2][4], Sd[2][4], Sz[4];
+            float Sc[2][4], Sd[2][4], Sz[2];
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) { Sc[mt][0] = Sc[mt][1] = Sc[mt][2] = Sc[mt][3] = 0.f; Sd[mt][0] = Sd[mt][1] = Sd[mt][2] = Sd[mt][3] = 0.f; }
-            Sz[0] = Sz[1] = Sz[2] = Sz[3] = 0.f;
-            // Three accumulators take turns, so that neighbours in the instruction stream never wait on each
-            // other, and the zero-point fragment of the next k-step is fetched before the MMAs of this one
+            // Two accumulators take turns, so that neighbours in the instruction stream never wait on each other
             // (the asm statements keep their order, so the order written here is the order issued).
             {
-                uint32_t zf[2];
-                ldsm_x2(a_zp, zf[0], zf[1]);
+                // q.zp of heads 2j and 2j+1: the two channel halves' fp32 partial sums, times sm_scale
+                const float2 za = *reinterpret_cast<const float2 *>(tile + ROW_ZP * DT_STRIDE + 8 * j);
+                const float2 zb = *reinterpret_cast<const float2 *>(tile + ROW_ZP * DT_STRIDE + 32 + 8 * j);
+                Sz[0] = (za.x + zb.x) * p.sm_scale;
+                Sz[1] = (za.y + zb.y) * p.sm_scale;
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const int wi = q >> 2, i0 = 2 * (q & 3);
@@ -752,8 +791,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                         const uint32_t wlo = wi ? kw[0].y : kw[0].x, whi = wi ? kw[1].y : kw[1].x;
                         mma_f16(Sc[0], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
                     }
-                    mma_f16(Sz, zf[0], 0u, zf[1], 0u, QD[2 * q], QD[2 * q + 1]);
-                    if (q < 7) ldsm_x2(a_zp + 32 * (q + 1), zf[0], zf[1]);
                     {
                         const uint32_t wlo = wi ? kw[2].y : kw[2].x, whi = wi ? kw[3].y : kw[3].x;
                         mma_f16(Sc[1], code_pair(wlo, i0), code_pair(whi, i0), code_pair(wlo, i0 + 1), code_pair(whi, i0 + 1), b0, b1);
@@ -1234,15 +1271,23 @@ static EncodeTiledFn encode_tiled_fn() {
 static bool make_code_map(CUtensorMap *m, const void *base, int64_t total_bytes, int rows_per_page) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr || total_bytes < 128 || rows_per_page < 8 || rows_per_page > 256) return false;
-    struct Entry { const void *base; int64_t bytes; int rows; CUtensorMap map; };
-    constexpr int N = 256;
-    static Entry table[N];
+    // 512 sets x 4 ways, keyed by (device, base, bytes, box rows) and compared in full; a set that is
+    // full evicts round-robin.  2048 entries hold the two code planes of a 1000-layer model.
+    struct Entry { const void *base; int64_t bytes; int rows, dev; CUtensorMap map; };
+    constexpr int SETS = 512, WAYS = 4;
+    static Entry table[SETS][WAYS];
+    static uint8_t next_way[SETS];
     static std::mutex mu;
-    const size_t slot = (reinterpret_cast<uintptr_t>(base) >> 8) % N;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    const uintptr_t key = reinterpret_cast<uintptr_t>(base) >> 8;
+    const size_t set = (size_t)((key ^ (key >> 9) ^ (key >> 18) ^ (uintptr_t)dev * 0x9E37u) % SETS);
     {
         std::lock_guard<std::mutex> g(mu);
-        const Entry &e = table[slot];
-        if (e.base == base && e.bytes == total_bytes && e.rows == rows_per_page) { *m = e.map; return true; }
+        for (int w = 0; w < WAYS; ++w) {
+            const Entry &e = table[set][w];
+            if (e.base == base && e.bytes == total_bytes && e.rows == rows_per_page && e.dev == dev) { *m = e.map; return true; }
+        }
     }
     cuuint64_t gdim[2] = {128, (cuuint64_t)(total_bytes / 128)};
     cuuint64_t gstride[1] = {128};
@@ -1253,7 +1298,9 @@ static bool make_code_map(CUtensorMap *m, const void *base, int64_t total_bytes,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     std::lock_guard<std::mutex> g(mu);
-    table[slot].base = base; table[slot].bytes = total_bytes; table[slot].rows = rows_per_page; table[slot].map = *m;
+    Entry &e = table[set][next_way[set]];
+    next_way[set] = (uint8_t)((next_way[set] + 1) % WAYS);
+    e.base = base; e.bytes = total_bytes; e.rows = rows_per_page; e.dev = dev; e.map = *m;
     return true;
 }
 
@@ -1263,20 +1310,32 @@ static size_t stage1_smem(const S1Params &p) {
            + (size_t)p.GS * (4 * p.ppg + 6) * sizeof(CopyDesc);       // the copy roles of one stage come last
 }
 
+constexpr int MAX_DEVICES = 64;
+static int current_device(int *dev) {
+    OMMX_CUDA_TRY(cudaGetDevice(dev));
+    if (*dev < 0 || *dev >= MAX_DEVICES) return fail(OMMX_E_UNSUPPORTED, "device ordinal %d (this build tracks %d devices)", *dev, MAX_DEVICES);
+    return 0;
+}
+
 template <int KOUT>
 static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st) {
-    static size_t attr_smem = 0;                       // one per instantiation
-    static int regs_ok = -1;
-    if (regs_ok < 0) {
+    // function attributes belong to (kernel instantiation, device): one entry per device ordinal
+    static std::atomic<size_t> attr_smem[MAX_DEVICES];
+    static std::atomic<int> regs_state[MAX_DEVICES];   // 0 unknown, 1 enough, 2 too few
+    int dev = 0;
+    if (int rc = current_device(&dev)) return rc;
+    int regs_ok = regs_state[dev].load(std::memory_order_acquire);
+    if (regs_ok == 0) {
         cudaFuncAttributes fa;
         OMMX_CUDA_TRY(cudaFuncGetAttributes(&fa, decode_stage1_kernel<KOUT>));
-        regs_ok = fa.numRegs * S1_THREADS >= NCW * 32 * REGS_MMA + (S1_THREADS - NCW * 32) * REGS_DECODE ? 1 : 0;
+        regs_ok = fa.numRegs * S1_THREADS >= NCW * 32 * REGS_MMA + (S1_THREADS - NCW * 32) * REGS_DECODE ? 1 : 2;
+        regs_state[dev].store(regs_ok, std::memory_order_release);
     }
-    if (!regs_ok) return fail(OMMX_E_CUDA, "stage 1 was compiled with fewer registers than its warp roles need");
-    if (smem > attr_smem) {
+    if (regs_ok != 1) return fail(OMMX_E_CUDA, "stage 1 was compiled with fewer registers than its warp roles need");
+    if (smem > attr_smem[dev].load(std::memory_order_acquire)) {
         OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel<KOUT>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_smem = smem;
+        attr_smem[dev].store(smem, std::memory_order_release);
     }
     decode_stage1_kernel<KOUT><<<grid, S1_THREADS, smem, st>>>(p);
     OMMX_CUDA_TRY(cudaGetLastError());
@@ -1290,6 +1349,7 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     S1Params p;
     p.q = (const __nv_bfloat16 *)a->q; p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h;
     p.B = a->batch; p.Hq = a->n_q_heads; p.H = pl.n_kv_heads; p.gqa = a->n_q_heads / pl.n_kv_heads;
+    p.q_pair_ok = (((uintptr_t)a->q & 3) == 0 && a->q_stride_b % 2 == 0 && a->q_stride_h % 2 == 0) ? 1 : 0;
     p.k_base = (const uint8_t *)pl.k_base; p.v_main = (const uint8_t *)pl.v_main;
     p.v_scale = (const uint8_t *)pl.v_scale; p.v_zp = (const uint8_t *)pl.v_zp;
     p.k_scale = (const uint8_t *)pl.k_scale; p.k_zp = (const uint8_t *)pl.k_zp;
@@ -1387,14 +1447,17 @@ extern "C" int ommx_b200_min_num_kv_splits(int32_t max_seq_len, int32_t page_siz
 
 extern "C" int ommx_b200_auto_num_kv_splits(int32_t max_seq_len, int32_t batch, int32_t n_kv_heads) {
     (void)n_kv_heads;                       // one CTA serves all local kv heads of its token range
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            sm_count = n;
-        else
-            sm_count = 148;
+    static std::atomic<int> sm_counts[ommx::MAX_DEVICES];       // per device ordinal
+    int dev = 0, sm_count = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < ommx::MAX_DEVICES) {
+        sm_count = sm_counts[dev].load(std::memory_order_acquire);
+        if (sm_count == 0) {
+            int n = 0;
+            sm_count = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+            sm_counts[dev].store(sm_count, std::memory_order_release);
+        }
+    } else {
+        (void)cudaGetLastError();
     }
     const int groups = max(1, (max_seq_len + 31) / 32);
     const int b = max(1, batch);

@@ -54,13 +54,31 @@ __device__ __forceinline__ float key_f32(uint32_t k) {
 // residual ring, and its destination comes from the sequence's own page / group-slot tables.
 struct PoolSrc {
     const int32_t *seq;               // null = linear source
-    const int32_t *slots;
+    const void *slots;                // batch row -> sequence slot (int32 or int64), null = identity
+    const void *wpos;                 // batch row -> absolute write position, null = the slot's seq entry
     const int32_t *r2t, *r2g;
     int32_t ring_cap, sink, recent, groups_per_seq, pages_per_seq;
+    int32_t num_seqs, pages_per_group, idx64;
 };
+__device__ __forceinline__ int pool_index(const void *tbl, int is64, int i) {
+    return is64 ? (int) reinterpret_cast<const int64_t *>(tbl)[i] : reinterpret_cast<const int32_t *>(tbl)[i];
+}
+__device__ __forceinline__ int pool_slot(const PoolSrc &ps, int i) { return ps.slots ? pool_index(ps.slots, ps.idx64, i) : i; }
+// tokens the sequence of batch row i holds before this step (its write position)
+__device__ __forceinline__ int pool_pos(const PoolSrc &ps, int i, int slot) {
+    return ps.wpos ? pool_index(ps.wpos, ps.idx64, i) : ps.seq[slot];
+}
 __device__ __forceinline__ int pool_groups_at(const PoolSrc &ps, int seq) {
     const int spare = seq - ps.sink - ps.recent;
     return spare > 0 ? spare / 32 : 0;
+}
+// A sequence slot outside the pool, or a step that would complete a group the sequence's table rows
+// cannot hold (it was stepped past its capacity): such a row is refused - nothing is written for it
+// and its length does not advance - because its group would land in the NEXT sequence's pages.
+__device__ __forceinline__ bool pool_row_refused(const PoolSrc &ps, int seq_slot, int pos_after) {
+    if (seq_slot < 0 || seq_slot >= ps.num_seqs) return true;
+    const int groups = pool_groups_at(ps, pos_after);
+    return groups > ps.groups_per_seq || groups * ps.pages_per_group > ps.pages_per_seq;
 }
 
 struct PackKParams {
@@ -257,10 +275,12 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_lane_kernel(PackKParam
     float x[32];
     int grp = g, seq_slot = 0;                // pool source: group index inside the sequence, sequence slot
     if (p.pool.seq) {
-        seq_slot = p.pool.slots ? p.pool.slots[g] : g;
-        const int pos = p.pool.seq[seq_slot];
+        seq_slot = pool_slot(p.pool, g);
+        if (seq_slot < 0 || seq_slot >= p.pool.num_seqs) return;     // reported by the ring-write kernel
+        const int pos = pool_pos(p.pool, g, seq_slot);
         grp = pool_groups_at(p.pool, pos);
         if (pool_groups_at(p.pool, pos + 1) == grp) return;          // this step completes no group
+        if (pool_row_refused(p.pool, seq_slot, pos + 1)) { if (lane == 0) or_status(p.status, OMMX_ST_BAD_LENGTH); return; }
         const int rec = p.pool.ring_cap - p.pool.sink;
         const int first = (grp * 32) % rec;                           // ring row (behind the sink rows) of token 0
         col += (int64_t)(seq_slot * p.pool.ring_cap + p.pool.sink) * p.stride_token;
@@ -451,10 +471,12 @@ __global__ void __launch_bounds__(128) pack_v_kernel(PackVParams p) {
     int seq_slot = 0;
     if (p.pool.seq) {
         const int i = t / 32, tt = t % 32;                              // batch row, token inside the completed group
-        seq_slot = p.pool.slots ? p.pool.slots[i] : i;
-        const int pos = p.pool.seq[seq_slot];
+        seq_slot = pool_slot(p.pool, i);
+        if (seq_slot < 0 || seq_slot >= p.pool.num_seqs) return;
+        const int pos = pool_pos(p.pool, i, seq_slot);
         const int grp = pool_groups_at(p.pool, pos);
         if (pool_groups_at(p.pool, pos + 1) == grp) return;
+        if (pool_row_refused(p.pool, seq_slot, pos + 1)) { or_status(p.status, OMMX_ST_BAD_LENGTH); return; }
         const int rec = p.pool.ring_cap - p.pool.sink;
         const int rr = (grp * 32 + tt) % rec;
         row += (int64_t)(seq_slot * p.pool.ring_cap + p.pool.sink + rr) * p.stride_token;
@@ -592,10 +614,10 @@ __device__ __forceinline__ int ring_row(const PoolSrc &ps, int pos) {
 // grid (batch), 128 threads: one new K row and one new V row of H*D bf16 each
 __global__ void __launch_bounds__(128) kv_ring_write_kernel(StoreParams p) {
     const int i = blockIdx.x;
-    const int r = p.pool.slots ? p.pool.slots[i] : i;
+    const int r = pool_slot(p.pool, i);
     if (r < 0 || r >= p.num_seqs) { if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_GROUP); return; }
-    const int pos = p.seq_len[r];
-    if (pos < 0) { if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_LENGTH); return; }
+    const int pos = pool_pos(p.pool, i, r);
+    if (pos < 0 || pool_row_refused(p.pool, r, pos + 1)) { if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_LENGTH); return; }
     const int64_t dst = ((int64_t)r * p.pool.ring_cap + ring_row(p.pool, pos)) * p.H * p.D;
     for (int x = threadIdx.x; x < p.H * p.D; x += blockDim.x) {
         const int h = x / p.D, c = x - h * p.D;
@@ -608,13 +630,17 @@ __global__ void __launch_bounds__(128) kv_ring_write_kernel(StoreParams p) {
 // the sequence and writes the two lengths.  Every block derives the lengths from the same old value.
 __global__ void __launch_bounds__(128) kv_finalize_kernel(StoreParams p) {
     const int i = blockIdx.x;
-    const int r = p.pool.slots ? p.pool.slots[i] : i;
+    const int r = pool_slot(p.pool, i);
     if (r < 0 || r >= p.num_seqs) return;
-    const int seq = p.seq_len[r] + (p.advance ? 1 : 0);
+    const int old = pool_pos(p.pool, i, r);
+    const int seq = old + ((p.advance && old >= 0 && !pool_row_refused(p.pool, r, old + 1)) ? 1 : 0);
     const int sink = p.pool.sink;
     const int spare = seq - sink - p.pool.recent;
     const int boundary = spare > 0 ? sink + spare / 32 * 32 : min(sink, seq);
     const int n_sink = min(sink, seq), n_rec = max(seq - boundary, 0);
+    // a residual buffer too small for sink + recent + a partial group would silently drop the newest rows
+    if (n_sink + n_rec > p.max_tail && (p.k_tail || p.b_tail_len) && blockIdx.y == 0 && threadIdx.x == 0)
+        or_status(p.status, OMMX_ST_BAD_LENGTH);
     const int n_tail = min(n_sink + n_rec, p.max_tail);
     if (p.k_tail && p.v_tail) {
         const int HD = p.H * p.D;
@@ -637,8 +663,42 @@ __global__ void __launch_bounds__(128) kv_finalize_kernel(StoreParams p) {
 __global__ void kv_advance_kernel(StoreParams p, int batch) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= batch) return;
-    const int r = p.pool.slots ? p.pool.slots[i] : i;
-    if (r >= 0 && r < p.num_seqs) p.seq_len[r] += 1;
+    const int r = pool_slot(p.pool, i);
+    if (r >= 0 && r < p.num_seqs) {
+        const int old = pool_pos(p.pool, i, r);
+        if (old >= 0 && !pool_row_refused(p.pool, r, old + 1)) p.seq_len[r] = old + 1;
+    }
+}
+
+// Residual rows by caller-supplied absolute token positions (the reference's _kv_gather_tail,
+// attention/kv_store_ops.py:42-57): grid (batch, rows); row y of batch row i is token idx[i*T + y] of
+// sequence slot sel[i], read from its ring row.  A negative position or a slot outside the pool is
+// reported and the row is zero-filled (the reference asserts on the device).
+struct GatherParams {
+    const __nv_bfloat16 *k_hist, *v_hist;
+    const void *sel, *idx;
+    int32_t idx64, T, HD, ring_cap, sink, num_seqs;
+    __nv_bfloat16 *k_tail, *v_tail;
+    int32_t *status;
+};
+__global__ void __launch_bounds__(128) kv_gather_tail_kernel(GatherParams p) {
+    const int i = blockIdx.x;
+    const int r = p.sel ? pool_index(p.sel, p.idx64, i) : i;
+    const bool slot_ok = r >= 0 && r < p.num_seqs;
+    for (int row = blockIdx.y; row < p.T; row += gridDim.y) {
+        const int pos = pool_index(p.idx, p.idx64, i * p.T + row);
+        const bool ok = slot_ok && pos >= 0;
+        if (!ok && threadIdx.x == 0) or_status(p.status, slot_ok ? OMMX_ST_BAD_LENGTH : OMMX_ST_BAD_GROUP);
+        const int rr = pos < p.sink ? pos : p.sink + (pos - p.sink) % (p.ring_cap - p.sink);
+        const uint4 *ks = reinterpret_cast<const uint4 *>(p.k_hist + ((int64_t)(ok ? r : 0) * p.ring_cap + (ok ? rr : 0)) * p.HD);
+        const uint4 *vs = reinterpret_cast<const uint4 *>(p.v_hist + ((int64_t)(ok ? r : 0) * p.ring_cap + (ok ? rr : 0)) * p.HD);
+        uint4 *kd = reinterpret_cast<uint4 *>(p.k_tail + ((int64_t)i * p.T + row) * p.HD);
+        uint4 *vd = reinterpret_cast<uint4 *>(p.v_tail + ((int64_t)i * p.T + row) * p.HD);
+        for (int x = threadIdx.x; x < p.HD / 8; x += blockDim.x) {
+            kd[x] = ok ? ks[x] : make_uint4(0, 0, 0, 0);
+            vd[x] = ok ? vs[x] : make_uint4(0, 0, 0, 0);
+        }
+    }
 }
 
 static int launch_append(const ommx_kv_append_args *a, cudaStream_t st) {
@@ -648,6 +708,8 @@ static int launch_append(const ommx_kv_append_args *a, cudaStream_t st) {
     sp.pool.seq = pool.seq_len; sp.pool.slots = a->slots; sp.pool.r2t = pool.req_to_token; sp.pool.r2g = pool.req_to_group;
     sp.pool.ring_cap = pool.ring_cap; sp.pool.sink = pool.sink_tokens; sp.pool.recent = pool.recent_window;
     sp.pool.groups_per_seq = pool.groups_per_seq; sp.pool.pages_per_seq = pool.pages_per_seq;
+    sp.pool.num_seqs = pool.num_seqs; sp.pool.pages_per_group = 32 / pl.page_size;
+    sp.pool.wpos = a->write_pos; sp.pool.idx64 = a->index_is_int64 ? 1 : 0;
     sp.k_hist = (__nv_bfloat16 *)pool.k_hist; sp.v_hist = (__nv_bfloat16 *)pool.v_hist;
     sp.k_new = (const __nv_bfloat16 *)a->k_new; sp.v_new = (const __nv_bfloat16 *)a->v_new;
     sp.new_sb = a->new_stride_b; sp.new_sh = a->new_stride_h;
@@ -699,7 +761,7 @@ static int launch_append(const ommx_kv_append_args *a, cudaStream_t st) {
         OMMX_CUDA_TRY(cudaGetLastError());
         count_launch();
     }
-    if (a->advance) {
+    if (a->advance == 1) {
         kv_advance_kernel<<<(B + 127) / 128, 128, 0, st>>>(sp, B);
         OMMX_CUDA_TRY(cudaGetLastError());
         count_launch();
@@ -787,4 +849,27 @@ extern "C" int ommx_b200_kv_append_decode(const ommx_kv_append_args *a, void *st
                       ((uintptr_t)pool.k_hist & 15) || ((uintptr_t)pool.v_hist & 15)))
         return fail(OMMX_E_ARG, "kv_append: residual buffers need max_tail > 0 and 16-byte alignment");
     return launch_append(a, (cudaStream_t)stream);
+}
+
+extern "C" int ommx_b200_kv_gather_tail(const ommx_kv_pool *pool, const void *sel, const void *tail_idx,
+                                        int32_t index_is_int64, int32_t batch, int32_t rows,
+                                        void *k_tail, void *v_tail, int32_t *status, void *stream) {
+    using namespace ommx;
+    if (!pool || !tail_idx || !k_tail || !v_tail) return fail(OMMX_E_ARG, "kv_gather_tail: null pointer");
+    if (!pool->k_hist || !pool->v_hist) return fail(OMMX_E_ARG, "kv_gather_tail: the pool has no residual ring");
+    if (batch <= 0 || rows <= 0) return fail(OMMX_E_ARG, "kv_gather_tail: batch=%d rows=%d", batch, rows);
+    const int HD = pool->planes.n_kv_heads * pool->planes.head_dim;
+    if (HD <= 0 || HD % 8 != 0 || ((uintptr_t)k_tail & 15) || ((uintptr_t)v_tail & 15) ||
+        ((uintptr_t)pool->k_hist & 15) || ((uintptr_t)pool->v_hist & 15))
+        return fail(OMMX_E_ARG, "kv_gather_tail: rows must be whole 16-byte pieces on 16-byte aligned buffers");
+    if (pool->ring_cap - pool->sink_tokens <= 0) return fail(OMMX_E_ARG, "kv_gather_tail: ring_cap=%d sink=%d", pool->ring_cap, pool->sink_tokens);
+    GatherParams g;
+    g.k_hist = (const __nv_bfloat16 *)pool->k_hist; g.v_hist = (const __nv_bfloat16 *)pool->v_hist;
+    g.sel = sel; g.idx = tail_idx; g.idx64 = index_is_int64 ? 1 : 0; g.T = rows; g.HD = HD;
+    g.ring_cap = pool->ring_cap; g.sink = pool->sink_tokens; g.num_seqs = pool->num_seqs;
+    g.k_tail = (__nv_bfloat16 *)k_tail; g.v_tail = (__nv_bfloat16 *)v_tail; g.status = status;
+    kv_gather_tail_kernel<<<dim3(batch, rows < 8 ? rows : 8), 128, 0, (cudaStream_t)stream>>>(g);
+    OMMX_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return 0;
 }
