@@ -97,7 +97,9 @@ class CanonicalKVStore:
 
     def append(self, k: torch.Tensor, v: torch.Tensor) -> None:
         """One decode step's K/V row ``[H, D]``: ring write, pack of a completed group, lengths."""
+        counted = self.packed_groups
         self.pool.append_decode_batched([0], k.reshape(1, self.H, self.D), v.reshape(1, self.H, self.D))
+        self.packed_groups = counted            # the reference counts completed groups in maybe_regroup(), not here
 
     def write_token(self, pos: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
         """Capture-safe row write at the device-side absolute position ``pos`` (``[1]`` int64 or int32): ring

@@ -444,6 +444,21 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             uint8_t *tile = s_tiles + unit * DT_BYTES;
             const int s = ring_slot(it, NS);
             const uint32_t ph = ring_phase(it, NS);
+            // This lane's two raw query values (channels 64hf + 2*lane, +1) of the kv head's query heads, for the
+            // fp32 q.zp sums; requested before the waits below so that the loads are in flight meanwhile.
+            uint32_t qpair[8];
+            {
+                const __nv_bfloat16 *qh = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa) * p.q_sh + 64 * hf + 2 * lane;
+#pragma unroll
+                for (int hd = 0; hd < 8; ++hd) {
+                    qpair[hd] = 0u;
+                    if (hd < p.gqa) {
+                        const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qh + (int64_t)hd * p.q_sh);
+                        if (p.q_pair_ok) qpair[hd] = __ldg(reinterpret_cast<const uint32_t *>(q16));
+                        else qpair[hd] = (uint32_t)__ldg(q16) | ((uint32_t)__ldg(q16 + 1) << 16);
+                    }
+                }
+            }
             if (!mbar_wait(bar_full + 8 * s, ph)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
@@ -483,19 +498,10 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     // raw bf16 query, as the reference forms it.  The 8 per-lane partials are summed over the warp by a
                     // halving exchange (lane bits 4, 3, 2 select the head, then two plain steps): 9 shuffles.
                     const float zp0 = bf16_bits_to_f32(z2 & 0xFFFFu), zp1 = bf16_bits_to_f32(z2 >> 16);
-                    const __nv_bfloat16 *qh = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa) * p.q_sh + d0;
                     float v[8];
 #pragma unroll
-                    for (int hd = 0; hd < 8; ++hd) {
-                        v[hd] = 0.f;
-                        if (hd < p.gqa) {
-                            const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qh + (int64_t)hd * p.q_sh);
-                            uint32_t qa, qb;
-                            if (p.q_pair_ok) { const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(q16)); qa = w & 0xFFFFu; qb = w >> 16; }
-                            else { qa = __ldg(q16); qb = __ldg(q16 + 1); }
-                            v[hd] = fmaf(bf16_bits_to_f32(qa), zp0, bf16_bits_to_f32(qb) * zp1);
-                        }
-                    }
+                    for (int hd = 0; hd < 8; ++hd)
+                        v[hd] = fmaf(bf16_bits_to_f32(qpair[hd] & 0xFFFFu), zp0, bf16_bits_to_f32(qpair[hd] >> 16) * zp1);
                     float w4[4], w2[2];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {

@@ -19,6 +19,7 @@ def _run_and_check(case, **kw):
     gate, cosine 0.999 / rel-L2 0.02, against fp64 attention over the dequantized cache."""
     lse_atol = kw.pop("lse_atol", 2e-2)
     max_abs = kw.pop("max_abs", 2e-2)
+    lse_atol_fp32 = kw.pop("lse_atol_fp32", 5e-2)
     o, lse = case.run(**kw)
     ctx = str(case.seq_lens[:6])
     # every GQA width runs the reference's split-PV arithmetic (exact code*scale products, zero-point bias
@@ -28,7 +29,9 @@ def _run_and_check(case, **kw):
     np.testing.assert_allclose(lse.cpu().numpy(), want_lse, atol=lse_atol, rtol=0)
     f_o, f_lse = case.oracle()
     check_fp32(o, f_o, ctx="fp32 " + ctx)
-    np.testing.assert_allclose(lse.cpu().numpy(), f_lse, atol=max(5e-2, 1.5 * lse_atol), rtol=0)
+    # against exact attention the reference's own rounding of q*sm_scale to bf16 shows in lse in proportion to the
+    # logit magnitude (|q.k| * 2^-9): a few 1e-2 with the x12 outlier channels, up to ~0.1 at x30
+    np.testing.assert_allclose(lse.cpu().numpy(), f_lse, atol=lse_atol_fp32, rtol=0)
     return o, lse
 
 
@@ -81,7 +84,7 @@ def test_decode_head_geometries(H, Hq):
 @pytest.mark.parametrize("k", [0, 2, 3, 4, 6, 8, 9, 10, 12, 16])
 @pytest.mark.parametrize("mag", [4.0, 30.0])
 def test_decode_outlier_sweep(k, mag):
-    _run_and_check(Case([2048], seed=k + 1, k=k, mag=mag))
+    _run_and_check(Case([2048], seed=k + 1, k=k, mag=mag), lse_atol_fp32=5e-2 if mag < 20 else 0.2)
 
 
 def test_decode_base_shared_outlier_map():
