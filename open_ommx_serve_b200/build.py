@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libommx_b200.so")
 SOURCES = ("ommx_capi.cu", "ommx_pack.cu", "ommx_decode.cu")
-HEADERS = ("ommx_common.cuh", "ommx_tables.inc", os.path.join("..", "..", "include", "ommx_b200.h"))
+HEADERS = ("ommx_common.cuh", "ommx_decode_tc.cuh", "ommx_tables.inc", os.path.join("..", "..", "include", "ommx_b200.h"))
 NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC")
 

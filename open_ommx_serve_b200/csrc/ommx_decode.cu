@@ -28,6 +28,8 @@
 #include "ommx_common.cuh"
 #include <cuda.h>                       // CUtensorMap (types only; the encoder is looked up at run time)
 #include <mutex>
+#include <stdlib.h>
+#include <string.h>
 
 namespace ommx {
 
@@ -1349,6 +1351,18 @@ static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st)
     return 0;
 }
 
+}  // namespace ommx
+#include "ommx_decode_tc.cuh"
+namespace ommx {
+
+// Which stage-1 kernel serves a call: the tensor-core kernel where its shared-memory plan fits (4 or 8 local kv
+// heads with GQA <= 4, or fewer heads at any GQA <= 8), the register-operand kernel otherwise and for the
+// differential-timing knobs.  OMMX_B200_STAGE1=legacy|tc overrides (tc still falls back when the shape is not served).
+static int stage1_choice() {
+    const char *e = getenv("OMMX_B200_STAGE1");                       // read per call: cheap, and a test can flip it
+    return (e && !strcmp(e, "legacy")) ? 0 : 1;
+}
+
 static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     if (a->max_seq_len <= 0) return 0;                                   // tail-only decode
     const ommx_kv_planes &pl = a->planes;
@@ -1391,6 +1405,20 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.gb_bytes = (p.gb_bytes + round_to - 1) / round_to * round_to;
     p.stage_bytes = p.GS * p.gb_bytes;
     p.abl = a->abl_flags;
+    if (stage1_choice() == 1 && p.abl == 0 && p.gqa <= 8) {
+        TcParams T;
+        T.s = p;
+        T.s.GS = 1;
+        T.s.stage_bytes = p.gb_bytes;
+        const int gqap = p.gqa <= 4 ? 4 : 8;
+        const int per_max = ((a->max_seq_len + a->num_kv_splits - 1) / a->num_kv_splits + 31) / 32;   // groups of the longest split
+        const size_t tsmem = tc_layout(T, gqap, per_max + 1);
+        if (tsmem != 0 && tsmem <= 232448) {
+            dim3 tgrid(a->num_kv_splits, a->batch);
+            if (gqap == 4) return H == 8 ? launch_tc<4, true>(T, tgrid, tsmem, st) : launch_tc<4, false>(T, tgrid, tsmem, st);
+            return H == 8 ? launch_tc<8, true>(T, tgrid, tsmem, st) : launch_tc<8, false>(T, tgrid, tsmem, st);
+        }
+    }
     // deepest ring that fits the 227 KB a CTA may use
     p.nstages = MAX_STAGES;
     while (p.nstages > 2 && stage1_smem(p) > 232448) --p.nstages;

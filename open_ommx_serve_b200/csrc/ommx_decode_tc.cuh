@@ -1,0 +1,827 @@
+// Split-KV stage 1 on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
+// Included by ommx_decode.cu after its PTX wrappers, S1Params and CopyDesc.
+//
+// Same contract as decode_stage1_kernel (it replaces _canonical_splitkv_stage1,
+// ommx_gpu_serve/attention/paged_decode.py:1255-2284 of the reference): one CTA serves one
+// (split, sequence) pair and all local kv heads of its token range.  What differs is where the
+// arithmetic runs.  A (32-token group, kv head) UNIT is expanded by stateless decode warps into fp16
+// operand tiles in shared memory; one thread issues tcgen05.mma on them; the logits and the output
+// accumulate in tensor memory, so no warp carries accumulator registers or a dependent MMA chain:
+//
+//   producer warp    streams one group (all kv heads) per ring stage, as the register-operand kernel does.
+//   decode warps     per (unit, channel half): K codes -> fp16 c * 2^-16 (a 2-bit field moved to bits 8..9
+//                    of a half-word IS that subnormal: shift + mask, exact) into the K tile
+//                    [4 units x 32 tokens][128 channels]; the unit's outliers written OVER their slots as
+//                    code + bf16(value - base value) / scale, times 2^-16 - the reference's own rounding of the
+//                    outlier delta, no delta tile (fp16 holds such an
+//                    entry to 2^-8 of a code step; for channels with a large scale the rounding residual goes into
+//                    one of 8 spare positions per channel half, whose B entries repeat the channel's); the query
+//                    rows scaled by the unit's power-of-two K scales (B tile); the fp32 q.zp sums; V codes
+//                    -> the V tile (channel-major, fields masked in place); V scale / zero-point factors.
+//   MMA thread       logits  D[4x32 tokens][unit, head] = Ktile . Bq^T            (8 x tcgen05.mma, K = 16)
+//                    output  O[128 channels][scale group, head] += Vtile . P'^T + ones . Pz^T   (4 per unit)
+//                    where P' = P * 2^e_v of the column's scale group and Pz = P * zero-point: a channel
+//                    row reads the columns of its own scale group, the others are never looked at.
+//   4 softmax warps  (one per unit of an item = one quarter of the tensor-memory lanes): logits from tensor
+//                    memory, lane = token; per-head maximum by redux.sync; online softmax whose reference
+//                    maximum moves only when the true one outgrows it by 2^4 (the accumulators are then
+//                    rescaled in tensor memory by all four warps, each on its lane quarter); P' and Pz tiles.
+//
+// Numerics keep the reference's rounding points where they matter for its gate: bf16 q * sm_scale, exact
+// code * 2^e products, fp32 q.zp from the raw query, fp32 accumulation, V as exact code * 2^e products with
+// the outlier delta rounded to bf16, the zero-point bias of V summed apart.  Differences inside the gate: P is
+// rounded to fp16, and an outlier of a channel whose scale is below 4 sits on the fp16 grid of the code tile
+// (2^-8 of a code step).
+#pragma once
+
+namespace ommx {
+
+constexpr int TC_WARPS = 24;
+constexpr int TC_THREADS = TC_WARPS * 32;
+constexpr int TC_W_PRODUCER = 0, TC_W_MMA = 1, TC_W_SOFTMAX = 4;     // softmax warps 4..7: lane quarter = warp & 3
+constexpr int TC_NDW = TC_WARPS - 6;                                  // decode warps: 2, 3, 8..23
+constexpr int TC_FBQ = 4;          // B tile entry = q_c * 2^(e_k + FBQ); logit = D * 2^(16 - FBQ)
+constexpr int TC_FBV = 2;          // P' = P * 2^(e_v + FBV); output = D * 2^(24 - 2 slot - FBV)
+constexpr float TC_RESCALE_LOG2 = 4.f;   // the reference maximum follows the true one once it is 2^4 behind
+constexpr int TC_KCHUNKS = 18;     // 8-position chunks of a K tile row: 16 of channels + 2 of outlier residuals (one per channel half)
+constexpr int TC_KTILE = TC_KCHUNKS * 2048, TC_VTILE = 32768, TC_UNIT_TILE = 8192, TC_ONES = 4096;
+constexpr int TC_FLAG_E = 2;       // channels whose K scale is 2^2 or more get their outliers' rounding residual carried too
+constexpr int TC_RES_SHIFT = 10;   // residual entries are stored times 2^10, their B entries times 2^-10
+constexpr int TC_MAX_STAGES = 8;
+constexpr int TC_SIDE_VF = 0, TC_SIDE_VZ = 1024, TC_SIDE_QZ = 2048, TC_SIDE_BYTES = 2304;
+
+// barrier slots (8 bytes each)
+// A waiter tells phases apart by parity only, so it must never be two completions away from the one it asks for.
+// The MMA thread and the softmax warps visit every item in order and need two barriers per event (item & 1).  The
+// decode warps skip items (tasks are dealt round-robin), so the events they wait for - logits of item i-2 issued
+// and consumed, probabilities of item i-2 written, output MMAs of item i-1 / i-2 landed - rotate over four.
+constexpr int TB_FULL = 0, TB_EMPTY = TC_MAX_STAGES, TB_KREADY = 2 * TC_MAX_STAGES, TB_KFREE = TB_KREADY + 2,
+              TB_VREADY = TB_KFREE + 4, TB_PVDONE = TB_VREADY + 2, TB_DQFULL = TB_PVDONE + 4, TB_DQFREE = TB_DQFULL + 2,
+              TB_PREADY = TB_DQFREE + 2, TB_COUNT = TB_PREADY + 4;
+// words after the barriers
+constexpr int TM_TMEM = 0, TM_ABORT = 1, TM_NEED = 2 /* [2][4] */, TM_CORR = 10 /* [2][4][8] */, TM_FM = 74 /* [8][8] */,
+              TM_FL = 138 /* [8][8] */, TM_WORDS = 202;
+
+struct TcParams {
+    S1Params s;
+    int32_t nb;                      // output accumulator blocks in tensor memory: max(H, 4)
+    int32_t nvb;                     // V tile buffers (1 or 2)
+    int32_t tab_pages, tab_groups;   // capacity of the split's page / group-slot tables
+    uint32_t o_ktile, o_vtile, o_bq, o_ptile, o_ones, o_side, o_q16, o_qraw, o_lut, o_tab, o_bar, o_desc;
+    uint32_t tmem_cols;
+};
+
+// ---- tcgen05 wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    // shared-memory matrix descriptor, no swizzle: start >> 4 | leading-dimension offset | stride offset | version 1
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46);
+}
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N, int a_mn_major, int b_mn_major) {
+    // kind::f16 instruction descriptor: D = f32, A = B = f16, major-ness, N >> 3, M >> 4
+    return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) |
+           ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t addr, uint32_t (&r)[N]) {
+    static_assert(N == 4 || N == 8, "4 or 8 columns");
+    if constexpr (N == 4)
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+    else
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_st(uint32_t addr, const uint32_t (&r)[N]) {
+    if constexpr (N == 4)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+    else
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float redux_max_f32(float x) {
+    float y;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t dup16(uint32_t h) { return h | (h << 16); }
+// fp16 bits of 2^(e + bias): 0 below the subnormal range of interest (e + bias < -14), clamped at 2^15
+__device__ __forceinline__ uint32_t tc_pow2_f16(int e, int bias, bool &clamped, int limit = 30) {
+    int u = e + 15 + bias;
+    clamped = u > limit;
+    u = min(u, limit);
+    return u < 1 ? 0u : (uint32_t)u << 10;
+}
+constexpr int TC_VF_LIMIT = 15 + 11;   // P' = P * 2^(e_v + FBV) with P up to 2^4: the factor stays at or below 2^11
+// channel held at position kpos of a K tile row (and row m of a V tile): a 32-bit code word yields its 16
+// channels as the pairs (i, i + 8), i = 0..7, so positions 2i and 2i + 1 of each 16-block hold channels i and i + 8
+__device__ __forceinline__ int tc_channel_of(int pos) { return (pos & ~15) + ((pos & 15) >> 1) + ((pos & 1) << 3); }
+__device__ __forceinline__ int tc_pos_of(int ch) { return (ch & ~15) + ((ch & 7) << 1) + ((ch >> 3) & 1); }
+__device__ __forceinline__ int tc_vslot(int m) { const int i = (m & 15) >> 1; return i < 5 ? i : i - 5; }
+
+// =================================================================================================
+template <int GQAP, bool NB8>
+__global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const __grid_constant__ TcParams P) {
+    const S1Params &p = P.s;
+    constexpr int N_QK = 4 * GQAP;                   // logit columns: (unit in item, head)
+    constexpr int N_PV = 4 * GQAP;                   // output columns: (V scale group, head)
+    constexpr int BQ_BYTES = TC_KCHUNKS * 16 * N_QK;
+    constexpr int PT_BYTES = N_PV * 64;              // one P' (or Pz) tile: N_PV rows x 32 tokens
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int split = blockIdx.x, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- split range (same rounding as the reference, paged_decode.py:1428-1432) ----
+    const int seq = p.b_seq_len[b];
+    if (seq <= 0) return;
+    const int per = (((seq + p.S - 1) / p.S) + 31) / 32 * 32;
+    const int t0 = split * per;
+    const int t1 = min(t0 + per, seq);
+    if (t1 <= t0) return;
+    const int ntok = t1 - t0;
+    const int ngroups = (ntok + 31) / 32;
+    if (ngroups > P.tab_groups || ngroups * p.ppg > P.tab_pages) {
+        if (threadIdx.x == 0) or_status(p.status, OMMX_ST_BAD_LENGTH);
+        return;
+    }
+    const int H = p.H, NS = p.nstages, gqa = p.gqa;
+    const int n_units = ngroups * H;
+    const int n_items = (n_units + 3) >> 2;
+    const int k_out = p.k_out;
+
+    uint8_t *s_stage = smem;
+    uint8_t *s_ktile = smem + P.o_ktile, *s_vtile = smem + P.o_vtile, *s_bq = smem + P.o_bq, *s_pt = smem + P.o_ptile;
+    uint8_t *s_ones = smem + P.o_ones, *s_side = smem + P.o_side;
+    uint16_t *s_q16 = reinterpret_cast<uint16_t *>(smem + P.o_q16), *s_qraw = reinterpret_cast<uint16_t *>(smem + P.o_qraw);
+    float *s_lut = reinterpret_cast<float *>(smem + P.o_lut);
+    int32_t *s_tab = reinterpret_cast<int32_t *>(smem + P.o_tab);
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + P.o_bar);
+    volatile uint32_t *s_misc = reinterpret_cast<volatile uint32_t *>(s_bar + TB_COUNT);
+    CopyDesc *s_desc = reinterpret_cast<CopyDesc *>(smem + P.o_desc);
+    const uint32_t bar0 = smem_u32(s_bar);
+#define TBAR(slot) (bar0 + 8u * (uint32_t)(slot))
+
+    // ---- prologue, spread over the CTA ----
+    if (threadIdx.x < 16) {
+        const int c = threadIdx.x;
+        const int mi = ((c >> 1) & 3) * 2 + (c & 1);
+        const float mag = mi == 0 ? 0.f : (mi == 1 ? .5f : (float)(2 + (mi & 1)) * (float)(1 << (mi >> 1)) * 0.25f);
+        s_lut[c] = (c & 8) ? -mag : mag;
+    }
+    if (threadIdx.x == 32) {
+        for (int s = 0; s < TC_MAX_STAGES; ++s) {
+            mbar_init(TBAR(TB_FULL + s), 1);
+            mbar_init(TBAR(TB_EMPTY + s), 2 * H);                   // every (unit, half) task of the group
+        }
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(TBAR(TB_KREADY + x), 8);                       // 4 units x 2 halves
+            mbar_init(TBAR(TB_VREADY + x), 8);
+            mbar_init(TBAR(TB_DQFULL + x), 1);
+            mbar_init(TBAR(TB_DQFREE + x), 4);
+        }
+        for (int x = 0; x < 4; ++x) {
+            mbar_init(TBAR(TB_KFREE + x), 1);
+            mbar_init(TBAR(TB_PVDONE + x), 1);
+            mbar_init(TBAR(TB_PREADY + x), 4);
+        }
+        s_misc[TM_ABORT] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TC_W_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(const_cast<uint32_t *>(&s_misc[TM_TMEM]))), "r"(P.tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    if (threadIdx.x == 0 && p.swz != 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_v)) : "memory");
+    }
+    const int cpg = 4 * p.ppg + 6;                                      // copies per group = per stage
+    {
+        const uint32_t page_b = (uint32_t)p.ps * H;
+        const int c = (int)threadIdx.x - 64;
+        if (c >= 0 && c < cpg) {
+            CopyDesc d;
+            d.src = nullptr; d.unit = 0; d.dst = 0; d.tbase = 0; d.tmul = 0; d.gi = 0; d.tok0 = 0;
+            if (c < 4 * p.ppg) {
+                const int pg = c >> 2, plane = c & 3;
+                const uint32_t w = plane < 2 ? 32u : (plane == 2 ? 4u : 8u);
+                d.src = plane == 0 ? p.k_base : (plane == 1 ? p.v_main : (plane == 2 ? p.v_scale : p.v_zp));
+                d.unit = page_b * w;
+                d.dst = (plane == 0 ? 0u : (plane == 1 ? (uint32_t)p.o_vm : (plane == 2 ? (uint32_t)p.o_vs : (uint32_t)p.o_vz))) + (uint32_t)pg * page_b * w;
+                d.tbase = pg; d.tmul = p.ppg; d.tok0 = pg * p.ps;
+                if (p.swz != 0 && plane < 2) d.gi |= (plane + 1) << 8;
+            } else {
+                const int gp = c - 4 * p.ppg;
+                const bool on = gp < 2 || (k_out > 0 && (gp >= 4 || p.use_map));
+                if (on) {
+                    const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 512u : (gp == 5 ? 128u * p.nb : 256u));
+                    d.src = gp == 0 ? p.k_scale : (gp == 1 ? p.k_zp : (gp == 2 ? p.k_ms : (gp == 3 ? p.k_mc : (gp == 4 ? p.k_obmp : p.k_oval))));
+                    d.unit = (uint32_t)H * w;
+                    d.dst = (uint32_t)(gp == 0 ? p.o_ks : (gp == 1 ? p.o_kz : (gp == 2 ? p.o_ms : (gp == 3 ? p.o_mc : (gp == 4 ? p.o_bm : p.o_ov)))));
+                    d.tbase = P.tab_pages; d.tmul = 1;
+                }
+            }
+            s_desc[c] = d;
+        }
+        const int g0 = p.seg_group_base + t0 / 32;
+        const int npages = (ntok + p.ps - 1) / p.ps;
+        const int64_t pg0 = ((int64_t)g0 * 32) / p.ps;
+        for (int i = threadIdx.x; i < npages; i += TC_THREADS) {
+            int64_t pg = load_index(p.r2t, p.tbl64, (int64_t)b * p.r2t_sb + pg0 + i);
+            if (pg < 0 || pg >= p.num_pages) { or_status(p.status, OMMX_ST_BAD_PAGE); pg = 0; }
+            s_tab[i] = (int)pg;
+        }
+        for (int i = TC_THREADS - 1 - (int)threadIdx.x; i < ngroups; i += TC_THREADS) {
+            int64_t sl = load_index(p.r2g, p.tbl64, (int64_t)b * p.r2g_sb + g0 + i);
+            if (sl < 0 || sl >= p.num_slots) { or_status(p.status, OMMX_ST_BAD_GROUP); sl = 0; }
+            s_tab[P.tab_pages + i] = (int)sl;
+        }
+        // query tables, rows = (kv head, padded query head), columns in tile position order:
+        // s_q16 = fp16 of bf16(q * sm_scale) for the B tile, s_qraw = the raw bf16 query for the q.zp sums
+        for (int idx = threadIdx.x; idx < H * GQAP * 128; idx += TC_THREADS) {
+            const int row = idx >> 7, pos = idx & 127;
+            const int h = row / GQAP, j = row - h * GQAP;
+            uint16_t raw = 0, q16 = 0;
+            if (j < gqa) {
+                const __nv_bfloat16 v = p.q[(int64_t)b * p.q_sb + (int64_t)(h * gqa + j) * p.q_sh + tc_channel_of(pos)];
+                raw = __bfloat16_as_ushort(v);
+                q16 = (uint16_t)f16_bits_sat(bf16_round_f32(__bfloat162float(v) * p.sm_scale));
+            }
+            s_qraw[idx] = raw;
+            s_q16[idx] = q16;
+        }
+        // the "ones" operand of the zero-point term: row m carries the factor its V codes carry
+        for (int hw = threadIdx.x; hw < TC_ONES / 2; hw += TC_THREADS)
+            reinterpret_cast<uint16_t *>(s_ones)[hw] = (uint16_t)(1u << (2 * tc_vslot((hw & 1023) >> 3)));
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t tmem = s_misc[TM_TMEM];
+    const uint32_t tm_dqk = tmem, tm_dpv = tmem + 2 * N_QK;
+    const float LOG2E = 1.4426950408889634f;
+    const int TS = H * 32;
+
+    if (warp == TC_W_PRODUCER) {
+        // =========================== producer: one group per stage ===========================
+        for (int g = 0; g < ngroups; ++g) {
+            const int s = g % NS;
+            const uint32_t ph = (uint32_t)(g / NS) & 1u;
+            if (!mbar_wait(TBAR(TB_EMPTY + s), ph ^ 1)) {
+                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
+                break;
+            }
+            uint32_t mine = 0;
+            for (int c = lane; c < cpg; c += 32) {
+                const CopyDesc d = s_desc[c];
+                if (d.unit && 32 * g + d.tok0 < ntok) mine += d.unit;
+            }
+            const uint32_t total = __reduce_add_sync(0xFFFFFFFFu, mine);
+            if (lane == 0) mbar_arrive_expect_tx(TBAR(TB_FULL + s), total);
+            __syncwarp();
+            const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
+            for (int c = lane; c < cpg; c += 32) {
+                const CopyDesc d = s_desc[c];
+                const int kind = d.gi >> 8;
+                if (d.unit && 32 * g + d.tok0 < ntok) {
+                    const int64_t idx = s_tab[d.tbase + g * d.tmul];
+                    if (kind == 0) bulk_g2s(sbase + d.dst, d.src + idx * d.unit, d.unit, TBAR(TB_FULL + s));
+                    else tma_2d_g2s(sbase + d.dst, kind == 1 ? &p.tmap_k : &p.tmap_v, 0, (int32_t)idx * p.rows_per_page, TBAR(TB_FULL + s));
+                }
+            }
+        }
+    } else if (warp == TC_W_MMA) {
+        // =========================== MMA issue (one thread) ===========================
+        constexpr uint32_t ID_QK = umma_idesc_f16(128, N_QK, 0, 0);
+        constexpr uint32_t ID_PV = umma_idesc_f16(128, N_PV, 1, 1);
+        constexpr uint32_t ID_PZ = umma_idesc_f16(128, N_PV, 0, 1);
+        const uint32_t a_k = smem_u32(s_ktile), a_v = smem_u32(s_vtile), a_bq = smem_u32(s_bq), a_pt = smem_u32(s_pt), a_one = smem_u32(s_ones);
+        bool dead = false;
+        // PV of item i is issued after the logits of item i + 1, so that the softmax of i overlaps them
+        for (int step = 0; step <= n_items && !dead; ++step) {
+            if (step < n_items) {
+                const int i = step, x = i & 1;
+                bool ok = mbar_wait(TBAR(TB_KREADY + x), (uint32_t)(i >> 1) & 1u);
+                if (ok && i >= 2) ok = mbar_wait(TBAR(TB_DQFREE + x), (uint32_t)((i >> 1) - 1) & 1u);
+                if (!ok) { dead = true; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const int ksteps = k_out > 0 ? TC_KCHUNKS / 2 : 8;      // the residual positions exist only with outliers
+#pragma unroll
+                    for (int ks = 0; ks < TC_KCHUNKS / 2; ++ks)
+                        if (ks < ksteps)
+                        umma_f16(tm_dqk + x * N_QK, umma_desc(a_k + x * TC_KTILE + ks * 4096, 2048, 128),
+                                 umma_desc(a_bq + x * BQ_BYTES + ks * 2 * (16 * N_QK), 16 * N_QK, 128), ID_QK, ks > 0 ? 1u : 0u);
+                    umma_commit(TBAR(TB_DQFULL + x));
+                    umma_commit(TBAR(TB_KFREE + (i & 3)));
+                }
+                __syncwarp();
+            }
+            if (step >= 1) {
+                const int i = step - 1, x = i & 1, vb = i % P.nvb;
+                bool ok = mbar_wait(TBAR(TB_PREADY + (i & 3)), (uint32_t)(i >> 2) & 1u);
+                if (ok) ok = mbar_wait(TBAR(TB_VREADY + vb), (uint32_t)(i / P.nvb) & 1u);
+                if (!ok) { dead = true; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    for (int ub = 0; ub < 4; ++ub) {
+                        if (4 * i + ub >= n_units) break;
+                        const int blk = ub + (NB8 ? 4 * (i & 1) : 0);
+                        const bool first = i < (NB8 ? 2 : 1);
+                        const uint32_t d = tm_dpv + blk * N_PV;
+                        const uint32_t av = a_v + vb * TC_VTILE + ub * TC_UNIT_TILE;
+                        const uint32_t bp = a_pt + (x * 4 + ub) * 2 * PT_BYTES;
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks)
+                            umma_f16(d, umma_desc(av + ks * 256, 128, 512), umma_desc(bp + ks * 256, 128, 512), ID_PV, (first && ks == 0) ? 0u : 1u);
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks)
+                            umma_f16(d, umma_desc(a_one, 2048, 128), umma_desc(bp + PT_BYTES + ks * 256, 128, 512), ID_PZ, 1u);
+                    }
+                    umma_commit(TBAR(TB_PVDONE + (i & 3)));
+                }
+                __syncwarp();
+            }
+        }
+        if (dead && lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
+    } else if (warp >= TC_W_SOFTMAX && warp < TC_W_SOFTMAX + 4) {
+        // =========================== softmax warps ===========================
+        const int w = warp & 3;                                       // unit in item = lane quarter of tensor memory
+        const uint32_t lane_base = (uint32_t)(32 * w) << 16;
+        float m0[GQAP], l0[GQAP], m1[GQAP], l1[GQAP];
+#pragma unroll
+        for (int j = 0; j < GQAP; ++j) { m0[j] = m1[j] = -INFINITY; l0[j] = l1[j] = 0.f; }
+        bool dead = false;
+
+        // A bounded wait that runs out raises the CTA's abort flag; the four warps look at the flag right after
+        // each of their common barriers, so they always leave the loop together and no barrier is left waiting.
+        auto give_up = [&]() { if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; } };
+        auto item_body = [&](const int i, float (&mref)[GQAP], float (&lsum)[GQAP]) {
+            const int x = i & 1, u = 4 * i + w;
+            const bool valid = u < n_units;
+            const int g = valid ? u / H : 0;
+            uint32_t raw[GQAP];
+#pragma unroll
+            for (int j = 0; j < GQAP; ++j) raw[j] = 0u;
+            if (mbar_wait(TBAR(TB_DQFULL + x), (uint32_t)(i >> 1) & 1u)) {
+                tc_fence_after();
+                tmem_ld<GQAP>(tm_dqk + lane_base + x * N_QK + w * GQAP, raw);
+                tc_fence_before();
+            } else {
+                give_up();
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(TBAR(TB_DQFREE + x));
+            const uint8_t *side = s_side + x * TC_SIDE_BYTES;
+            float xs[GQAP], mloc[GQAP];
+            const bool tok_ok = valid && (32 * g + lane < ntok);
+            {
+                const float *qz = reinterpret_cast<const float *>(side + TC_SIDE_QZ) + w * 16;
+#pragma unroll
+                for (int j = 0; j < GQAP; ++j) {
+                    float v = fmaf(__uint_as_float(raw[j]), (float)(1 << (16 - TC_FBQ)), (qz[j] + qz[8 + j]) * p.sm_scale);
+                    if (p.logit_cap > 0.f) v = p.logit_cap * tanhf(v / p.logit_cap);
+                    xs[j] = tok_ok ? v : -INFINITY;
+                    mloc[j] = redux_max_f32(xs[j]);
+                }
+            }
+            // does the reference maximum of this block have to move?
+            bool need = false, blk_started = false;
+            float corr[GQAP];
+#pragma unroll
+            for (int j = 0; j < GQAP; ++j) {
+                need |= (mloc[j] - mref[j]) * LOG2E > TC_RESCALE_LOG2;   // -inf reference: true whenever mloc is finite
+                blk_started |= (mref[j] != -INFINITY);
+            }
+            const bool rescale = need && blk_started && valid;
+#pragma unroll
+            for (int j = 0; j < GQAP; ++j) {
+                const float target = need ? fmaxf(mref[j], mloc[j]) : mref[j];
+                const float safe = target == -INFINITY ? 0.f : target;
+                corr[j] = (mref[j] == -INFINITY) ? (need ? 0.f : 1.f) : fast_exp2((mref[j] - safe) * LOG2E);
+                mref[j] = target;
+            }
+            // publish, then all four warps look at all four flags: a block's accumulator spans every lane quarter
+            if (lane == 0) {
+                s_misc[TM_NEED + x * 4 + w] = rescale ? 1u : 0u;
+                if (rescale) {
+#pragma unroll
+                    for (int j = 0; j < GQAP; ++j) s_misc[TM_CORR + (x * 4 + w) * 8 + j] = __float_as_uint(corr[j]);
+                }
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (s_misc[TM_ABORT] != 0) { dead = true; return; }
+            uint32_t anyneed = 0;
+#pragma unroll
+            for (int o = 0; o < 4; ++o) anyneed |= s_misc[TM_NEED + x * 4 + o] << o;
+            if (anyneed) {
+                // every output MMA issued so far must have landed before its accumulator is rewritten
+                const bool landed = i < 1 || mbar_wait(TBAR(TB_PVDONE + ((i - 1) & 3)), (uint32_t)((i - 1) >> 2) & 1u);
+                if (!landed) give_up();
+                tc_fence_after();
+                if (landed) {
+#pragma unroll
+                    for (int o = 0; o < 4; ++o) {
+                        if (!(anyneed & (1u << o))) continue;
+                        const int blk = o + (NB8 ? 4 * (i & 1) : 0);
+                        const uint32_t addr = tm_dpv + lane_base + blk * N_PV + w * GQAP;   // this quarter's scale-group columns
+                        uint32_t acc[GQAP];
+                        tmem_ld<GQAP>(addr, acc);
+#pragma unroll
+                        for (int j = 0; j < GQAP; ++j)
+                            acc[j] = __float_as_uint(__uint_as_float(acc[j]) * __uint_as_float(s_misc[TM_CORR + (x * 4 + o) * 8 + j]));
+                        tmem_st<GQAP>(addr, acc);
+                    }
+                }
+                tc_fence_before();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (s_misc[TM_ABORT] != 0) { dead = true; return; }
+            }
+            // probabilities against the reference maximum; P' and Pz tiles of this unit
+            float pr[GQAP];
+#pragma unroll
+            for (int j = 0; j < GQAP; ++j) {
+                const float ms = mref[j] == -INFINITY ? 0.f : mref[j];
+                pr[j] = fast_exp2((xs[j] - ms) * LOG2E);                 // masked tokens: exp2(-inf) = 0
+                lsum[j] = lsum[j] * corr[j] + pr[j];
+            }
+            bool tiles_free = true;
+            if (i >= 2) tiles_free = mbar_wait(TBAR(TB_PVDONE + ((i - 2) & 3)), (uint32_t)((i - 2) >> 2) & 1u);   // tiles of item i - 2 consumed
+            if (!tiles_free) give_up();
+            if (valid && tiles_free) {
+                const uint2 vf = *reinterpret_cast<const uint2 *>(side + TC_SIDE_VF + (w * 32 + lane) * 8);
+                const uint2 vz = *reinterpret_cast<const uint2 *>(side + TC_SIDE_VZ + (w * 32 + lane) * 8);
+                uint32_t pp[GQAP / 2];
+#pragma unroll
+                for (int j = 0; j < GQAP / 2; ++j) pp[j] = pack_f16x2(pr[2 * j], pr[2 * j + 1]);
+                uint8_t *pt = s_pt + (x * 4 + w) * 2 * PT_BYTES + 16 * lane;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {                            // t = 0: P' (scale factors), 1: Pz (zero-points)
+                    const uint2 f = t ? vz : vf;
+                    uint32_t f2[4] = {dup16(f.x & 0xFFFFu), dup16(f.x >> 16), dup16(f.y & 0xFFFFu), dup16(f.y >> 16)};
+                    uint8_t *dst = pt + t * PT_BYTES;
+                    if constexpr (GQAP == 4) {
+#pragma unroll
+                        for (int nb2 = 0; nb2 < 2; ++nb2)                // row block of 8 = two scale groups x four heads
+                            *reinterpret_cast<uint4 *>(dst + nb2 * 512) =
+                                make_uint4(hmul2_f16(pp[0], f2[2 * nb2]), hmul2_f16(pp[1], f2[2 * nb2]),
+                                           hmul2_f16(pp[0], f2[2 * nb2 + 1]), hmul2_f16(pp[1], f2[2 * nb2 + 1]));
+                    } else {
+#pragma unroll
+                        for (int cg = 0; cg < 4; ++cg)                   // row block of 8 = one scale group x eight heads
+                            *reinterpret_cast<uint4 *>(dst + cg * 512) =
+                                make_uint4(hmul2_f16(pp[0], f2[cg]), hmul2_f16(pp[1], f2[cg]), hmul2_f16(pp[2], f2[cg]), hmul2_f16(pp[3], f2[cg]));
+                    }
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(TBAR(TB_PREADY + (i & 3)));
+        };
+
+        for (int i = 0; i < n_items && !dead; ++i) {
+            if (!NB8 || !(i & 1)) item_body(i, m0, l0);
+            else item_body(i, m1, l1);
+        }
+
+        // ---- epilogue: block states to shared memory, then every warp finishes its 32 channel rows ----
+#pragma unroll
+        for (int j = 0; j < GQAP; ++j) {
+            float a = l0[j], c = l1[j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xFFFFFFFFu, a, o); c += __shfl_xor_sync(0xFFFFFFFFu, c, o); }
+            if (lane == 0) {
+                s_misc[TM_FM + w * 8 + j] = __float_as_uint(m0[j]); s_misc[TM_FL + w * 8 + j] = __float_as_uint(a);
+                s_misc[TM_FM + (w + 4) * 8 + j] = __float_as_uint(m1[j]); s_misc[TM_FL + (w + 4) * 8 + j] = __float_as_uint(c);
+            }
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        bool fin_ok = !dead && s_misc[TM_ABORT] == 0;
+        if (fin_ok && n_items > 0) fin_ok = mbar_wait(TBAR(TB_PVDONE + ((n_items - 1) & 3)), (uint32_t)((n_items - 1) >> 2) & 1u);
+        tc_fence_after();
+        const int nbh = P.nb / H;                                        // accumulator blocks per kv head (1, 2 or 4)
+        const int m_row = 32 * w + lane;                                 // tile row = tensor-memory lane
+        const int ch = tc_channel_of(m_row);
+        const float row_f = exp2f((float)(24 - 2 * tc_vslot(m_row) - TC_FBV));
+        for (int h = 0; h < H; ++h) {
+            float acc[GQAP], den[GQAP], mx[GQAP];
+#pragma unroll
+            for (int j = 0; j < GQAP; ++j) { acc[j] = 0.f; den[j] = 0.f; mx[j] = -INFINITY; }
+            for (int r = 0; r < nbh; ++r) {
+                const int blk = h + r * H;
+                if (blk >= n_units) continue;
+#pragma unroll
+                for (int j = 0; j < GQAP; ++j) mx[j] = fmaxf(mx[j], __uint_as_float(s_misc[TM_FM + blk * 8 + j]));
+            }
+            for (int r = 0; r < nbh; ++r) {
+                const int blk = h + r * H;
+                if (blk >= n_units || !fin_ok) continue;
+                uint32_t d[GQAP];
+                tmem_ld<GQAP>(tm_dpv + lane_base + blk * N_PV + w * GQAP, d);
+#pragma unroll
+                for (int j = 0; j < GQAP; ++j) {
+                    const float mb = __uint_as_float(s_misc[TM_FM + blk * 8 + j]);
+                    const float wgt = (mb == -INFINITY) ? 0.f : fast_exp2((mb - mx[j]) * LOG2E);
+                    acc[j] = fmaf(__uint_as_float(d[j]), wgt, acc[j]);
+                    den[j] = fmaf(__uint_as_float(s_misc[TM_FL + blk * 8 + j]), wgt, den[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < GQAP; ++j) {
+                if (j >= gqa) continue;
+                float *dst = p.al + (int64_t)b * p.al_sb + (int64_t)(h * gqa + j) * p.al_sh + (int64_t)split * p.al_ss;
+                const bool some = fin_ok && den[j] > 0.f;
+                dst[ch] = some ? acc[j] * row_f / den[j] : 0.f;
+                if (w == 0 && lane == 0) dst[HD] = some ? mx[j] + logf(den[j]) : -INFINITY;
+            }
+        }
+        tc_fence_before();
+    } else {
+        // =========================== decode warps ===========================
+        const int dw = warp < TC_W_SOFTMAX ? warp - 2 : warp - 6;        // 0..TC_NDW-1
+        const int nbytes_oval = p.nb;                                    // bytes of outlier values per channel
+        bool dead = false;
+        for (int task = dw; task < n_items * 8 && !dead; task += TC_NDW) {
+            const int i = task >> 3, ub = (task >> 1) & 3, hf = task & 1, x = i & 1;
+            const int u = 4 * i + ub;
+            const bool valid = u < n_units;
+            const int g = valid ? u / H : 0, h = valid ? u - g * H : 0;
+            const int s = g % NS;
+            // Item i - 2 used the same K tile, B tile and factor buffers: its logits must have been computed and its
+            // softmax must have read the factors.  These waits come first: they also mean that every earlier user of
+            // this group's ring stage has long seen it filled, so the parity asked for below is the right phase.
+            if (i >= 2 && !mbar_wait(TBAR(TB_KFREE + ((i - 2) & 3)), (uint32_t)((i - 2) >> 2) & 1u)) { dead = true; break; }
+            if (i >= 2 && !mbar_wait(TBAR(TB_PREADY + ((i - 2) & 3)), (uint32_t)((i - 2) >> 2) & 1u)) { dead = true; break; }
+            if (valid && !mbar_wait(TBAR(TB_FULL + s), (uint32_t)(g / NS) & 1u)) { dead = true; break; }
+            const uint8_t *gb = s_stage + (size_t)s * p.stage_bytes;
+            uint8_t *ktile = s_ktile + x * TC_KTILE;
+            uint8_t *side = s_side + x * TC_SIDE_BYTES;
+            bool clamped_any = false;
+            if (valid) {
+                // ---- K codes of this half: token row `lane`, four 32-bit words = channels 64hf .. 64hf+63 ----
+                {
+                    const uint4 kw = *reinterpret_cast<const uint4 *>(gb + swz128((uint32_t)(lane * TS + h * 32 + 16 * hf), p.swz));
+                    const uint32_t wv[4] = {kw.x, kw.y, kw.z, kw.w};
+                    uint8_t *row = ktile + 16 * (32 * ub + lane) + (8 * hf) * 2048;
+#pragma unroll
+                    for (int jw = 0; jw < 4; ++jw) {
+                        const uint32_t wd = wv[jw];
+                        const uint32_t M = 0x03000300u;
+                        *reinterpret_cast<uint4 *>(row + (2 * jw) * 2048) = make_uint4((wd << 8) & M, (wd << 6) & M, (wd << 4) & M, (wd << 2) & M);
+                        *reinterpret_cast<uint4 *>(row + (2 * jw + 1) * 2048) = make_uint4(wd & M, (wd >> 2) & M, (wd >> 4) & M, (wd >> 6) & M);
+                    }
+                }
+                // ---- B tile rows of this unit (query x 2^(e_k + FBQ)) and the fp32 q.zp sums, positions 64hf .. 64hf+63:
+                //      lane = (8-position chunk c, head j4 [+4]) ----
+                {
+                    const int c = lane >> 2, j4 = lane & 3;
+                    const int blk16 = 4 * hf + (c >> 1), c0 = 16 * blk16 + 4 * (c & 1);   // channels c0..c0+3 (even positions), c0+8.. (odd)
+                    const uint32_t ea = *reinterpret_cast<const uint32_t *>(gb + p.o_ks + h * 128 + c0);
+                    const uint32_t eb = *reinterpret_cast<const uint32_t *>(gb + p.o_ks + h * 128 + c0 + 8);
+                    uint32_t fac[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        bool c1, c2;
+                        const uint32_t fa = tc_pow2_f16(max((int)(int8_t)(ea >> (8 * t)), -126), TC_FBQ, c1);
+                        const uint32_t fb = tc_pow2_f16(max((int)(int8_t)(eb >> (8 * t)), -126), TC_FBQ, c2);
+                        clamped_any |= c1 | c2;
+                        fac[t] = fa | (fb << 16);
+                    }
+                    const uint2 za = *reinterpret_cast<const uint2 *>(gb + p.o_kz + h * 256 + 2 * c0);
+                    const uint2 zb = *reinterpret_cast<const uint2 *>(gb + p.o_kz + h * 256 + 2 * (c0 + 8));
+                    const float zpa[4] = {bf16_bits_to_f32(za.x & 0xFFFFu), bf16_bits_to_f32(za.x >> 16), bf16_bits_to_f32(za.y & 0xFFFFu), bf16_bits_to_f32(za.y >> 16)};
+                    const float zpb[4] = {bf16_bits_to_f32(zb.x & 0xFFFFu), bf16_bits_to_f32(zb.x >> 16), bf16_bits_to_f32(zb.y & 0xFFFFu), bf16_bits_to_f32(zb.y >> 16)};
+                    const int pos0 = 64 * hf + 8 * c;
+#pragma unroll
+                    for (int pass = 0; pass < GQAP / 4; ++pass) {
+                        const int j = j4 + 4 * pass;
+                        const int qrow = (h * GQAP + j) * 128 + pos0;
+                        const uint4 q = *reinterpret_cast<const uint4 *>(s_q16 + qrow);
+                        const int n = ub * GQAP + j;
+                        *reinterpret_cast<uint4 *>(s_bq + x * BQ_BYTES + 16 * n + (8 * hf + c) * (16 * N_QK)) =
+                            make_uint4(hmul2_f16(q.x, fac[0]), hmul2_f16(q.y, fac[1]), hmul2_f16(q.z, fac[2]), hmul2_f16(q.w, fac[3]));
+                        const uint4 r = *reinterpret_cast<const uint4 *>(s_qraw + qrow);
+                        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+                        float sum = 0.f;
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            sum = fmaf(bf16_bits_to_f32(rw[t] & 0xFFFFu), zpa[t], fmaf(bf16_bits_to_f32(rw[t] >> 16), zpb[t], sum));
+                        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+                        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
+                        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
+                        if (c == 0) reinterpret_cast<float *>(side + TC_SIDE_QZ)[ub * 16 + hf * 8 + j] = sum;
+                    }
+                }
+                // ---- V factors of tokens 16hf .. 16hf+15: lane = (token, pair of scale groups) ----
+                {
+                    const int tk = 16 * hf + (lane & 15), cg0 = 2 * (lane >> 4);
+                    uint32_t fpair = 0u, zpair = 0u;
+                    if (32 * g + tk < ntok) {
+                        const uint32_t ve = *reinterpret_cast<const uint16_t *>(gb + p.o_vs + (tk * H + h) * 4 + cg0);
+                        const uint32_t vz2 = *reinterpret_cast<const uint32_t *>(gb + p.o_vz + (tk * H + h) * 8 + 2 * cg0);
+                        bool c1, c2;
+                        fpair = tc_pow2_f16((int)(int8_t)(ve & 0xFFu), TC_FBV, c1, TC_VF_LIMIT) | (tc_pow2_f16((int)(int8_t)(ve >> 8), TC_FBV, c2, TC_VF_LIMIT) << 16);
+                        clamped_any |= c1 | c2;
+                        // the zero-point carries the same 2^FBV as the scale factor, so that both terms of the output agree
+                        zpair = f16_bits_sat(bf16_bits_to_f32(vz2 & 0xFFFFu) * (float)(1 << TC_FBV)) |
+                                (f16_bits_sat(bf16_bits_to_f32(vz2 >> 16) * (float)(1 << TC_FBV)) << 16);
+                    }
+                    *reinterpret_cast<uint32_t *>(side + TC_SIDE_VF + (ub * 32 + tk) * 8 + 2 * cg0) = fpair;
+                    *reinterpret_cast<uint32_t *>(side + TC_SIDE_VZ + (ub * 32 + tk) * 8 + 2 * cg0) = zpair;
+                }
+                // ---- outliers of this half's channels, written over their slots of the K tile (after the codes) ----
+                __syncwarp();
+                if (k_out > 0) {
+                    const int d0 = 64 * hf + 2 * lane;
+                    const uint32_t e2 = *reinterpret_cast<const uint16_t *>(gb + p.o_ks + h * 128 + d0);
+                    const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
+                    uint32_t ms2 = 0, mc2 = 0;
+                    if (p.use_map) {
+                        ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
+                        mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
+                    }
+                    const uint2 bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
+                    const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nbytes_oval;
+                    // Channels with a large scale: the entry's rounding error (up to 2^-9 of a code step) times the scale
+                    // would show in the logits, so their outliers' residuals go to spare positions 128 + 8hf + slot of the
+                    // row, whose B entries are the channel's own times 2^-10.  Up to 8 such channels per half.
+                    const int e_c0 = (int)(int8_t)(e2 & 0xFFu), e_c1 = (int)(int8_t)(e2 >> 8);
+                    const uint32_t fm0 = __ballot_sync(0xFFFFFFFFu, e_c0 >= TC_FLAG_E), fm1 = __ballot_sync(0xFFFFFFFFu, e_c1 >= TC_FLAG_E);
+                    const uint32_t lt = (1u << lane) - 1u;
+                    const int slot_c[2] = {__popc(fm0 & lt), __popc(fm0) + __popc(fm1 & lt)};
+                    const bool res_c[2] = {e_c0 >= TC_FLAG_E && slot_c[0] < 8, e_c1 >= TC_FLAG_E && slot_c[1] < 8};
+                    const int kc = 16 + hf;                                   // the residual chunk of this half
+                    *reinterpret_cast<uint4 *>(ktile + 16 * (32 * ub + lane) + kc * 2048) = make_uint4(0u, 0u, 0u, 0u);
+                    uint8_t *bq_res = s_bq + x * BQ_BYTES + 16 * (ub * GQAP) + kc * (16 * N_QK);
+                    if (lane < GQAP) *reinterpret_cast<uint4 *>(bq_res + 16 * lane) = make_uint4(0u, 0u, 0u, 0u);
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int e = min(max((int)(int8_t)(e2 >> (8 * c)), -126), 100);
+                        const float inv_s = __uint_as_float((uint32_t)(127 - 16 - e) << 23);   // 2^-16 / scale
+                        const float zp = bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu));
+                        // the outlier's value: level / map scale + map centre (dedicated map) or level * scale + zp (shared map)
+                        const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
+                        float A = sc, Bc = zp;
+                        if (p.use_map) {
+                            A = __fdividef(1.f, bf16_bits_to_f32(c ? (ms2 >> 16) : (ms2 & 0xFFFFu)));
+                            Bc = bf16_bits_to_f32(c ? (mc2 >> 16) : (mc2 & 0xFFFFu));
+                        }
+                        uint32_t bits = c ? bm2.y : bm2.x;
+                        const int pos = tc_pos_of(d0 + c);
+                        uint8_t *col = ktile + 16 * (32 * ub) + (pos >> 3) * 2048 + (pos & 7) * 2;
+                        uint8_t *rcol = ktile + 16 * (32 * ub) + kc * 2048 + 2 * slot_c[c];
+                        const bool res = res_c[c];
+                        if (res) {                                         // B entries of the spare position: the channel's, times 2^-10
+                            bool cl;
+                            const uint32_t f = tc_pow2_f16(e, TC_FBQ - TC_RES_SHIFT, cl);
+                            for (int j = 0; j < gqa; ++j) {
+                                const uint32_t qv = s_q16[(h * GQAP + j) * 128 + pos];
+                                *reinterpret_cast<uint16_t *>(bq_res + 16 * j + 2 * slot_c[c]) = (uint16_t)(hmul2_f16(qv, f) & 0xFFFFu);
+                            }
+                        }
+                        const uint8_t *sv = ov + c * nbytes_oval;
+                        int r = __popc(bits) - 1;
+                        if (r + 1 != k_out) or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
+                        r = min(r, 2 * nbytes_oval - 1);
+                        while (bits) {
+                            const int pz = 31 - __clz(bits);
+                            bits ^= 1u << pz;
+                            const uint32_t nib = ((uint32_t)sv[r >> 1] >> (4 * (r & 1))) & 0xFu;
+                            --r;
+                            // The reference adds to the base value code * scale + zp a delta rounded to bf16
+                            // (paged_decode.py:1923-1950); the same rounding here, with the base code read back from the
+                            // slot the entry is about to replace, keeps the two paths' rounding noise in step.
+                            const float cf = (float)(*reinterpret_cast<const uint16_t *>(col + 16 * pz) >> 8);
+                            const float delta = bf16_round_f32(fmaf(s_lut[nib], A, Bc) - fmaf(cf, sc, zp));
+                            const float X = fmaf(delta, inv_s, cf * 1.52587890625e-05f);      // (code + delta / scale) * 2^-16
+                            const uint32_t hbits = f16_bits_sat(X);
+                            *reinterpret_cast<uint16_t *>(col + 16 * pz) = (uint16_t)hbits;
+                            if (res) {
+                                const float back = __half2float(__ushort_as_half((unsigned short)hbits));
+                                *reinterpret_cast<uint16_t *>(rcol + 16 * pz) = (uint16_t)f16_bits_sat((X - back) * (float)(1 << TC_RES_SHIFT));
+                            }
+                        }
+                    }
+                }
+            }
+            if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(TBAR(TB_KREADY + x));
+
+            // ---- V codes of this half into the V tile (channel-major), once the tile's previous user is done ----
+            const int vb = i % P.nvb;
+            if (i >= P.nvb) {
+                const int jdone = i - P.nvb;
+                if (!mbar_wait(TBAR(TB_PVDONE + (jdone & 3)), (uint32_t)(jdone >> 2) & 1u)) { dead = true; break; }
+            }
+            if (valid) {
+                uint4 vw = make_uint4(0u, 0u, 0u, 0u);
+                if (32 * g + lane < ntok) vw = *reinterpret_cast<const uint4 *>(gb + p.o_vm + swz128((uint32_t)(lane * TS + h * 32 + 16 * hf), p.swz));
+                const uint32_t wv[4] = {vw.x, vw.y, vw.z, vw.w};
+                uint8_t *vt = s_vtile + vb * TC_VTILE + ub * TC_UNIT_TILE + 16 * lane + (8 * hf) * 512;
+#pragma unroll
+                for (int jw = 0; jw < 4; ++jw) {
+                    const uint32_t wd = wv[jw];
+                    *reinterpret_cast<uint4 *>(vt + (2 * jw) * 512) = make_uint4(code_pair(wd, 0), code_pair(wd, 1), code_pair(wd, 2), code_pair(wd, 3));
+                    *reinterpret_cast<uint4 *>(vt + (2 * jw + 1) * 512) = make_uint4(code_pair(wd, 4), code_pair(wd, 5), code_pair(wd, 6), code_pair(wd, 7));
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(TBAR(TB_VREADY + vb));
+                if (valid) mbar_arrive(TBAR(TB_EMPTY + s));
+            }
+        }
+        if (dead && lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TC_W_MMA) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P.tmem_cols));
+#undef TBAR
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+// Fills the tensor-core kernel's shared-memory layout; returns the bytes needed (0 = the shape is not served).
+static size_t tc_layout(TcParams &P, int gqap, int max_groups_per_split) {
+    S1Params &p = P.s;
+    const int H = p.H;
+    const int n_qk = 4 * gqap;
+    const size_t bq = (size_t)TC_KCHUNKS * 16 * n_qk, pt = (size_t)(4 * gqap) * 64;
+    P.nb = H > 4 ? H : 4;
+    P.tab_groups = max_groups_per_split;
+    P.tab_pages = max_groups_per_split * p.ppg;
+    const size_t fixed = 2 * TC_KTILE + 2 * bq + 2 * 4 * 2 * pt + TC_ONES + 2 * TC_SIDE_BYTES + 2 * (size_t)H * gqap * 256 + 64 +
+                         (size_t)(P.tab_pages + P.tab_groups) * 4 + 64 + TB_COUNT * 8 + TM_WORDS * 4 + 64 +
+                         (size_t)(4 * p.ppg + 6) * sizeof(CopyDesc) + 1024 /* alignment slack */ + 1024 /* offset rounding */;
+    const size_t limit = 232448;
+    const int min_stages = 2 * (H >= 4 ? 1 : 4 / H);                      // two items' worth of groups in flight
+    int best_ns = 0, best_nvb = 0;
+    for (int nvb = 2; nvb >= 1 && !best_ns; --nvb)
+        for (int ns = TC_MAX_STAGES; ns >= min_stages; --ns)
+            if (fixed + (size_t)nvb * TC_VTILE + (size_t)ns * p.stage_bytes <= limit) {
+                // prefer the second V buffer only when at least 3 stages still fit
+                if (nvb == 2 && ns < 3 && min_stages < 3) continue;
+                best_ns = ns; best_nvb = nvb;
+                break;
+            }
+    if (!best_ns) return 0;
+    if (const char *e = getenv("OMMX_TC_NS")) { int v = atoi(e); if (v >= min_stages && v <= best_ns) best_ns = v; }
+    if (const char *e = getenv("OMMX_TC_NVB")) { int v = atoi(e); if (v >= 1 && v <= best_nvb) best_nvb = v; }
+    p.nstages = best_ns;
+    P.nvb = best_nvb;
+    auto up = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
+    size_t o = (size_t)best_ns * p.stage_bytes;
+    o = up(o, 128); P.o_ktile = (uint32_t)o; o += 2 * TC_KTILE;
+    P.o_vtile = (uint32_t)o; o += (size_t)best_nvb * TC_VTILE;
+    P.o_bq = (uint32_t)o; o += 2 * bq;
+    P.o_ptile = (uint32_t)o; o += 2 * 4 * 2 * pt;
+    P.o_ones = (uint32_t)o; o += TC_ONES;
+    P.o_side = (uint32_t)o; o += 2 * TC_SIDE_BYTES;
+    P.o_q16 = (uint32_t)o; o += (size_t)H * gqap * 256;
+    P.o_qraw = (uint32_t)o; o += (size_t)H * gqap * 256;
+    P.o_lut = (uint32_t)o; o += 64;
+    P.o_tab = (uint32_t)o; o += (size_t)(P.tab_pages + P.tab_groups) * 4;
+    o = up(o, 16); P.o_bar = (uint32_t)o; o += TB_COUNT * 8 + TM_WORDS * 4;
+    o = up(o, 16); P.o_desc = (uint32_t)o; o += (size_t)(4 * p.ppg + 6) * sizeof(CopyDesc);
+    const int cols = 2 * n_qk + P.nb * (4 * gqap);
+    P.tmem_cols = cols <= 32 ? 32 : (cols <= 64 ? 64 : (cols <= 128 ? 128 : (cols <= 256 ? 256 : 512)));
+    if (cols > 512) return 0;
+    return o + 1024;
+}
+
+template <int GQAP, bool NB8>
+static int launch_tc(const TcParams &P, dim3 grid, size_t smem, cudaStream_t st) {
+    static std::atomic<size_t> attr_smem[MAX_DEVICES];
+    int dev = 0;
+    if (int rc = current_device(&dev)) return rc;
+    if (smem > attr_smem[dev].load(std::memory_order_acquire)) {
+        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_tc_kernel<GQAP, NB8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_smem[dev].store(smem, std::memory_order_release);
+    }
+    decode_stage1_tc_kernel<GQAP, NB8><<<grid, TC_THREADS, smem, st>>>(P);
+    OMMX_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
+}  // namespace ommx
