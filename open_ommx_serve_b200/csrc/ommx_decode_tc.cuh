@@ -9,7 +9,7 @@
 // accumulate in tensor memory, so no warp carries accumulator registers or a dependent MMA chain:
 //
 //   producer warp    streams one group (all kv heads) per ring stage, as the register-operand kernel does.
-//   decode warps     per (unit, channel half): K codes -> fp16 c * 2^-16 (a 2-bit field moved to bits 8..9
+//   decode warps     per (unit, channel quarter): K codes -> fp16 c * 2^-16 (a 2-bit field moved to bits 8..9
 //                    of a half-word IS that subnormal: shift + mask, exact) into the K tile
 //                    [4 units x 32 tokens][128 channels]; the unit's outliers written OVER their slots as
 //                    code + bf16(value - base value) / scale, times 2^-16 - the reference's own rounding of the
@@ -19,13 +19,14 @@
 //                    rows scaled by the unit's power-of-two K scales (B tile); the fp32 q.zp sums; V codes
 //                    -> the V tile (channel-major, fields masked in place); V scale / zero-point factors.
 //   MMA thread       logits  D[4x32 tokens][unit, head] = Ktile . Bq^T            (8 x tcgen05.mma, K = 16)
-//                    output  O[128 channels][scale group, head] += Vtile . P'^T + ones . Pz^T   (4 per unit)
-//                    where P' = P * 2^e_v of the column's scale group and Pz = P * zero-point: a channel
-//                    row reads the columns of its own scale group, the others are never looked at.
+//                    output  O[128 channels][scale group, head] += Vtile . P'^T                  (2 per unit)
+//                    where P' = P * 2^e_v of the column's scale group: a channel row reads the columns of its
+//                    own scale group, the others are never looked at.
 //   4 softmax warps  (one per unit of an item = one quarter of the tensor-memory lanes): logits from tensor
 //                    memory, lane = token; per-head maximum by redux.sync; online softmax whose reference
 //                    maximum moves only when the true one outgrows it by 2^4 (the accumulators are then
-//                    rescaled in tensor memory by all four warps, each on its lane quarter); P' and Pz tiles.
+//                    rescaled in tensor memory by all four warps, each on its lane quarter); the P' tiles; the
+//                    V zero-point term sum_t P * zp as per-lane fp32 partial sums, reduced once at the end.
 //
 // Numerics keep the reference's rounding points where they matter for its gate: bf16 q * sm_scale, exact
 // code * 2^e products, fp32 q.zp from the raw query, fp32 accumulation, V as exact code * 2^e products with
@@ -44,11 +45,11 @@ constexpr int TC_FBQ = 4;          // B tile entry = q_c * 2^(e_k + FBQ); logit 
 constexpr int TC_FBV = 2;          // P' = P * 2^(e_v + FBV); output = D * 2^(24 - 2 slot - FBV)
 constexpr float TC_RESCALE_LOG2 = 4.f;   // the reference maximum follows the true one once it is 2^4 behind
 constexpr int TC_KCHUNKS = 18;     // 8-position chunks of a K tile row: 16 of channels + 2 of outlier residuals (one per channel half)
-constexpr int TC_KTILE = TC_KCHUNKS * 2048, TC_VTILE = 32768, TC_UNIT_TILE = 8192, TC_ONES = 4096;
+constexpr int TC_KTILE = TC_KCHUNKS * 2048, TC_VTILE = 32768, TC_UNIT_TILE = 8192;
 constexpr int TC_FLAG_E = 2;       // channels whose K scale is 2^2 or more get their outliers' rounding residual carried too
 constexpr int TC_RES_SHIFT = 10;   // residual entries are stored times 2^10, their B entries times 2^-10
 constexpr int TC_MAX_STAGES = 8;
-constexpr int TC_SIDE_VF = 0, TC_SIDE_VZ = 1024, TC_SIDE_QZ = 2048, TC_SIDE_BYTES = 2304;
+constexpr int TC_SIDE_VF = 0, TC_SIDE_VZ = 1024, TC_SIDE_QZ = 2048, TC_SIDE_BYTES = 2560;   // factors, zero-points, q.zp [unit][quarter][8]
 
 // barrier slots (8 bytes each)
 // A waiter tells phases apart by parity only, so it must never be two completions away from the one it asks for.
@@ -60,14 +61,26 @@ constexpr int TB_FULL = 0, TB_EMPTY = TC_MAX_STAGES, TB_KREADY = 2 * TC_MAX_STAG
               TB_PREADY = TB_DQFREE + 2, TB_COUNT = TB_PREADY + 4;
 // words after the barriers
 constexpr int TM_TMEM = 0, TM_ABORT = 1, TM_NEED = 2 /* [2][4] */, TM_CORR = 10 /* [2][4][8] */, TM_FM = 74 /* [8][8] */,
-              TM_FL = 138 /* [8][8] */, TM_WORDS = 202;
+              TM_FL = 138 /* [8][8] */, TM_FB = 202 /* [8][32] */, TM_WORDS = 458;
+
+// Development builds (-DOMMX_TC_TRACE) stamp the SM clock at fixed points of one CTA into a device array;
+// service builds compile the probes away.
+#ifdef OMMX_TC_TRACE
+__device__ long long g_tc_trace[8 * 512];
+#define TCTR(role, slot)                                                                                        \
+    do {                                                                                                        \
+        if (blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (role) < 8 && (slot) >= 0 && (slot) < 512) g_tc_trace[(role) * 512 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define TCTR(role, slot) do { } while (0)
+#endif
 
 struct TcParams {
     S1Params s;
     int32_t nb;                      // output accumulator blocks in tensor memory: max(H, 4)
     int32_t nvb;                     // V tile buffers (1 or 2)
     int32_t tab_pages, tab_groups;   // capacity of the split's page / group-slot tables
-    uint32_t o_ktile, o_vtile, o_bq, o_ptile, o_ones, o_side, o_q16, o_qraw, o_lut, o_tab, o_bar, o_desc;
+    uint32_t o_ktile, o_vtile, o_bq, o_ptile, o_side, o_q16, o_qraw, o_lut, o_tab, o_bar, o_desc;
     uint32_t tmem_cols;
 };
 
@@ -132,6 +145,98 @@ __device__ __forceinline__ int tc_channel_of(int pos) { return (pos & ~15) + ((p
 __device__ __forceinline__ int tc_pos_of(int ch) { return (ch & ~15) + ((ch & 7) << 1) + ((ch >> 3) & 1); }
 __device__ __forceinline__ int tc_vslot(int m) { const int i = (m & 15) >> 1; return i < 5 ? i : i - 5; }
 
+// Outliers of channel 32qt + lane of one unit, written over their slots of the K tile row by row (the codes of the
+// quarter are in place).  KO > 0: the count is known, all gathers (bit walk, FP4 level, base code read back from the
+// slot) are issued before the first store, so their latencies overlap; KO < 0: any count, one pass.
+// Entry = (code + bf16(value - base value) / scale) * 2^-16: the reference adds to the base value code * scale + zp a
+// delta rounded to bf16 (paged_decode.py:1923-1950), and the same rounding here keeps the two paths' noise in step.
+// Channels with a scale of 2^TC_FLAG_E or more also carry the entry's rounding residual (times 2^10) in one of four
+// spare positions of the quarter, whose B entries are the channel's own times 2^-10.
+template <int KO>
+__device__ __forceinline__ void tc_splice(const S1Params &p, const uint8_t *gb, uint8_t *ktile, uint8_t *bq, const uint16_t *s_q16,
+                                          const float *s_lut, int h, int ub, int qt, int lane, int gqap, int n_qk, bool &clamped_any) {
+    const int d = 32 * qt + lane;
+    const int nb = p.nb;
+    const int e_raw = (int)(int8_t)gb[p.o_ks + h * 128 + d];
+    const float zp = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(gb + p.o_kz + h * 256 + 2 * d));
+    uint32_t bits = *reinterpret_cast<const uint32_t *>(gb + p.o_bm + h * 512 + 4 * d);
+    const uint8_t *sv = gb + p.o_ov + (h * 128 + d) * nb;
+    const int e = min(max(e_raw, -126), 100);
+    const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
+    const float inv_s = __uint_as_float((uint32_t)(127 - 16 - e) << 23);           // 2^-16 / scale
+    float A = sc, Bc = zp;                                                          // shared map: value = level * scale + zp
+    if (p.use_map) {                                                                // dedicated map: level / map scale + map centre
+        A = __fdividef(1.f, bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(gb + p.o_ms + h * 256 + 2 * d)));
+        Bc = bf16_bits_to_f32(*reinterpret_cast<const uint16_t *>(gb + p.o_mc + h * 256 + 2 * d));
+    }
+    const uint32_t fm = __ballot_sync(0xFFFFFFFFu, e_raw >= TC_FLAG_E);
+    const int slot = __popc(fm & ((1u << lane) - 1u));
+    const bool res = e_raw >= TC_FLAG_E && slot < 4;
+    const int kc = 16 + (qt >> 1), so = 8 * (qt & 1);                               // residual chunk, byte offset of this quarter's four slots
+    *reinterpret_cast<uint2 *>(ktile + 16 * (32 * ub + lane) + kc * 2048 + so) = make_uint2(0u, 0u);
+    uint8_t *bq_res = bq + 16 * (ub * gqap) + kc * (16 * n_qk) + so;
+    if (lane < gqap) *reinterpret_cast<uint2 *>(bq_res + 16 * lane) = make_uint2(0u, 0u);
+    __syncwarp();
+    const int pos = tc_pos_of(d);
+    uint8_t *col = ktile + 16 * (32 * ub) + (pos >> 3) * 2048 + (pos & 7) * 2;
+    uint8_t *rcol = ktile + 16 * (32 * ub) + kc * 2048 + so + 2 * slot;
+    if (res) {
+        bool cl;
+        const uint32_t f = tc_pow2_f16(e, TC_FBQ - TC_RES_SHIFT, cl);
+        for (int j = 0; j < p.gqa; ++j)
+            *reinterpret_cast<uint16_t *>(bq_res + 16 * j + 2 * slot) = (uint16_t)(hmul2_f16(s_q16[(h * gqap + j) * 128 + pos], f) & 0xFFFFu);
+    }
+    (void)clamped_any;
+    auto entry = [&](float lvl, uint32_t cbits, int pz) {
+        const float cf = (float)(cbits >> 8);
+        const float delta = bf16_round_f32(fmaf(lvl, A, Bc) - fmaf(cf, sc, zp));
+        const float X = fmaf(delta, inv_s, cf * 1.52587890625e-05f);                // (code + delta / scale) * 2^-16
+        const uint32_t hbits = f16_bits_sat(X);
+        *reinterpret_cast<uint16_t *>(col + 16 * pz) = (uint16_t)hbits;
+        if (res) {
+            const float back = __half2float(__ushort_as_half((unsigned short)hbits));
+            *reinterpret_cast<uint16_t *>(rcol + 16 * pz) = (uint16_t)f16_bits_sat((X - back) * (float)(1 << TC_RES_SHIFT));
+        }
+    };
+    if constexpr (KO > 0) {
+        if (__popc(bits) != KO) { or_status(p.status, OMMX_ST_BAD_GROUP); return; }   // bitmask and value stream disagree
+        uint32_t stream = 0;
+#pragma unroll
+        for (int i = 0; i < (KO + 1) / 2; ++i) stream |= (uint32_t)sv[i] << (8 * i);
+        // batches of up to four: all gathers of a batch before its first store (more would cost registers)
+#pragma unroll
+        for (int top = KO - 1; top >= 0; top -= 4) {
+            int pzs[4];
+            float lvs[4];
+            uint32_t cbs[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int r = top - q;
+                if (r < 0) continue;
+                const int pz = 31 - __clz(bits);
+                bits ^= 1u << pz;
+                pzs[q] = pz;
+                lvs[q] = s_lut[(stream >> (4 * r)) & 0xFu];
+                cbs[q] = *reinterpret_cast<const uint16_t *>(col + 16 * pz);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (top - q >= 0) entry(lvs[q], cbs[q], pzs[q]);
+        }
+    } else {
+        int r = __popc(bits) - 1;
+        if (r + 1 != p.k_out) or_status(p.status, OMMX_ST_BAD_GROUP);
+        r = min(r, 2 * nb - 1);
+        while (bits) {
+            const int pz = 31 - __clz(bits);
+            bits ^= 1u << pz;
+            const uint32_t nib = ((uint32_t)sv[r >> 1] >> (4 * (r & 1))) & 0xFu;
+            --r;
+            entry(s_lut[nib], *reinterpret_cast<const uint16_t *>(col + 16 * pz), pz);
+        }
+    }
+}
+
 // =================================================================================================
 template <int GQAP, bool NB8>
 __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const __grid_constant__ TcParams P) {
@@ -139,7 +244,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
     constexpr int N_QK = 4 * GQAP;                   // logit columns: (unit in item, head)
     constexpr int N_PV = 4 * GQAP;                   // output columns: (V scale group, head)
     constexpr int BQ_BYTES = TC_KCHUNKS * 16 * N_QK;
-    constexpr int PT_BYTES = N_PV * 64;              // one P' (or Pz) tile: N_PV rows x 32 tokens
+    constexpr int PT_BYTES = N_PV * 64;              // one P' tile: N_PV rows x 32 tokens
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int split = blockIdx.x, b = blockIdx.y;
@@ -165,7 +270,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
 
     uint8_t *s_stage = smem;
     uint8_t *s_ktile = smem + P.o_ktile, *s_vtile = smem + P.o_vtile, *s_bq = smem + P.o_bq, *s_pt = smem + P.o_ptile;
-    uint8_t *s_ones = smem + P.o_ones, *s_side = smem + P.o_side;
+    uint8_t *s_side = smem + P.o_side;
     uint16_t *s_q16 = reinterpret_cast<uint16_t *>(smem + P.o_q16), *s_qraw = reinterpret_cast<uint16_t *>(smem + P.o_qraw);
     float *s_lut = reinterpret_cast<float *>(smem + P.o_lut);
     int32_t *s_tab = reinterpret_cast<int32_t *>(smem + P.o_tab);
@@ -185,11 +290,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
     if (threadIdx.x == 32) {
         for (int s = 0; s < TC_MAX_STAGES; ++s) {
             mbar_init(TBAR(TB_FULL + s), 1);
-            mbar_init(TBAR(TB_EMPTY + s), 2 * H);                   // every (unit, half) task of the group
+            mbar_init(TBAR(TB_EMPTY + s), 4 * H);                   // every (unit, quarter) task of the group
         }
         for (int x = 0; x < 2; ++x) {
-            mbar_init(TBAR(TB_KREADY + x), 8);                       // 4 units x 2 halves
-            mbar_init(TBAR(TB_VREADY + x), 8);
+            mbar_init(TBAR(TB_KREADY + x), 16);                      // 4 units x 4 quarters
+            mbar_init(TBAR(TB_VREADY + x), 16);
             mbar_init(TBAR(TB_DQFULL + x), 1);
             mbar_init(TBAR(TB_DQFREE + x), 4);
         }
@@ -254,26 +359,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
         // query tables, rows = (kv head, padded query head), columns in tile position order:
         // s_q16 = fp16 of bf16(q * sm_scale) for the B tile, s_qraw = the raw bf16 query for the q.zp sums
         for (int idx = threadIdx.x; idx < H * GQAP * 128; idx += TC_THREADS) {
-            const int row = idx >> 7, pos = idx & 127;
+            const int row = idx >> 7, ch = idx & 127;                  // consecutive threads read consecutive channels
             const int h = row / GQAP, j = row - h * GQAP;
             uint16_t raw = 0, q16 = 0;
             if (j < gqa) {
-                const __nv_bfloat16 v = p.q[(int64_t)b * p.q_sb + (int64_t)(h * gqa + j) * p.q_sh + tc_channel_of(pos)];
+                const __nv_bfloat16 v = p.q[(int64_t)b * p.q_sb + (int64_t)(h * gqa + j) * p.q_sh + ch];
                 raw = __bfloat16_as_ushort(v);
                 q16 = (uint16_t)f16_bits_sat(bf16_round_f32(__bfloat162float(v) * p.sm_scale));
             }
-            s_qraw[idx] = raw;
-            s_q16[idx] = q16;
+            s_qraw[row * 128 + tc_pos_of(ch)] = raw;
+            s_q16[row * 128 + tc_pos_of(ch)] = q16;
         }
-        // the "ones" operand of the zero-point term: row m carries the factor its V codes carry
-        for (int hw = threadIdx.x; hw < TC_ONES / 2; hw += TC_THREADS)
-            reinterpret_cast<uint16_t *>(s_ones)[hw] = (uint16_t)(1u << (2 * tc_vslot((hw & 1023) >> 3)));
     }
+    if (warp == 0) TCTR(6, 0);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (warp == 0) TCTR(6, 1);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Register budget per role (setmaxnreg, warpgroup granularity; the CTA was launched with 768 x 80): the softmax
+    // warpgroup (warps 4..7) carries the per-block sums, everyone else needs little.  128 x 120 + 640 x 72 = 768 x 80.
+    if (!(warp >= TC_W_SOFTMAX && warp < TC_W_SOFTMAX + 4)) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     const uint32_t tmem = s_misc[TM_TMEM];
     const uint32_t tm_dqk = tmem, tm_dpv = tmem + 2 * N_QK;
     const float LOG2E = 1.4426950408889634f;
@@ -288,6 +395,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
                 break;
             }
+            TCTR(0, g);
             uint32_t mine = 0;
             for (int c = lane; c < cpg; c += 32) {
                 const CopyDesc d = s_desc[c];
@@ -311,8 +419,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
         // =========================== MMA issue (one thread) ===========================
         constexpr uint32_t ID_QK = umma_idesc_f16(128, N_QK, 0, 0);
         constexpr uint32_t ID_PV = umma_idesc_f16(128, N_PV, 1, 1);
-        constexpr uint32_t ID_PZ = umma_idesc_f16(128, N_PV, 0, 1);
-        const uint32_t a_k = smem_u32(s_ktile), a_v = smem_u32(s_vtile), a_bq = smem_u32(s_bq), a_pt = smem_u32(s_pt), a_one = smem_u32(s_ones);
+        const uint32_t a_k = smem_u32(s_ktile), a_v = smem_u32(s_vtile), a_bq = smem_u32(s_bq), a_pt = smem_u32(s_pt);
         bool dead = false;
         // PV of item i is issued after the logits of item i + 1, so that the softmax of i overlaps them
         for (int step = 0; step <= n_items && !dead; ++step) {
@@ -321,6 +428,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 bool ok = mbar_wait(TBAR(TB_KREADY + x), (uint32_t)(i >> 1) & 1u);
                 if (ok && i >= 2) ok = mbar_wait(TBAR(TB_DQFREE + x), (uint32_t)((i >> 1) - 1) & 1u);
                 if (!ok) { dead = true; break; }
+                TCTR(1, 4 * i);
                 tc_fence_after();
                 if (lane == 0) {
                     const int ksteps = k_out > 0 ? TC_KCHUNKS / 2 : 8;      // the residual positions exist only with outliers
@@ -333,12 +441,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                     umma_commit(TBAR(TB_KFREE + (i & 3)));
                 }
                 __syncwarp();
+                TCTR(1, 4 * i + 1);
             }
             if (step >= 1) {
                 const int i = step - 1, x = i & 1, vb = i % P.nvb;
                 bool ok = mbar_wait(TBAR(TB_PREADY + (i & 3)), (uint32_t)(i >> 2) & 1u);
+                TCTR(1, 4 * i + 2);
                 if (ok) ok = mbar_wait(TBAR(TB_VREADY + vb), (uint32_t)(i / P.nvb) & 1u);
                 if (!ok) { dead = true; break; }
+                TCTR(1, 4 * i + 3);
                 tc_fence_after();
                 if (lane == 0) {
                     for (int ub = 0; ub < 4; ++ub) {
@@ -347,13 +458,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                         const bool first = i < (NB8 ? 2 : 1);
                         const uint32_t d = tm_dpv + blk * N_PV;
                         const uint32_t av = a_v + vb * TC_VTILE + ub * TC_UNIT_TILE;
-                        const uint32_t bp = a_pt + (x * 4 + ub) * 2 * PT_BYTES;
+                        const uint32_t bp = a_pt + (x * 4 + ub) * PT_BYTES;
 #pragma unroll
                         for (int ks = 0; ks < 2; ++ks)
                             umma_f16(d, umma_desc(av + ks * 256, 128, 512), umma_desc(bp + ks * 256, 128, 512), ID_PV, (first && ks == 0) ? 0u : 1u);
-#pragma unroll
-                        for (int ks = 0; ks < 2; ++ks)
-                            umma_f16(d, umma_desc(a_one, 2048, 128), umma_desc(bp + PT_BYTES + ks * 256, 128, 512), ID_PZ, 1u);
                     }
                     umma_commit(TBAR(TB_PVDONE + (i & 3)));
                 }
@@ -363,24 +471,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
         if (dead && lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
     } else if (warp >= TC_W_SOFTMAX && warp < TC_W_SOFTMAX + 4) {
         // =========================== softmax warps ===========================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
         const int w = warp & 3;                                       // unit in item = lane quarter of tensor memory
         const uint32_t lane_base = (uint32_t)(32 * w) << 16;
-        float m0[GQAP], l0[GQAP], m1[GQAP], l1[GQAP];
+        // per accumulator block: reference maximum, per-lane sums of P, per-lane sums of P * V zero-point [scale group][head]
+        constexpr int NBZ = NB8 ? 4 * GQAP : 1;                       // the second block's zero-point sums exist only with 8 blocks
+        float m0[GQAP], l0[GQAP], m1[GQAP], l1[GQAP], z0[4 * GQAP], z1[NBZ];
 #pragma unroll
         for (int j = 0; j < GQAP; ++j) { m0[j] = m1[j] = -INFINITY; l0[j] = l1[j] = 0.f; }
+#pragma unroll
+        for (int j = 0; j < 4 * GQAP; ++j) z0[j] = 0.f;
+#pragma unroll
+        for (int j = 0; j < NBZ; ++j) z1[j] = 0.f;
         bool dead = false;
 
         // A bounded wait that runs out raises the CTA's abort flag; the four warps look at the flag right after
         // each of their common barriers, so they always leave the loop together and no barrier is left waiting.
         auto give_up = [&]() { if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; } };
-        auto item_body = [&](const int i, float (&mref)[GQAP], float (&lsum)[GQAP]) {
+        auto item_body = [&](const int i, float (&mref)[GQAP], float (&lsum)[GQAP], auto &zsum) {
             const int x = i & 1, u = 4 * i + w;
             const bool valid = u < n_units;
             const int g = valid ? u / H : 0;
             uint32_t raw[GQAP];
 #pragma unroll
             for (int j = 0; j < GQAP; ++j) raw[j] = 0u;
+            if (w == 0) TCTR(2, 4 * i);
             if (mbar_wait(TBAR(TB_DQFULL + x), (uint32_t)(i >> 1) & 1u)) {
+                if (w == 0) TCTR(2, 4 * i + 1);
                 tc_fence_after();
                 tmem_ld<GQAP>(tm_dqk + lane_base + x * N_QK + w * GQAP, raw);
                 tc_fence_before();
@@ -393,10 +510,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             float xs[GQAP], mloc[GQAP];
             const bool tok_ok = valid && (32 * g + lane < ntok);
             {
-                const float *qz = reinterpret_cast<const float *>(side + TC_SIDE_QZ) + w * 16;
+                const float *qz = reinterpret_cast<const float *>(side + TC_SIDE_QZ) + w * 32;
 #pragma unroll
                 for (int j = 0; j < GQAP; ++j) {
-                    float v = fmaf(__uint_as_float(raw[j]), (float)(1 << (16 - TC_FBQ)), (qz[j] + qz[8 + j]) * p.sm_scale);
+                    float v = fmaf(__uint_as_float(raw[j]), (float)(1 << (16 - TC_FBQ)), ((qz[j] + qz[8 + j]) + (qz[16 + j] + qz[24 + j])) * p.sm_scale);
                     if (p.logit_cap > 0.f) v = p.logit_cap * tanhf(v / p.logit_cap);
                     xs[j] = tok_ok ? v : -INFINITY;
                     mloc[j] = redux_max_f32(xs[j]);
@@ -427,6 +544,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 }
             }
             asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (w == 0) TCTR(2, 4 * i + 2);
             if (s_misc[TM_ABORT] != 0) { dead = true; return; }
             uint32_t anyneed = 0;
 #pragma unroll
@@ -454,7 +572,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (s_misc[TM_ABORT] != 0) { dead = true; return; }
             }
-            // probabilities against the reference maximum; P' and Pz tiles of this unit
+            // probabilities against the reference maximum; the unit's P' tile; its share of the V zero-point term
             float pr[GQAP];
 #pragma unroll
             for (int j = 0; j < GQAP; ++j) {
@@ -468,37 +586,45 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             if (valid && tiles_free) {
                 const uint2 vf = *reinterpret_cast<const uint2 *>(side + TC_SIDE_VF + (w * 32 + lane) * 8);
                 const uint2 vz = *reinterpret_cast<const uint2 *>(side + TC_SIDE_VZ + (w * 32 + lane) * 8);
+                const float vzf[4] = {bf16_bits_to_f32(vz.x & 0xFFFFu), bf16_bits_to_f32(vz.x >> 16), bf16_bits_to_f32(vz.y & 0xFFFFu), bf16_bits_to_f32(vz.y >> 16)};
+#pragma unroll
+                for (int cg = 0; cg < 4; ++cg)
+#pragma unroll
+                    for (int j = 0; j < GQAP; ++j) zsum[cg * GQAP + j] = fmaf(zsum[cg * GQAP + j], corr[j], pr[j] * vzf[cg]);
                 uint32_t pp[GQAP / 2];
 #pragma unroll
                 for (int j = 0; j < GQAP / 2; ++j) pp[j] = pack_f16x2(pr[2 * j], pr[2 * j + 1]);
-                uint8_t *pt = s_pt + (x * 4 + w) * 2 * PT_BYTES + 16 * lane;
+                const uint32_t f2[4] = {dup16(vf.x & 0xFFFFu), dup16(vf.x >> 16), dup16(vf.y & 0xFFFFu), dup16(vf.y >> 16)};
+                uint8_t *dst = s_pt + (x * 4 + w) * PT_BYTES + 16 * lane;
+                if constexpr (GQAP == 4) {
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {                            // t = 0: P' (scale factors), 1: Pz (zero-points)
-                    const uint2 f = t ? vz : vf;
-                    uint32_t f2[4] = {dup16(f.x & 0xFFFFu), dup16(f.x >> 16), dup16(f.y & 0xFFFFu), dup16(f.y >> 16)};
-                    uint8_t *dst = pt + t * PT_BYTES;
-                    if constexpr (GQAP == 4) {
+                    for (int nb2 = 0; nb2 < 2; ++nb2)                    // row block of 8 = two scale groups x four heads
+                        *reinterpret_cast<uint4 *>(dst + nb2 * 512) =
+                            make_uint4(hmul2_f16(pp[0], f2[2 * nb2]), hmul2_f16(pp[1], f2[2 * nb2]),
+                                       hmul2_f16(pp[0], f2[2 * nb2 + 1]), hmul2_f16(pp[1], f2[2 * nb2 + 1]));
+                } else {
 #pragma unroll
-                        for (int nb2 = 0; nb2 < 2; ++nb2)                // row block of 8 = two scale groups x four heads
-                            *reinterpret_cast<uint4 *>(dst + nb2 * 512) =
-                                make_uint4(hmul2_f16(pp[0], f2[2 * nb2]), hmul2_f16(pp[1], f2[2 * nb2]),
-                                           hmul2_f16(pp[0], f2[2 * nb2 + 1]), hmul2_f16(pp[1], f2[2 * nb2 + 1]));
-                    } else {
-#pragma unroll
-                        for (int cg = 0; cg < 4; ++cg)                   // row block of 8 = one scale group x eight heads
-                            *reinterpret_cast<uint4 *>(dst + cg * 512) =
-                                make_uint4(hmul2_f16(pp[0], f2[cg]), hmul2_f16(pp[1], f2[cg]), hmul2_f16(pp[2], f2[cg]), hmul2_f16(pp[3], f2[cg]));
-                    }
+                    for (int cg = 0; cg < 4; ++cg)                       // row block of 8 = one scale group x eight heads
+                        *reinterpret_cast<uint4 *>(dst + cg * 512) =
+                            make_uint4(hmul2_f16(pp[0], f2[cg]), hmul2_f16(pp[1], f2[cg]), hmul2_f16(pp[2], f2[cg]), hmul2_f16(pp[3], f2[cg]));
                 }
+            } else if (valid) {
+#pragma unroll
+                for (int j = 0; j < 4 * GQAP; ++j) zsum[j] *= corr[j % GQAP];
             }
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(TBAR(TB_PREADY + (i & 3)));
+            if (w == 0) TCTR(2, 4 * i + 3);
         };
 
         for (int i = 0; i < n_items && !dead; ++i) {
-            if (!NB8 || !(i & 1)) item_body(i, m0, l0);
-            else item_body(i, m1, l1);
+            if constexpr (NB8) {
+                if (!(i & 1)) item_body(i, m0, l0, z0);
+                else item_body(i, m1, l1, z1);
+            } else {
+                item_body(i, m0, l0, z0);
+            }
         }
 
         // ---- epilogue: block states to shared memory, then every warp finishes its 32 channel rows ----
@@ -510,6 +636,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             if (lane == 0) {
                 s_misc[TM_FM + w * 8 + j] = __float_as_uint(m0[j]); s_misc[TM_FL + w * 8 + j] = __float_as_uint(a);
                 s_misc[TM_FM + (w + 4) * 8 + j] = __float_as_uint(m1[j]); s_misc[TM_FL + (w + 4) * 8 + j] = __float_as_uint(c);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4 * GQAP; ++j) {
+            float a = z0[j], c = NB8 ? z1[NB8 ? j : 0] : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xFFFFFFFFu, a, o); if (NB8) c += __shfl_xor_sync(0xFFFFFFFFu, c, o); }
+            if (lane == 0) {
+                s_misc[TM_FB + w * 32 + j] = __float_as_uint(a);
+                if (NB8) s_misc[TM_FB + (w + 4) * 32 + j] = __float_as_uint(c);
             }
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -539,7 +675,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 for (int j = 0; j < GQAP; ++j) {
                     const float mb = __uint_as_float(s_misc[TM_FM + blk * 8 + j]);
                     const float wgt = (mb == -INFINITY) ? 0.f : fast_exp2((mb - mx[j]) * LOG2E);
-                    acc[j] = fmaf(__uint_as_float(d[j]), wgt, acc[j]);
+                    acc[j] = fmaf(fmaf(__uint_as_float(d[j]), row_f, __uint_as_float(s_misc[TM_FB + blk * 32 + w * GQAP + j])), wgt, acc[j]);
                     den[j] = fmaf(__uint_as_float(s_misc[TM_FL + blk * 8 + j]), wgt, den[j]);
                 }
             }
@@ -548,18 +684,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 if (j >= gqa) continue;
                 float *dst = p.al + (int64_t)b * p.al_sb + (int64_t)(h * gqa + j) * p.al_sh + (int64_t)split * p.al_ss;
                 const bool some = fin_ok && den[j] > 0.f;
-                dst[ch] = some ? acc[j] * row_f / den[j] : 0.f;
+                dst[ch] = some ? acc[j] / den[j] : 0.f;
                 if (w == 0 && lane == 0) dst[HD] = some ? mx[j] + logf(den[j]) : -INFINITY;
             }
         }
         tc_fence_before();
     } else {
         // =========================== decode warps ===========================
+        // A task is (item, unit, channel quarter): 32 channels = two 32-bit code words per token, lane = token for the
+        // code expansion and lane = channel for the outliers.  16 tasks per item, dealt round-robin.
         const int dw = warp < TC_W_SOFTMAX ? warp - 2 : warp - 6;        // 0..TC_NDW-1
-        const int nbytes_oval = p.nb;                                    // bytes of outlier values per channel
         bool dead = false;
-        for (int task = dw; task < n_items * 8 && !dead; task += TC_NDW) {
-            const int i = task >> 3, ub = (task >> 1) & 3, hf = task & 1, x = i & 1;
+        for (int task = dw; task < n_items * 16 && !dead; task += TC_NDW) {
+            const int i = task >> 4, ub = (task >> 2) & 3, qt = task & 3, x = i & 1;
+            const int trn = 6 * ((task - dw) / TC_NDW), trr = dw == 0 ? 3 : (dw == 5 ? 4 : (dw == 17 ? 5 : 8)), tr8 = dw == 1 ? 8 * ((task - dw) / TC_NDW) : -1000;
+            (void)tr8;
+            (void)trn; (void)trr;
+            TCTR(trr, trn);
             const int u = 4 * i + ub;
             const bool valid = u < n_units;
             const int g = valid ? u / H : 0, h = valid ? u - g * H : 0;
@@ -570,180 +711,111 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             if (i >= 2 && !mbar_wait(TBAR(TB_KFREE + ((i - 2) & 3)), (uint32_t)((i - 2) >> 2) & 1u)) { dead = true; break; }
             if (i >= 2 && !mbar_wait(TBAR(TB_PREADY + ((i - 2) & 3)), (uint32_t)((i - 2) >> 2) & 1u)) { dead = true; break; }
             if (valid && !mbar_wait(TBAR(TB_FULL + s), (uint32_t)(g / NS) & 1u)) { dead = true; break; }
+            TCTR(trr, trn + 1);
+            TCTR(7, tr8);
             const uint8_t *gb = s_stage + (size_t)s * p.stage_bytes;
             uint8_t *ktile = s_ktile + x * TC_KTILE;
             uint8_t *side = s_side + x * TC_SIDE_BYTES;
             bool clamped_any = false;
             if (valid) {
-                // ---- K codes of this half: token row `lane`, four 32-bit words = channels 64hf .. 64hf+63 ----
+                // ---- K codes: token row `lane`, two 32-bit words = channels 32qt .. 32qt+31 -> four 8-position chunks ----
                 {
-                    const uint4 kw = *reinterpret_cast<const uint4 *>(gb + swz128((uint32_t)(lane * TS + h * 32 + 16 * hf), p.swz));
-                    const uint32_t wv[4] = {kw.x, kw.y, kw.z, kw.w};
-                    uint8_t *row = ktile + 16 * (32 * ub + lane) + (8 * hf) * 2048;
-#pragma unroll
-                    for (int jw = 0; jw < 4; ++jw) {
-                        const uint32_t wd = wv[jw];
-                        const uint32_t M = 0x03000300u;
-                        *reinterpret_cast<uint4 *>(row + (2 * jw) * 2048) = make_uint4((wd << 8) & M, (wd << 6) & M, (wd << 4) & M, (wd << 2) & M);
-                        *reinterpret_cast<uint4 *>(row + (2 * jw + 1) * 2048) = make_uint4(wd & M, (wd >> 2) & M, (wd >> 4) & M, (wd >> 6) & M);
-                    }
+                    const uint2 kw = *reinterpret_cast<const uint2 *>(gb + swz128((uint32_t)(lane * TS + h * 32 + 8 * qt), p.swz));
+                    uint8_t *row = ktile + 16 * (32 * ub + lane) + (4 * qt) * 2048;
+                    const uint32_t M = 0x03000300u;
+                    *reinterpret_cast<uint4 *>(row) = make_uint4((kw.x << 8) & M, (kw.x << 6) & M, (kw.x << 4) & M, (kw.x << 2) & M);
+                    *reinterpret_cast<uint4 *>(row + 2048) = make_uint4(kw.x & M, (kw.x >> 2) & M, (kw.x >> 4) & M, (kw.x >> 6) & M);
+                    *reinterpret_cast<uint4 *>(row + 4096) = make_uint4((kw.y << 8) & M, (kw.y << 6) & M, (kw.y << 4) & M, (kw.y << 2) & M);
+                    *reinterpret_cast<uint4 *>(row + 6144) = make_uint4(kw.y & M, (kw.y >> 2) & M, (kw.y >> 4) & M, (kw.y >> 6) & M);
                 }
-                // ---- B tile rows of this unit (query x 2^(e_k + FBQ)) and the fp32 q.zp sums, positions 64hf .. 64hf+63:
-                //      lane = (8-position chunk c, head j4 [+4]) ----
+                TCTR(7, tr8 + 1);
+                // ---- B tile rows of this unit (query x 2^(e_k + FBQ)) and the fp32 q.zp sums of positions 32qt .. 32qt+31:
+                //      lane = (8-position chunk c of 4, head j of 8) ----
                 {
-                    const int c = lane >> 2, j4 = lane & 3;
-                    const int blk16 = 4 * hf + (c >> 1), c0 = 16 * blk16 + 4 * (c & 1);   // channels c0..c0+3 (even positions), c0+8.. (odd)
-                    const uint32_t ea = *reinterpret_cast<const uint32_t *>(gb + p.o_ks + h * 128 + c0);
-                    const uint32_t eb = *reinterpret_cast<const uint32_t *>(gb + p.o_ks + h * 128 + c0 + 8);
-                    uint32_t fac[4];
+                    const int c = lane & 3, j = lane >> 2;
+                    const int kc = 4 * qt + c;                                            // chunk of the row
+                    const int c0 = 16 * (kc >> 1) + 4 * (kc & 1);                         // channels c0..c0+3 (even positions), c0+8.. (odd)
+                    float sum = 0.f;
+                    if (j < GQAP) {
+                        const uint32_t ea = *reinterpret_cast<const uint32_t *>(gb + p.o_ks + h * 128 + c0);
+                        const uint32_t eb = *reinterpret_cast<const uint32_t *>(gb + p.o_ks + h * 128 + c0 + 8);
+                        uint32_t fac[4];
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        bool c1, c2;
-                        const uint32_t fa = tc_pow2_f16(max((int)(int8_t)(ea >> (8 * t)), -126), TC_FBQ, c1);
-                        const uint32_t fb = tc_pow2_f16(max((int)(int8_t)(eb >> (8 * t)), -126), TC_FBQ, c2);
-                        clamped_any |= c1 | c2;
-                        fac[t] = fa | (fb << 16);
-                    }
-                    const uint2 za = *reinterpret_cast<const uint2 *>(gb + p.o_kz + h * 256 + 2 * c0);
-                    const uint2 zb = *reinterpret_cast<const uint2 *>(gb + p.o_kz + h * 256 + 2 * (c0 + 8));
-                    const float zpa[4] = {bf16_bits_to_f32(za.x & 0xFFFFu), bf16_bits_to_f32(za.x >> 16), bf16_bits_to_f32(za.y & 0xFFFFu), bf16_bits_to_f32(za.y >> 16)};
-                    const float zpb[4] = {bf16_bits_to_f32(zb.x & 0xFFFFu), bf16_bits_to_f32(zb.x >> 16), bf16_bits_to_f32(zb.y & 0xFFFFu), bf16_bits_to_f32(zb.y >> 16)};
-                    const int pos0 = 64 * hf + 8 * c;
-#pragma unroll
-                    for (int pass = 0; pass < GQAP / 4; ++pass) {
-                        const int j = j4 + 4 * pass;
-                        const int qrow = (h * GQAP + j) * 128 + pos0;
+                        for (int t = 0; t < 4; ++t) {
+                            bool c1, c2;
+                            const uint32_t fa = tc_pow2_f16(max((int)(int8_t)(ea >> (8 * t)), -126), TC_FBQ, c1);
+                            const uint32_t fb = tc_pow2_f16(max((int)(int8_t)(eb >> (8 * t)), -126), TC_FBQ, c2);
+                            clamped_any |= c1 | c2;
+                            fac[t] = fa | (fb << 16);
+                        }
+                        const uint2 za = *reinterpret_cast<const uint2 *>(gb + p.o_kz + h * 256 + 2 * c0);
+                        const uint2 zb = *reinterpret_cast<const uint2 *>(gb + p.o_kz + h * 256 + 2 * (c0 + 8));
+                        const int qrow = (h * GQAP + j) * 128 + 8 * kc;
                         const uint4 q = *reinterpret_cast<const uint4 *>(s_q16 + qrow);
-                        const int n = ub * GQAP + j;
-                        *reinterpret_cast<uint4 *>(s_bq + x * BQ_BYTES + 16 * n + (8 * hf + c) * (16 * N_QK)) =
+                        *reinterpret_cast<uint4 *>(s_bq + x * BQ_BYTES + 16 * (ub * GQAP + j) + kc * (16 * N_QK)) =
                             make_uint4(hmul2_f16(q.x, fac[0]), hmul2_f16(q.y, fac[1]), hmul2_f16(q.z, fac[2]), hmul2_f16(q.w, fac[3]));
                         const uint4 r = *reinterpret_cast<const uint4 *>(s_qraw + qrow);
-                        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
-                        float sum = 0.f;
+                        const uint32_t rw[4] = {r.x, r.y, r.z, r.w}, zaw[4] = {za.x & 0xFFFFu, za.x >> 16, za.y & 0xFFFFu, za.y >> 16},
+                                       zbw[4] = {zb.x & 0xFFFFu, zb.x >> 16, zb.y & 0xFFFFu, zb.y >> 16};
 #pragma unroll
                         for (int t = 0; t < 4; ++t)
-                            sum = fmaf(bf16_bits_to_f32(rw[t] & 0xFFFFu), zpa[t], fmaf(bf16_bits_to_f32(rw[t] >> 16), zpb[t], sum));
-                        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
-                        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
-                        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
-                        if (c == 0) reinterpret_cast<float *>(side + TC_SIDE_QZ)[ub * 16 + hf * 8 + j] = sum;
+                            sum = fmaf(bf16_bits_to_f32(rw[t] & 0xFFFFu), bf16_bits_to_f32(zaw[t]), fmaf(bf16_bits_to_f32(rw[t] >> 16), bf16_bits_to_f32(zbw[t]), sum));
                     }
+                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+                    if (c == 0 && j < GQAP) reinterpret_cast<float *>(side + TC_SIDE_QZ)[ub * 32 + qt * 8 + j] = sum;
                 }
-                // ---- V factors of tokens 16hf .. 16hf+15: lane = (token, pair of scale groups) ----
+                TCTR(7, tr8 + 2);
+                // ---- V factors of tokens 8qt .. 8qt+7: lane = (token, scale group) ----
                 {
-                    const int tk = 16 * hf + (lane & 15), cg0 = 2 * (lane >> 4);
-                    uint32_t fpair = 0u, zpair = 0u;
+                    const int tk = 8 * qt + (lane & 7), cg = lane >> 3;
+                    uint32_t fbits = 0u, zbits = 0u;
                     if (32 * g + tk < ntok) {
-                        const uint32_t ve = *reinterpret_cast<const uint16_t *>(gb + p.o_vs + (tk * H + h) * 4 + cg0);
-                        const uint32_t vz2 = *reinterpret_cast<const uint32_t *>(gb + p.o_vz + (tk * H + h) * 8 + 2 * cg0);
-                        bool c1, c2;
-                        fpair = tc_pow2_f16((int)(int8_t)(ve & 0xFFu), TC_FBV, c1, TC_VF_LIMIT) | (tc_pow2_f16((int)(int8_t)(ve >> 8), TC_FBV, c2, TC_VF_LIMIT) << 16);
-                        clamped_any |= c1 | c2;
-                        // the zero-point carries the same 2^FBV as the scale factor, so that both terms of the output agree
-                        zpair = f16_bits_sat(bf16_bits_to_f32(vz2 & 0xFFFFu) * (float)(1 << TC_FBV)) |
-                                (f16_bits_sat(bf16_bits_to_f32(vz2 >> 16) * (float)(1 << TC_FBV)) << 16);
+                        bool c1;
+                        fbits = tc_pow2_f16((int)(int8_t)gb[p.o_vs + (tk * H + h) * 4 + cg], TC_FBV, c1, TC_VF_LIMIT);
+                        clamped_any |= c1;
+                        zbits = *reinterpret_cast<const uint16_t *>(gb + p.o_vz + (tk * H + h) * 8 + 2 * cg);   // bf16, as stored
                     }
-                    *reinterpret_cast<uint32_t *>(side + TC_SIDE_VF + (ub * 32 + tk) * 8 + 2 * cg0) = fpair;
-                    *reinterpret_cast<uint32_t *>(side + TC_SIDE_VZ + (ub * 32 + tk) * 8 + 2 * cg0) = zpair;
+                    *reinterpret_cast<uint16_t *>(side + TC_SIDE_VF + (ub * 32 + tk) * 8 + 2 * cg) = (uint16_t)fbits;
+                    *reinterpret_cast<uint16_t *>(side + TC_SIDE_VZ + (ub * 32 + tk) * 8 + 2 * cg) = (uint16_t)zbits;
                 }
-                // ---- outliers of this half's channels, written over their slots of the K tile (after the codes) ----
+                TCTR(7, tr8 + 3);
+                // ---- outliers of channel 32qt + lane, written over their slots of the K tile (after the codes) ----
                 __syncwarp();
+                TCTR(7, tr8 + 4);
                 if (k_out > 0) {
-                    const int d0 = 64 * hf + 2 * lane;
-                    const uint32_t e2 = *reinterpret_cast<const uint16_t *>(gb + p.o_ks + h * 128 + d0);
-                    const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
-                    uint32_t ms2 = 0, mc2 = 0;
-                    if (p.use_map) {
-                        ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
-                        mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
-                    }
-                    const uint2 bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
-                    const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nbytes_oval;
-                    // Channels with a large scale: the entry's rounding error (up to 2^-9 of a code step) times the scale
-                    // would show in the logits, so their outliers' residuals go to spare positions 128 + 8hf + slot of the
-                    // row, whose B entries are the channel's own times 2^-10.  Up to 8 such channels per half.
-                    const int e_c0 = (int)(int8_t)(e2 & 0xFFu), e_c1 = (int)(int8_t)(e2 >> 8);
-                    const uint32_t fm0 = __ballot_sync(0xFFFFFFFFu, e_c0 >= TC_FLAG_E), fm1 = __ballot_sync(0xFFFFFFFFu, e_c1 >= TC_FLAG_E);
-                    const uint32_t lt = (1u << lane) - 1u;
-                    const int slot_c[2] = {__popc(fm0 & lt), __popc(fm0) + __popc(fm1 & lt)};
-                    const bool res_c[2] = {e_c0 >= TC_FLAG_E && slot_c[0] < 8, e_c1 >= TC_FLAG_E && slot_c[1] < 8};
-                    const int kc = 16 + hf;                                   // the residual chunk of this half
-                    *reinterpret_cast<uint4 *>(ktile + 16 * (32 * ub + lane) + kc * 2048) = make_uint4(0u, 0u, 0u, 0u);
-                    uint8_t *bq_res = s_bq + x * BQ_BYTES + 16 * (ub * GQAP) + kc * (16 * N_QK);
-                    if (lane < GQAP) *reinterpret_cast<uint4 *>(bq_res + 16 * lane) = make_uint4(0u, 0u, 0u, 0u);
-                    __syncwarp();
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const int e = min(max((int)(int8_t)(e2 >> (8 * c)), -126), 100);
-                        const float inv_s = __uint_as_float((uint32_t)(127 - 16 - e) << 23);   // 2^-16 / scale
-                        const float zp = bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu));
-                        // the outlier's value: level / map scale + map centre (dedicated map) or level * scale + zp (shared map)
-                        const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
-                        float A = sc, Bc = zp;
-                        if (p.use_map) {
-                            A = __fdividef(1.f, bf16_bits_to_f32(c ? (ms2 >> 16) : (ms2 & 0xFFFFu)));
-                            Bc = bf16_bits_to_f32(c ? (mc2 >> 16) : (mc2 & 0xFFFFu));
-                        }
-                        uint32_t bits = c ? bm2.y : bm2.x;
-                        const int pos = tc_pos_of(d0 + c);
-                        uint8_t *col = ktile + 16 * (32 * ub) + (pos >> 3) * 2048 + (pos & 7) * 2;
-                        uint8_t *rcol = ktile + 16 * (32 * ub) + kc * 2048 + 2 * slot_c[c];
-                        const bool res = res_c[c];
-                        if (res) {                                         // B entries of the spare position: the channel's, times 2^-10
-                            bool cl;
-                            const uint32_t f = tc_pow2_f16(e, TC_FBQ - TC_RES_SHIFT, cl);
-                            for (int j = 0; j < gqa; ++j) {
-                                const uint32_t qv = s_q16[(h * GQAP + j) * 128 + pos];
-                                *reinterpret_cast<uint16_t *>(bq_res + 16 * j + 2 * slot_c[c]) = (uint16_t)(hmul2_f16(qv, f) & 0xFFFFu);
-                            }
-                        }
-                        const uint8_t *sv = ov + c * nbytes_oval;
-                        int r = __popc(bits) - 1;
-                        if (r + 1 != k_out) or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
-                        r = min(r, 2 * nbytes_oval - 1);
-                        while (bits) {
-                            const int pz = 31 - __clz(bits);
-                            bits ^= 1u << pz;
-                            const uint32_t nib = ((uint32_t)sv[r >> 1] >> (4 * (r & 1))) & 0xFu;
-                            --r;
-                            // The reference adds to the base value code * scale + zp a delta rounded to bf16
-                            // (paged_decode.py:1923-1950); the same rounding here, with the base code read back from the
-                            // slot the entry is about to replace, keeps the two paths' rounding noise in step.
-                            const float cf = (float)(*reinterpret_cast<const uint16_t *>(col + 16 * pz) >> 8);
-                            const float delta = bf16_round_f32(fmaf(s_lut[nib], A, Bc) - fmaf(cf, sc, zp));
-                            const float X = fmaf(delta, inv_s, cf * 1.52587890625e-05f);      // (code + delta / scale) * 2^-16
-                            const uint32_t hbits = f16_bits_sat(X);
-                            *reinterpret_cast<uint16_t *>(col + 16 * pz) = (uint16_t)hbits;
-                            if (res) {
-                                const float back = __half2float(__ushort_as_half((unsigned short)hbits));
-                                *reinterpret_cast<uint16_t *>(rcol + 16 * pz) = (uint16_t)f16_bits_sat((X - back) * (float)(1 << TC_RES_SHIFT));
-                            }
-                        }
+                    switch (k_out) {
+                        case 2: tc_splice<2>(p, gb, ktile, s_bq + x * BQ_BYTES, s_q16, s_lut, h, ub, qt, lane, GQAP, N_QK, clamped_any); break;
+                        case 4: tc_splice<4>(p, gb, ktile, s_bq + x * BQ_BYTES, s_q16, s_lut, h, ub, qt, lane, GQAP, N_QK, clamped_any); break;
+                        case 6: tc_splice<6>(p, gb, ktile, s_bq + x * BQ_BYTES, s_q16, s_lut, h, ub, qt, lane, GQAP, N_QK, clamped_any); break;
+                        case 8: tc_splice<8>(p, gb, ktile, s_bq + x * BQ_BYTES, s_q16, s_lut, h, ub, qt, lane, GQAP, N_QK, clamped_any); break;
+                        default: tc_splice<-1>(p, gb, ktile, s_bq + x * BQ_BYTES, s_q16, s_lut, h, ub, qt, lane, GQAP, N_QK, clamped_any); break;
                     }
                 }
             }
             if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
+            TCTR(trr, trn + 2);
+            TCTR(7, tr8 + 5);
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(TBAR(TB_KREADY + x));
+            TCTR(trr, trn + 3);
 
-            // ---- V codes of this half into the V tile (channel-major), once the tile's previous user is done ----
+            // ---- V codes of this quarter into the V tile (channel-major), once the tile's previous user is done ----
             const int vb = i % P.nvb;
             if (i >= P.nvb) {
                 const int jdone = i - P.nvb;
                 if (!mbar_wait(TBAR(TB_PVDONE + (jdone & 3)), (uint32_t)(jdone >> 2) & 1u)) { dead = true; break; }
             }
+            TCTR(trr, trn + 4);
             if (valid) {
-                uint4 vw = make_uint4(0u, 0u, 0u, 0u);
-                if (32 * g + lane < ntok) vw = *reinterpret_cast<const uint4 *>(gb + p.o_vm + swz128((uint32_t)(lane * TS + h * 32 + 16 * hf), p.swz));
-                const uint32_t wv[4] = {vw.x, vw.y, vw.z, vw.w};
-                uint8_t *vt = s_vtile + vb * TC_VTILE + ub * TC_UNIT_TILE + 16 * lane + (8 * hf) * 512;
-#pragma unroll
-                for (int jw = 0; jw < 4; ++jw) {
-                    const uint32_t wd = wv[jw];
-                    *reinterpret_cast<uint4 *>(vt + (2 * jw) * 512) = make_uint4(code_pair(wd, 0), code_pair(wd, 1), code_pair(wd, 2), code_pair(wd, 3));
-                    *reinterpret_cast<uint4 *>(vt + (2 * jw + 1) * 512) = make_uint4(code_pair(wd, 4), code_pair(wd, 5), code_pair(wd, 6), code_pair(wd, 7));
-                }
+                uint2 vw = make_uint2(0u, 0u);
+                if (32 * g + lane < ntok) vw = *reinterpret_cast<const uint2 *>(gb + p.o_vm + swz128((uint32_t)(lane * TS + h * 32 + 8 * qt), p.swz));
+                uint8_t *vt = s_vtile + vb * TC_VTILE + ub * TC_UNIT_TILE + 16 * lane + (4 * qt) * 512;
+                *reinterpret_cast<uint4 *>(vt) = make_uint4(code_pair(vw.x, 0), code_pair(vw.x, 1), code_pair(vw.x, 2), code_pair(vw.x, 3));
+                *reinterpret_cast<uint4 *>(vt + 512) = make_uint4(code_pair(vw.x, 4), code_pair(vw.x, 5), code_pair(vw.x, 6), code_pair(vw.x, 7));
+                *reinterpret_cast<uint4 *>(vt + 1024) = make_uint4(code_pair(vw.y, 0), code_pair(vw.y, 1), code_pair(vw.y, 2), code_pair(vw.y, 3));
+                *reinterpret_cast<uint4 *>(vt + 1536) = make_uint4(code_pair(vw.y, 4), code_pair(vw.y, 5), code_pair(vw.y, 6), code_pair(vw.y, 7));
             }
             fence_async_smem();
             __syncwarp();
@@ -751,11 +823,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 mbar_arrive(TBAR(TB_VREADY + vb));
                 if (valid) mbar_arrive(TBAR(TB_EMPTY + s));
             }
+            TCTR(trr, trn + 5);
         }
         if (dead && lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
     }
+    if (warp == TC_W_SOFTMAX) TCTR(6, 2);
     tc_fence_before();
     __syncthreads();
+    if (warp == 0) TCTR(6, 3);
     if (warp == TC_W_MMA) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P.tmem_cols));
 #undef TBAR
 }
@@ -770,7 +845,7 @@ static size_t tc_layout(TcParams &P, int gqap, int max_groups_per_split) {
     P.nb = H > 4 ? H : 4;
     P.tab_groups = max_groups_per_split;
     P.tab_pages = max_groups_per_split * p.ppg;
-    const size_t fixed = 2 * TC_KTILE + 2 * bq + 2 * 4 * 2 * pt + TC_ONES + 2 * TC_SIDE_BYTES + 2 * (size_t)H * gqap * 256 + 64 +
+    const size_t fixed = 2 * TC_KTILE + 2 * bq + 2 * 4 * pt + 2 * TC_SIDE_BYTES + 2 * (size_t)H * gqap * 256 + 64 +
                          (size_t)(P.tab_pages + P.tab_groups) * 4 + 64 + TB_COUNT * 8 + TM_WORDS * 4 + 64 +
                          (size_t)(4 * p.ppg + 6) * sizeof(CopyDesc) + 1024 /* alignment slack */ + 1024 /* offset rounding */;
     const size_t limit = 232448;
@@ -785,8 +860,6 @@ static size_t tc_layout(TcParams &P, int gqap, int max_groups_per_split) {
                 break;
             }
     if (!best_ns) return 0;
-    if (const char *e = getenv("OMMX_TC_NS")) { int v = atoi(e); if (v >= min_stages && v <= best_ns) best_ns = v; }
-    if (const char *e = getenv("OMMX_TC_NVB")) { int v = atoi(e); if (v >= 1 && v <= best_nvb) best_nvb = v; }
     p.nstages = best_ns;
     P.nvb = best_nvb;
     auto up = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
@@ -794,8 +867,7 @@ static size_t tc_layout(TcParams &P, int gqap, int max_groups_per_split) {
     o = up(o, 128); P.o_ktile = (uint32_t)o; o += 2 * TC_KTILE;
     P.o_vtile = (uint32_t)o; o += (size_t)best_nvb * TC_VTILE;
     P.o_bq = (uint32_t)o; o += 2 * bq;
-    P.o_ptile = (uint32_t)o; o += 2 * 4 * 2 * pt;
-    P.o_ones = (uint32_t)o; o += TC_ONES;
+    P.o_ptile = (uint32_t)o; o += 2 * 4 * pt;
     P.o_side = (uint32_t)o; o += 2 * TC_SIDE_BYTES;
     P.o_q16 = (uint32_t)o; o += (size_t)H * gqap * 256;
     P.o_qraw = (uint32_t)o; o += (size_t)H * gqap * 256;
@@ -818,6 +890,15 @@ static int launch_tc(const TcParams &P, dim3 grid, size_t smem, cudaStream_t st)
         OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_tc_kernel<GQAP, NB8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_smem[dev].store(smem, std::memory_order_release);
     }
+    static std::atomic<int> regs_state[MAX_DEVICES];   // 0 unknown, 1 enough, 2 too few
+    int regs_ok = regs_state[dev].load(std::memory_order_acquire);
+    if (regs_ok == 0) {
+        cudaFuncAttributes fa;
+        OMMX_CUDA_TRY(cudaFuncGetAttributes(&fa, decode_stage1_tc_kernel<GQAP, NB8>));
+        regs_ok = fa.numRegs * TC_THREADS >= 128 * 120 + (TC_THREADS - 128) * 72 ? 1 : 2;   // setmaxnreg.inc must find the registers
+        regs_state[dev].store(regs_ok, std::memory_order_release);
+    }
+    if (regs_ok != 1) return fail(OMMX_E_CUDA, "the tensor-core stage 1 was compiled with fewer registers than its warp roles need");
     decode_stage1_tc_kernel<GQAP, NB8><<<grid, TC_THREADS, smem, st>>>(P);
     OMMX_CUDA_TRY(cudaGetLastError());
     count_launch();

@@ -263,3 +263,38 @@ def test_store_then_decode_end_to_end():
     check_close(o, case.oracle_kernel_arith(split_pv=True)[0], ctx="store->decode")
     from open_ommx_serve_b200 import launch_stats
     assert launch_stats()["stage1"] > 0 and launch_stats()["bitmap"] > 0
+
+
+@pytest.fixture
+def tensor_core_stage1(monkeypatch):
+    """Route stage 1 through the tcgen05 kernel (the launcher reads the variable per call)."""
+    monkeypatch.setenv("OMMX_B200_STAGE1", "tc")
+    yield
+
+
+@pytest.mark.parametrize("H,Hq,seq,splits", [(8, 32, 4136, None), (8, 32, 16384, 37), (4, 16, 8232, 4), (2, 8, 8232, 16),
+                                             (1, 4, 4136, 4), (1, 8, 8232, 8), (2, 16, 3000, None), (4, 12, 1500, None)])
+def test_tensor_core_stage1_matches_oracle(tensor_core_stage1, H, Hq, seq, splits):
+    """The tcgen05 / tensor-memory stage 1 (opt-in) against the same two gates as the default kernel."""
+    _run_and_check(Case([seq], H=H, Hq=Hq, seed=H * 7 + Hq + seq), num_kv_splits=splits)
+
+
+@pytest.mark.parametrize("k,mag", [(0, 12.0), (2, 4.0), (6, 30.0), (8, 12.0), (12, 12.0)])
+def test_tensor_core_stage1_outlier_sweep(tensor_core_stage1, k, mag):
+    _run_and_check(Case([2048], seed=k + 1, k=k, mag=mag), lse_atol_fp32=5e-2 if mag < 20 else 0.2)
+
+
+def test_tensor_core_stage1_ragged_batch_and_segments(tensor_core_stage1):
+    lens = [40, 71, 72, 1024, 5000, 333, 8, 2049]
+    _run_and_check(Case(lens, seed=11, tables_dtype=torch.int64))
+    _run_and_check(Case([1000], seed=3, outlier_map=False))
+    _run_and_check(Case([3000], seed=32, page_size=32))
+
+
+def test_tensor_core_stage1_agrees_with_default_kernel(monkeypatch):
+    case = Case([9000, 700], seed=8)
+    monkeypatch.setenv("OMMX_B200_STAGE1", "legacy")
+    o1, l1 = case.run(num_kv_splits=24)
+    monkeypatch.setenv("OMMX_B200_STAGE1", "tc")
+    o2, l2 = case.run(num_kv_splits=24)
+    assert (o1 - o2).abs().max().item() < 2e-3 and (l1 - l2).abs().max().item() < 2e-3
