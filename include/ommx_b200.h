@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define OMMX_B200_ABI_VERSION 2
+#define OMMX_B200_ABI_VERSION 3
 
 /* host-side argument errors (return values) */
 #define OMMX_E_ARG          (-1)   /* null pointer, bad size, misaligned plane */
@@ -40,6 +40,10 @@ extern "C" {
 #define OMMX_DT_F32   0
 #define OMMX_DT_BF16  1
 #define OMMX_DT_F16   2
+
+/* outlier-index plane encoding (ommx_kv_planes.outlier_index) */
+#define OMMX_OIDX_BITMASK 0
+#define OMMX_OIDX_RELIDX7 1
 
 /* how k_scale / v_scale are stored */
 #define OMMX_SCALE_INT8_EXP 0      /* int8 power-of-two exponent (the serving default) */
@@ -71,6 +75,11 @@ typedef struct ommx_kv_planes {
     int32_t scale_kind;           /* OMMX_SCALE_* (zp and map planes are f32 iff OMMX_SCALE_F32) */
     void *k_base, *k_scale, *k_zp, *k_obmp, *k_oval, *k_mapscale, *k_mapcenter;
     void *v_main, *v_scale, *v_zp;
+    int32_t outlier_index;        /* what k_obmp holds per (group, head, channel) frame: OMMX_OIDX_BITMASK = 4 bytes, bit p
+                                     set iff token p is an outlier (attention/codec.py:330-372); OMMX_OIDX_RELIDX7 = the
+                                     reference's relidx7 stream, ceil(7k/8) bytes of 7-bit token positions, ascending,
+                                     LSB first (attention/codec.py:91-130, its k_oidx plane).  Decode reads both; the
+                                     store kernels write the bitmask (ommx_b200_outlier_index_convert makes the other). */
 } ommx_kv_planes;
 
 /*
@@ -94,6 +103,17 @@ typedef struct ommx_pack_args {
 } ommx_pack_args;
 
 int ommx_b200_pack_kv(const ommx_pack_args *args, void *stream);
+
+/*
+ * Re-encode an outlier-index plane of `frames` (group, head, channel) frames with k outliers each between the
+ * flat bitmask (4 bytes per frame) and relidx7 (ceil(7k/8) bytes per frame): to_relidx7 = 1 bitmask -> relidx7,
+ * 0 the other way.  Replaces _pack_relidx7_frames / _unpack_relidx7_streams (attention/pack.py:128-176) and the
+ * codec they call (attention/codec.py:91-130); both encodings list the same positions, so the value plane is
+ * shared.  A frame whose bitmask does not hold k bits, or whose stream names a position beyond 31 or the same
+ * position twice, raises OMMX_ST_BAD_GROUP in *status (optional) and is written as far as it goes.
+ */
+int ommx_b200_outlier_index_convert(const void *src, void *dst, int64_t frames, int32_t k, int32_t to_relidx7,
+                                    int32_t *status, void *stream);
 
 /*
  * Paged decode attention.  Replaces ommx_paged_decode_attention_canonical

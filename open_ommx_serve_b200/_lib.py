@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(PKG, "libommx_b200.so")
 
 OMMX_DT_F32, OMMX_DT_BF16, OMMX_DT_F16 = 0, 1, 2
 OMMX_SCALE_INT8_EXP, OMMX_SCALE_BF16, OMMX_SCALE_F32 = 0, 1, 2
+OMMX_OIDX_BITMASK, OMMX_OIDX_RELIDX7 = 0, 1
 ST_BAD_PAGE, ST_BAD_GROUP, ST_NONFINITE, ST_TIMEOUT, ST_BAD_LENGTH, ST_SCALE_RANGE = 1, 2, 4, 8, 16, 32
 STATUS_NAMES = {ST_BAD_PAGE: "page id out of range", ST_BAD_GROUP: "group slot out of range",
                 ST_NONFINITE: "non-finite K/V value", ST_TIMEOUT: "a bounded device wait ran out",
@@ -28,7 +29,7 @@ class KVPlanes(C.Structure):
                 ("k_base", C.c_void_p), ("k_scale", C.c_void_p), ("k_zp", C.c_void_p),
                 ("k_obmp", C.c_void_p), ("k_oval", C.c_void_p), ("k_mapscale", C.c_void_p),
                 ("k_mapcenter", C.c_void_p), ("v_main", C.c_void_p), ("v_scale", C.c_void_p),
-                ("v_zp", C.c_void_p)]
+                ("v_zp", C.c_void_p), ("outlier_index", C.c_int32)]
 
 
 class PackArgs(C.Structure):
@@ -79,6 +80,7 @@ class KVAppendArgs(C.Structure):
 #: every symbol include/ommx_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "ommx_b200_pack_kv": (C.c_int, [C.POINTER(PackArgs), C.c_void_p]),
+    "ommx_b200_outlier_index_convert": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "ommx_b200_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_decode_stage1": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "ommx_b200_decode_stage2": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),

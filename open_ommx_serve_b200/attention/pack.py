@@ -52,8 +52,9 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
-def planes_struct(planes: dict, *, k: int, outlier_map: bool) -> "_lib.KVPlanes":
-    """Fill the C plane descriptor from a plane dict (every plane contiguous, same device)."""
+def planes_struct(planes: dict, *, k: int, outlier_map: bool, relidx7: bool = False) -> "_lib.KVPlanes":
+    """Fill the C plane descriptor from a plane dict (every plane contiguous, same device).  With ``relidx7`` the
+    outlier-index plane is ``k_oidx`` (the reference's 7-bit position stream) instead of the flat bitmask ``k_obmp``."""
     kb = planes["k_base"]
     for name in ("k_base", "k_scale", "k_zp", "k_obmp", "k_oval", "k_fp4_mapscale",
                  "k_fp4_mapcenter", "v_main", "v_scale", "v_zp"):
@@ -79,7 +80,14 @@ def planes_struct(planes: dict, *, k: int, outlier_map: bool) -> "_lib.KVPlanes"
     s.kv_outlier_map = 1 if (outlier_map and k > 0) else 0
     s.scale_kind = kind
     s.k_base, s.k_scale, s.k_zp = _ptr(kb), _ptr(ks), _ptr(planes["k_zp"])
-    s.k_obmp, s.k_oval = _ptr(planes.get("k_obmp")), _ptr(planes.get("k_oval"))
+    if relidx7 and k > 0:
+        idx = planes.get("k_oidx")
+        if idx is None or not idx.is_contiguous() or idx.dtype != torch.uint8 or int(idx.shape[-1]) != (7 * int(k) + 7) // 8:
+            raise ValueError(f"k_oidx must be a contiguous uint8 plane of ceil(7k/8)={(7 * int(k) + 7) // 8} bytes per frame")
+        s.k_obmp, s.outlier_index = _ptr(idx), _lib.OMMX_OIDX_RELIDX7
+    else:
+        s.k_obmp, s.outlier_index = _ptr(planes.get("k_obmp")), _lib.OMMX_OIDX_BITMASK
+    s.k_oval = _ptr(planes.get("k_oval"))
     s.k_mapscale, s.k_mapcenter = _ptr(planes.get("k_fp4_mapscale")), _ptr(planes.get("k_fp4_mapcenter"))
     s.v_main, s.v_scale, s.v_zp = _ptr(planes["v_main"]), _ptr(planes["v_scale"]), _ptr(planes["v_zp"])
     return s
@@ -176,7 +184,8 @@ def ommx_pack_kv_canonical_block(
     ``K``/``V`` are ``[num_tokens, n_kv_heads, head_dim]`` float32 / bfloat16 / float16; CPU
     tensors are copied to ``device`` (default: the current CUDA device) first.  The returned
     dict has the reference's keys (``attention/pack.py:628-655``).  Served here: the flat
-    bitmask outlier index (``outlier_repr='bitmap'``), 32-token / 32-channel groups, INT2 V.
+    bitmask and the relidx7 outlier index (``outlier_repr='bitmap'`` / ``'relidx7'``, k <= 16),
+    32-token / 32-channel groups, INT2 V.
     Anything else raises ``NotImplementedError`` - there is no slower fallback.
     ``check_finite`` reads one status word back (a host sync, as the reference's own finite
     check is) and raises ``ValueError`` on NaN/Inf input.
@@ -211,9 +220,11 @@ def ommx_pack_kv_canonical_block(
         raise ValueError(f"head_dim={D} must be a multiple of {gc}")
     if k < 0 or k > gt:
         raise ValueError(f"outliers_per_vector={k} out of range [0, {gt}]")
-    if k > 0 and repr_l != "bitmap":
+    if k > 0 and repr_l == "combinadic":
         raise NotImplementedError(
-            f"outlier_repr={repr_l!r}: this build packs the flat-bitmask outlier index only")
+            "outlier_repr='combinadic': this build packs the flat-bitmask and relidx7 outlier indices")
+    if k > 16 and repr_l == "relidx7":
+        raise NotImplementedError("relidx7 planes are packed for up to 16 outliers per vector")
     if gt != 32 or gc != 32:
         raise NotImplementedError("this build packs 32-token K groups and 32-channel V groups only")
     if vfmt != "i2":
@@ -239,8 +250,17 @@ def ommx_pack_kv_canonical_block(
         if bits:
             raise RuntimeError(f"KV pack: device reported {_lib.status_text(bits)}")
     G, pages = T // gt, T // int(page_size)
+    if k > 0 and repr_l == "relidx7":
+        # same outlier set, other index encoding: k ascending 7-bit positions per frame (the value plane is shared)
+        lib = _lib.load()
+        oidx = torch.zeros(G, H, D, (7 * k + 7) // 8, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            _lib.check(lib.ommx_b200_outlier_index_convert(planes["k_obmp"].data_ptr(), oidx.data_ptr(), G * H * D, k, 1, None,
+                                                           torch.cuda.current_stream().cuda_stream),
+                       "ommx_b200_outlier_index_convert")
+        planes["k_oidx"], planes["k_obmp"] = oidx, None
     planes.update({
-        "k_field_bytes": 4 if k > 0 else 0,
+        "k_field_bytes": (4 if repr_l == "bitmap" else (7 * k + 7) // 8) if k > 0 else 0,
         "req_to_token": torch.arange(pages, dtype=torch.int32, device=device).reshape(1, pages),
         "req_to_group": torch.arange(G, dtype=torch.int32, device=device).reshape(1, G),
         "head_dim": D, "n_kv_heads": H, "num_tokens": T, "n_groups": G, "page_size": int(page_size),

@@ -211,10 +211,14 @@ def ommx_paged_decode_attention_canonical(
     # paged_decode.py:3055-3058); this kernel walks a 64-bit stream, so the 32-bit bitmask serves k <= 16.
     if bitmap_read and k > 16:
         raise ValueError(f"bitmap_read holds the k_oval stream in two 32-bit words, i.e. k <= 16; got k={k}.")
-    if k > 0 and not bitmap_read:
-        raise NotImplementedError(
-            "this build reads the flat-bitmask outlier index only: pass bitmap_read=True with k_obmp "
-            "(relidx7 / combinadic planes are not served)")
+    relidx7_read = k > 0 and not bitmap_read
+    if relidx7_read and combinadic_read:
+        raise NotImplementedError("combinadic rank planes are not served: derive relidx7 planes at load time "
+                                  "(the reference's derive_relidx7_from_combinadic) or pack with outlier_repr='bitmap'")
+    if relidx7_read and k_oidx is None:
+        raise ValueError("k_outliers_per_vector > 0 without bitmap_read requires the k_oidx (relidx7) sidecar plane.")
+    if relidx7_read and k > 16:
+        raise ValueError(f"the relidx7 read path serves k <= 16; got k={k}.")
     use_map = bool(kv_outlier_map) and k > 0
     if use_map and (k_fp4_mapscale is None or k_fp4_mapcenter is None):
         raise ValueError("kv_outlier_map=True requires k_fp4_mapscale + k_fp4_mapcenter planes.")
@@ -252,12 +256,13 @@ def ommx_paged_decode_attention_canonical(
     a = _lib.DecodeArgs()
     a.q, a.q_dtype, a.batch, a.n_q_heads = q.data_ptr(), _lib.OMMX_DT_BF16, batch, head_num
     a.q_stride_b, a.q_stride_h = int(q.stride(0)), int(q.stride(1))
-    planes = {"k_base": k_base, "k_scale": k_scale, "k_zp": k_zp, "k_obmp": k_obmp if k > 0 else None,
+    planes = {"k_base": k_base, "k_scale": k_scale, "k_zp": k_zp, "k_obmp": k_obmp if (k > 0 and bitmap_read) else None,
+              "k_oidx": k_oidx if relidx7_read else None,
               "k_oval": k_oval if k > 0 else None,
               "k_fp4_mapscale": k_fp4_mapscale if use_map else None,
               "k_fp4_mapcenter": k_fp4_mapcenter if use_map else None,
               "v_main": v_main, "v_scale": v_scale, "v_zp": v_zp}
-    a.planes = planes_struct(planes, k=k, outlier_map=use_map)
+    a.planes = planes_struct(planes, k=k, outlier_map=use_map, relidx7=relidx7_read)
     if max_tail > 0:
         if k_tail is None or v_tail is None or b_tail_len is None:
             raise ValueError("max_tail_len > 0 needs k_tail, v_tail and b_tail_len")

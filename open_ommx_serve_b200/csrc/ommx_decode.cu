@@ -63,6 +63,8 @@ struct S1Params {
     int32_t B, Hq, H, gqa, q_pair_ok;    // q_pair_ok: two adjacent q elements may be fetched as one 32-bit word
     const uint8_t *k_base, *v_main, *v_scale, *v_zp, *k_scale, *k_zp, *k_ms, *k_mc, *k_obmp, *k_oval;
     int32_t ps, ppg, num_pages, num_slots, k_out, nb, use_map;
+    int32_t nbi;                         // bytes of outlier index per channel: 4 (flat bitmask) or ceil(7k/8) (relidx7, idx7 = 1)
+    int32_t idx7;
     const int32_t *b_seq_len;
     const void *r2t, *r2g;
     int32_t tbl64;
@@ -336,7 +338,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 const int gp = ci - 4 * p.ppg;
                 const bool on = gp < 2 || (k_out > 0 && (gp >= 4 || p.use_map));
                 if (on) {
-                    const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 512u : (gp == 5 ? 128u * p.nb : 256u));
+                    const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 128u * p.nbi : (gp == 5 ? 128u * p.nb : 256u));
                     d.src = gp == 0 ? p.k_scale : (gp == 1 ? p.k_zp : (gp == 2 ? p.k_ms : (gp == 3 ? p.k_mc : (gp == 4 ? p.k_obmp : p.k_oval))));
                     d.unit = (uint32_t)H * w;
                     d.dst = gbo + (uint32_t)(gp == 0 ? p.o_ks : (gp == 1 ? p.o_kz : (gp == 2 ? p.o_ms : (gp == 3 ? p.o_mc : (gp == 4 ? p.o_bm : p.o_ov)))));
@@ -563,7 +565,29 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                         ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
                         mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
                     }
-                    const uint2 bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
+                    uint2 bm2;
+                    if (!p.idx7) {
+                        bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
+                    } else {
+                        // relidx7 (attention/codec.py:91-130 of the reference): k ascending token positions, 7 bits each,
+                        // LSB first; the outlier set as a bitmask again, the value stream is shared with that encoding
+                        uint32_t m2[2];
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const uint8_t *ip = gb + p.o_bm + (h * 128 + d0 + c) * p.nbi;
+                            uint32_t w[5] = {0u, 0u, 0u, 0u, 0u};
+                            for (int i = 0; i < p.nbi; ++i) w[i >> 2] |= (uint32_t)ip[i] << (8 * (i & 3));
+                            uint32_t bits = 0u;
+                            for (int r = 0; r < k_out; ++r) {
+                                const int bp = 7 * r;
+                                const uint32_t f = __funnelshift_r(w[bp >> 5], w[(bp >> 5) + 1], bp & 31) & 0x7Fu;
+                                if (f > 31u) or_status(p.status, OMMX_ST_BAD_GROUP);
+                                else bits |= 1u << f;
+                            }
+                            m2[c] = bits;
+                        }
+                        bm2 = make_uint2(m2[0], m2[1]);
+                    }
                     uint32_t st[2] = {0, 0}, sth[2] = {0, 0};            // nibble stream of each channel: outliers 0..7, 8..15
                     const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
                     const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nb;          // 2*nb bytes, 2-byte aligned
@@ -1223,6 +1247,10 @@ static int validate_decode(const ommx_decode_args *a) {
         return fail(OMMX_E_UNSUPPORTED, "decode: only int8 power-of-two scale planes are served (pack with use_pow2)");
     if (pl.outliers_per_vector < 0 || pl.outliers_per_vector > 16)
         return fail(OMMX_E_UNSUPPORTED, "decode: outliers_per_vector=%d outside [0,16]", pl.outliers_per_vector);
+    if (pl.outlier_index != OMMX_OIDX_BITMASK && pl.outlier_index != OMMX_OIDX_RELIDX7)
+        return fail(OMMX_E_ARG, "decode: outlier_index=%d", pl.outlier_index);
+    if (pl.outlier_index == OMMX_OIDX_RELIDX7 && (128 * ((7 * pl.outliers_per_vector + 7) / 8)) % 16 != 0)
+        return fail(OMMX_E_UNSUPPORTED, "decode: relidx7 frames of %d outliers do not stage in 16-byte pieces", pl.outliers_per_vector);
     if (a->packed_start_offset != 0) return fail(OMMX_E_UNSUPPORTED, "decode: packed_start_offset must be 0");
     if (a->seg_group_base < 0) return fail(OMMX_E_ARG, "decode: seg_group_base=%d", a->seg_group_base);
     if (a->num_kv_splits < 1) return fail(OMMX_E_ARG, "decode: num_kv_splits=%d", a->num_kv_splits);
@@ -1379,6 +1407,8 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.k_obmp = (const uint8_t *)pl.k_obmp; p.k_oval = (const uint8_t *)pl.k_oval;
     p.ps = pl.page_size; p.ppg = 32 / pl.page_size; p.num_pages = pl.num_pages; p.num_slots = pl.num_group_slots;
     p.k_out = pl.outliers_per_vector; p.nb = (pl.outliers_per_vector + 1) / 2;
+    p.idx7 = (pl.outlier_index == OMMX_OIDX_RELIDX7 && pl.outliers_per_vector > 0) ? 1 : 0;
+    p.nbi = p.idx7 ? (7 * pl.outliers_per_vector + 7) / 8 : 4;
     p.use_map = (pl.kv_outlier_map && pl.outliers_per_vector > 0) ? 1 : 0;
     p.b_seq_len = a->b_seq_len; p.r2t = a->req_to_token; p.r2g = a->req_to_group; p.tbl64 = a->table_is_int64;
     p.r2t_sb = a->r2t_stride_b; p.r2g_sb = a->r2g_stride_b;
@@ -1390,7 +1420,7 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.hshift = H == 8 ? 3 : (H == 4 ? 2 : (H == 2 ? 1 : 0));
     p.o_vm = H * 1024; p.o_vs = H * 2048; p.o_vz = p.o_vs + H * 128; p.o_ks = p.o_vz + H * 256;
     p.o_kz = p.o_ks + H * 128; p.o_ms = p.o_kz + H * 256; p.o_mc = p.o_ms + H * 256; p.o_bm = p.o_mc + H * 256;
-    p.o_ov = p.o_bm + H * 512;
+    p.o_ov = (p.o_bm + H * 128 * p.nbi + 15) / 16 * 16;
     p.gb_bytes = p.o_ov + H * 128 * (p.nb > 0 ? p.nb : 0);
     // swizzled tensor-map staging of the two code planes when a page is whole 1 KB swizzle atoms and
     // the 1 KB rounding of the group block still fits shared memory (4 or 8 local kv heads)
@@ -1407,7 +1437,7 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     p.gb_bytes = (p.gb_bytes + round_to - 1) / round_to * round_to;
     p.stage_bytes = p.GS * p.gb_bytes;
     p.abl = a->abl_flags;
-    if (stage1_choice() == 1 && p.abl == 0 && p.gqa <= 8) {
+    if (stage1_choice() == 1 && p.abl == 0 && p.gqa <= 8 && !p.idx7) {
         TcParams T;
         T.s = p;
         T.s.GS = 1;

@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 const int gp = c - 4 * p.ppg;
                 const bool on = gp < 2 || (k_out > 0 && (gp >= 4 || p.use_map));
                 if (on) {
-                    const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 512u : (gp == 5 ? 128u * p.nb : 256u));
+                    const uint32_t w = gp == 0 ? 128u : (gp == 4 ? 128u * p.nbi : (gp == 5 ? 128u * p.nb : 256u));
                     d.src = gp == 0 ? p.k_scale : (gp == 1 ? p.k_zp : (gp == 2 ? p.k_ms : (gp == 3 ? p.k_mc : (gp == 4 ? p.k_obmp : p.k_oval))));
                     d.unit = (uint32_t)H * w;
                     d.dst = (uint32_t)(gp == 0 ? p.o_ks : (gp == 1 ? p.o_kz : (gp == 2 ? p.o_ms : (gp == 3 ? p.o_mc : (gp == 4 ? p.o_bm : p.o_ov)))));

@@ -771,10 +771,66 @@ static int launch_append(const ommx_kv_append_args *a, cudaStream_t st) {
 
 }  // namespace ommx
 
+namespace ommx {
+// One thread per frame.  relidx7 (ommx_gpu_serve/attention/codec.py:91-130 of the reference): the k token positions of
+// a frame, ascending, 7 bits each, LSB first, in ceil(7k/8) bytes.
+__global__ void outlier_index_convert_kernel(const uint8_t *src, uint8_t *dst, int64_t frames, int k, int to_relidx7, int32_t *status) {
+    const int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= frames) return;
+    const int nbi = (7 * k + 7) / 8;
+    if (to_relidx7) {
+        uint32_t bits = (uint32_t)src[4 * f] | ((uint32_t)src[4 * f + 1] << 8) | ((uint32_t)src[4 * f + 2] << 16) | ((uint32_t)src[4 * f + 3] << 24);
+        if (__popc(bits) != k) or_status(status, OMMX_ST_BAD_GROUP);
+        unsigned long long lo = 0, hi = 0;                       // 7k <= 112 bits
+        int r = 0;
+        while (bits && r < k) {
+            const int pz = __ffs(bits) - 1;
+            bits &= bits - 1;
+            const int bp = 7 * r;
+            if (bp < 64) { lo |= (unsigned long long)pz << bp; if (bp > 57) hi |= (unsigned long long)pz >> (64 - bp); }
+            else hi |= (unsigned long long)pz << (bp - 64);
+            ++r;
+        }
+        for (int i = 0; i < nbi; ++i) dst[f * nbi + i] = (uint8_t)((i < 8 ? lo >> (8 * i) : hi >> (8 * (i - 8))) & 0xFFu);
+    } else {
+        unsigned long long lo = 0, hi = 0;
+        for (int i = 0; i < nbi; ++i) {
+            const unsigned long long b = src[f * nbi + i];
+            if (i < 8) lo |= b << (8 * i); else hi |= b << (8 * (i - 8));
+        }
+        uint32_t bits = 0;
+        for (int r = 0; r < k; ++r) {
+            const int bp = 7 * r;
+            unsigned long long v = bp < 64 ? lo >> bp : hi >> (bp - 64);
+            if (bp < 64 && bp > 57) v |= hi << (64 - bp);
+            const uint32_t pz = (uint32_t)(v & 0x7Fu);
+            if (pz > 31u || (bits >> pz) & 1u) or_status(status, OMMX_ST_BAD_GROUP);
+            else bits |= 1u << pz;
+        }
+        dst[4 * f] = (uint8_t)bits; dst[4 * f + 1] = (uint8_t)(bits >> 8); dst[4 * f + 2] = (uint8_t)(bits >> 16); dst[4 * f + 3] = (uint8_t)(bits >> 24);
+    }
+}
+}  // namespace ommx
+
+extern "C" int ommx_b200_outlier_index_convert(const void *src, void *dst, int64_t frames, int32_t k, int32_t to_relidx7,
+                                               int32_t *status, void *stream) {
+    using namespace ommx;
+    if (!src || !dst) return fail(OMMX_E_ARG, "outlier_index_convert: null plane");
+    if (frames < 0 || k < 1 || k > 16) return fail(OMMX_E_ARG, "outlier_index_convert: frames=%lld k=%d (k must be 1..16)", (long long)frames, k);
+    if (frames == 0) return 0;
+    outlier_index_convert_kernel<<<(unsigned)((frames + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (const uint8_t *)src, (uint8_t *)dst, frames, k, to_relidx7 ? 1 : 0, status);
+    OMMX_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return 0;
+}
+
 extern "C" int ommx_b200_pack_kv(const ommx_pack_args *a, void *stream) {
     using namespace ommx;
     if (!a) return fail(OMMX_E_ARG, "pack: null args");
     const ommx_kv_planes &pl = a->planes;
+    if (pl.outlier_index != OMMX_OIDX_BITMASK)
+        return fail(OMMX_E_UNSUPPORTED, "pack: the store kernels write the flat bitmask (re-encode with ommx_b200_outlier_index_convert)");
     if (!a->k || !a->v) return fail(OMMX_E_ARG, "pack: null k/v");
     if (a->num_tokens < 0 || a->num_tokens % 32 != 0)
         return fail(OMMX_E_ARG, "pack: num_tokens=%d must be a multiple of 32", a->num_tokens);
@@ -812,6 +868,7 @@ extern "C" int ommx_b200_kv_append_decode(const ommx_kv_append_args *a, void *st
     if (!a) return fail(OMMX_E_ARG, "kv_append: null args");
     const ommx_kv_pool &pool = a->pool;
     const ommx_kv_planes &pl = pool.planes;
+    if (pl.outlier_index != OMMX_OIDX_BITMASK) return fail(OMMX_E_UNSUPPORTED, "kv_append: the store kernels write the flat bitmask");
     if (a->batch <= 0) return fail(OMMX_E_ARG, "kv_append: batch=%d", a->batch);
     if (!pool.k_hist || !pool.v_hist || !pool.seq_len || !pool.req_to_token || !pool.req_to_group)
         return fail(OMMX_E_ARG, "kv_append: ring, seq_len and the two tables must not be null");

@@ -217,6 +217,54 @@ def pack_kv(K, V, *, outliers_per_vector=6, outlier_select="signed", use_pow2=Tr
     return out
 
 
+def relidx7_from_bitmask(obmp, k):
+    """Flat bitmask plane [..., 4] -> relidx7 plane [..., ceil(7k/8)]: the k token positions of a frame, ascending,
+    7 bits each, LSB first (ommx_gpu_serve/attention/codec.py:91-113, pack.py:128-165 of the reference)."""
+    obmp = np.ascontiguousarray(obmp, dtype=np.uint8)
+    lead = obmp.shape[:-1]
+    word = obmp.reshape(-1, 4).copy().view(np.uint32)[:, 0]
+    n = word.shape[0]
+    nbi = (7 * k + 7) // 8
+    bits = ((word[:, None] >> np.arange(32, dtype=np.uint32)[None, :]) & 1).astype(bool)
+    if not (bits.sum(1) == k).all():
+        raise ValueError("a frame does not hold exactly k outliers")
+    pos = np.nonzero(bits)[1].reshape(n, k).astype(np.uint64)            # ascending within a frame
+    stream_bits = np.zeros((n, nbi * 8), dtype=np.uint8)
+    for r in range(k):
+        for b in range(7):
+            stream_bits[:, 7 * r + b] = (pos[:, r] >> np.uint64(b)) & np.uint64(1)
+    out = np.packbits(stream_bits.reshape(n, nbi, 8), axis=-1, bitorder="little")[..., 0]
+    return out.reshape(lead + (nbi,))
+
+
+def bitmask_from_relidx7(oidx, k):
+    """Inverse of :func:`relidx7_from_bitmask` (codec.py:116-130): relidx7 plane -> flat bitmask plane [..., 4]."""
+    oidx = np.ascontiguousarray(oidx, dtype=np.uint8)
+    lead = oidx.shape[:-1]
+    nbi = oidx.shape[-1]
+    sb = np.unpackbits(oidx.reshape(-1, nbi), axis=-1, bitorder="little")
+    word = np.zeros(sb.shape[0], dtype=np.uint32)
+    for r in range(k):
+        pos = np.zeros(sb.shape[0], dtype=np.uint32)
+        for b in range(7):
+            pos |= sb[:, 7 * r + b].astype(np.uint32) << np.uint32(b)
+        if (pos > 31).any():
+            raise ValueError("a relidx7 position lies beyond the 32-token group")
+        word |= np.uint32(1) << pos
+    return np.ascontiguousarray(word)[:, None].view(np.uint8).reshape(lead + (4,))
+
+
+def with_bitmask(planes):
+    """Planes whose outlier index is the relidx7 stream (``k_oidx``) re-expressed with the flat bitmask the other
+    oracle functions read; planes that already hold ``k_obmp`` pass through."""
+    if planes.get("k_obmp") is not None or planes.get("k_oidx") is None:
+        return planes
+    out = dict(planes)
+    out["k_obmp"] = bitmask_from_relidx7(planes["k_oidx"], int(planes["k_oval"].shape[-1]) * 2 if "outliers_per_vector" not in planes
+                                         else int(planes["outliers_per_vector"]))
+    return out
+
+
 def _plane_f32(p, scale_bf16):
     return bf16_from_bits(p) if (scale_bf16 and p.dtype == np.uint16) else p.astype(F32)
 

@@ -9,7 +9,8 @@ It imports, unmodified, from the reference checkout:
   * ommx_gpu_serve.attention.pack.ommx_pack_kv_canonical_block / dequant_kv_canonical
   * ommx_gpu_serve.attention.oracle.synth_kv / reference_output
   * ommx_fakequant/quant_function.py::_apply_group_quantization_vectorized   (loaded by path)
-and writes one ``.npz`` per case: the seeded inputs plus every output plane.  The fixtures are
+and writes one ``.npz`` per case: the seeded inputs plus every output plane; for the two benchmark-sized
+blocks it writes the SHA-256 of every reference-made plane to ``plane_sha256.json`` instead.  The fixtures are
 the pin that tests/test_oracle.py holds the CPU oracle to (bit for bit), and that the GPU parity
 tests hold the CUDA kernels to.  The reference is needed only here; the tests read the files.
 bf16 tensors are stored as uint16 bit patterns.
@@ -126,6 +127,19 @@ def main():
         Vb, is_key=False, outlier_percent_topk=0.0, outlier_percent_bottomk=0.0, **kw)[0]
     _save("fakequant_t200", {"K": K.numpy(), "V": V.numpy(), "K_fq": fk.numpy(), "V_fq": fv.numpy()})
 
+    # the other outlier-index encoding the reference's presets name: relidx7 (k = 6 and the k = 10 recipe)
+    for k in (6, 10):
+        K, V = gaussian_kv(20 + k, 64, 2, 128)
+        ref = ommx_pack_kv_canonical_block(K, V, outliers_per_vector=k, outlier_repr="relidx7", outlier_select="signed",
+                                           use_pow2=True, kv_outlier_map=True, page_size=16)
+        out = {"K": K.numpy(), "V": V.numpy(), "cfg": np.array([k, 1, 1, 1, 16]), "k_oidx": _np(ref["k_oidx"])}
+        for p in PLANES:
+            if ref[p] is not None:
+                out[p] = _np(ref[p])
+        Kd, Vd = dequant_kv_canonical(ref)
+        out["K_dq"], out["V_dq"] = Kd.numpy(), Vd.numpy()
+        _save(f"pack_relidx7_k{k}", out)
+
     # attention: the reference's fp32 oracle over (dequantized packed prefix + bf16 residual rows)
     for name, seed, seq, H, Hq in (("attn_seq168", 42, 168, 2, 8), ("attn_seq300_gqa8", 9, 300, 1, 8)):
         D, sink, recent = 128, 8, 32
@@ -144,5 +158,27 @@ def main():
                      "o": o.numpy(), "cfg": np.array([seq, H, Hq, D, sink, recent])})
 
 
+def plane_hashes():
+    """SHA-256 of every plane the reference packer makes for the benchmark-sized blocks (too large to commit as
+    arrays): config 1's 4 032 x 8 x 128 block (seed 42, bf16-valued) and an 8 192-token prefill chunk (seed 43)."""
+    import json
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    out = {}
+    for name, seed, T, skip in (("config1_ctx4096", 42, 4096, 8), ("prefill_chunk_8192", 43, 8192 + 8, 8)):
+        K, V = gaussian_kv(seed, T, 8, 128)
+        n = (T - skip - 32) // 32 * 32 if name.startswith("config1") else 8192
+        ref = ommx_pack_kv_canonical_block(
+            K[skip:skip + n], V[skip:skip + n], outliers_per_vector=6, outlier_repr="bitmap",
+            outlier_select="signed", use_pow2=True, kv_outlier_map=True, page_size=16)
+        out[name] = {"seed": seed, "tokens": n, "first_token": skip,
+                     "sha256": {p: hashlib.sha256(np.ascontiguousarray(_np(ref[p])).tobytes()).hexdigest()
+                                for p in PLANES if ref[p] is not None}}
+        print(name, n, "tokens hashed")
+    with open(os.path.join(HERE, "plane_sha256.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+
+
 if __name__ == "__main__":
     main()
+    if len(sys.argv) <= 2 or "plane_sha256" in sys.argv[2:]:
+        plane_hashes()

@@ -116,3 +116,36 @@ def test_packed_boundary_values():
     # 1K->960, 4K->4032, 64K->65472 packed tokens with sink 8 / recent 32
     for seq, packed in ((1024, 960), (4096, 4032), (16384, 16320), (65536, 65472), (131072, 131008), (71, 0), (72, 32)):
         assert O.packed_boundary(seq) - 8 == packed or (packed == 0 and O.packed_boundary(seq) <= 8)
+
+
+@pytest.mark.parametrize("name", ["config1_ctx4096", "prefill_chunk_8192"])
+def test_oracle_packer_hashes_to_the_reference_at_benchmark_size(name):
+    """Config 1's 4 032 x 8 x 128 block and an 8 192-token chunk: every plane of the oracle's packer hashes
+    (SHA-256) to what the reference packer made for the same seeded input (tests/golden/plane_sha256.json)."""
+    import hashlib
+    import json
+    from helpers import GOLDEN, gaussian_kv
+    rec = json.load(open(os.path.join(GOLDEN, "plane_sha256.json")))[name]
+    T = 4096 if name.startswith("config1") else rec["tokens"] + 8
+    K, V = gaussian_kv(rec["seed"], T, 8, 128)
+    a, b = rec["first_token"], rec["first_token"] + rec["tokens"]
+    pl = O.pack_kv(K[a:b].numpy(), V[a:b].numpy(), outliers_per_vector=6, kv_outlier_map=True, page_size=16)
+    for plane, want in rec["sha256"].items():
+        assert hashlib.sha256(np.ascontiguousarray(pl[plane]).tobytes()).hexdigest() == want, plane
+
+
+@pytest.mark.parametrize("k", [6, 10])
+def test_oracle_relidx7_planes_match_reference_fixture(k):
+    """The reference packer run with outlier_repr='relidx7': same planes as the bitmask encoding except the index
+    plane, which is its 7-bit position stream; the oracle's codec reproduces it and inverts it."""
+    g = load_golden(f"pack_relidx7_k{k}")
+    pl = O.pack_kv(g["K"], g["V"], outliers_per_vector=k, kv_outlier_map=True, page_size=16)
+    for name in PLANES:
+        if name in g and name != "k_obmp":
+            assert (np.asarray(pl[name]).view(g[name].dtype) == g[name]).all(), name
+    idx = O.relidx7_from_bitmask(pl["k_obmp"], k)
+    assert idx.shape == g["k_oidx"].shape and (idx == g["k_oidx"]).all()
+    assert (O.bitmask_from_relidx7(g["k_oidx"], k) == pl["k_obmp"]).all()
+    planes = dict(pl, k_obmp=None, k_oidx=g["k_oidx"], outliers_per_vector=k)
+    Kd, Vd = O.dequant_kv(O.with_bitmask(planes))
+    assert (Kd == g["K_dq"]).all() and (Vd == g["V_dq"]).all()

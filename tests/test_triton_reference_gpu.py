@@ -39,7 +39,7 @@ def _reference():
     return rdec, rpack
 
 
-def _build(rpack, ctx, *, k=6, mag=12.0, seed=42, h=H, hq=HQ, batch=1, permute=True):
+def _build(rpack, ctx, *, k=6, mag=12.0, seed=42, h=H, hq=HQ, batch=1, permute=True, repr_="bitmap"):
     """Pack `batch` sequences with the REFERENCE packer into one pooled, permuted plane set."""
     packed = max(0, (ctx - SINK - RECENT) // 32 * 32)
     edge = SINK + packed
@@ -54,12 +54,12 @@ def _build(rpack, ctx, *, k=6, mag=12.0, seed=42, h=H, hq=HQ, batch=1, permute=T
     k_tail = torch.zeros(batch, tail_len, h, D, dtype=torch.bfloat16)
     v_tail = torch.zeros(batch, tail_len, h, D, dtype=torch.bfloat16)
     page_planes = ("k_base", "v_main", "v_scale", "v_zp")
-    names = page_planes + ("k_scale", "k_zp", "k_obmp", "k_oval", "k_fp4_mapscale", "k_fp4_mapcenter")
+    names = page_planes + ("k_scale", "k_zp", "k_obmp", "k_oidx", "k_oval", "k_fp4_mapscale", "k_fp4_mapcenter")
     for b in range(batch):
         K, V = gaussian_kv(seed + 1000 * b, ctx, h, D, mag=mag)
         pl = rpack.ommx_pack_kv_canonical_block(
             K[SINK:edge], V[SINK:edge], outliers_per_vector=k, group_tokens=32, group_channels=32,
-            page_size=PAGE, k_format="i2f4", outlier_repr="bitmap", use_pow2=True, outlier_select="signed")
+            page_size=PAGE, k_format="i2f4", outlier_repr=repr_, use_pow2=True, outlier_select="signed")
         meta = pl
         mine_p, mine_g = pp[b * n_pages:(b + 1) * n_pages], gp[b * n_groups:(b + 1) * n_groups]
         for n in names:
@@ -86,11 +86,11 @@ def _decode(fn, c, **extra):
     p = c["planes"]
     o = torch.full((c["batch"], c["hq"], D), float("nan"), dtype=torch.float32, device="cuda")
     lse = torch.full((c["batch"], c["hq"]), float("nan"), dtype=torch.float32, device="cuda")
-    fn(c["q"], p["k_base"], p["k_scale"], p["k_zp"], None, p.get("k_oval"),
+    fn(c["q"], p["k_base"], p["k_scale"], p["k_zp"], p.get("k_oidx"), p.get("k_oval"),
        p["v_main"], p["v_scale"], p["v_zp"], c["k_tail"], c["v_tail"], c["b_tail_len"],
        o, lse, c["r2t"], c["r2g"], c["b_seq_len"],
        sm_scale=1.0 / math.sqrt(D), page_size=PAGE, k_outliers_per_vector=c["k"], k_format="i2f4",
-       bitmap_read=c["k"] > 0, k_obmp=p.get("k_obmp"),
+       bitmap_read=c["k"] > 0 and p.get("k_obmp") is not None, k_obmp=p.get("k_obmp"),
        k_fp4_mapscale=p.get("k_fp4_mapscale"), k_fp4_mapcenter=p.get("k_fp4_mapcenter"),
        kv_outlier_map=bool(c["meta"].get("kv_outlier_map", False)) and c["k"] > 0,
        kv_int8_scale=bool(c["meta"].get("kv_int8_scale", False)),
@@ -121,6 +121,13 @@ def test_matches_triton_reference(ctx):
 def test_matches_triton_reference_outlier_magnitudes(k, mag):
     _, rpack = _reference()
     _compare(_build(rpack, 2048, k=k, mag=mag, seed=7 + k), f"ctx 2048 k={k} mag={mag}")
+
+
+@pytest.mark.parametrize("k", [6, 10])
+def test_matches_triton_reference_relidx7(k):
+    """The reference's relidx7 read path (attention/paged_decode.py:640-706), which also serves k > 8."""
+    _, rpack = _reference()
+    _compare(_build(rpack, 2048, k=k, seed=30 + k, repr_="relidx7"), f"ctx 2048 relidx7 k={k}")
 
 
 def test_matches_triton_reference_batch_gqa8():
