@@ -94,18 +94,6 @@ struct __align__(16) CopyDesc {
 };                                       // kind 0 bulk copy, 1 k_base through tmap_k, 2 v_main through tmap_v
 // a stage holds at most 8 groups x (4 planes x 4 pages + 6 group planes) = 176 copies (1 kv head, 8-token pages)
 
-// Development builds (-DOMMX_TRACE) stamp the SM clock at fixed points of one CTA's warps into a
-// device array that ommx_b200_debug_read_trace copies out; service builds compile the probes away.
-#ifdef OMMX_TRACE
-__device__ long long g_trace[32 * 256];
-#define OMMX_TR(slot)                                                                              \
-    do {                                                                                           \
-        if (blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (slot) < 256) g_trace[warp * 256 + (slot)] = clock64(); \
-    } while (0)
-#else
-#define OMMX_TR(slot) do { } while (0)
-#endif
-
 // ---- PTX wrappers --------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -254,7 +242,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int split = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    OMMX_TR(250);
     // the first tensor-map copy otherwise pays for fetching its descriptor
     if (threadIdx.x == S1_THREADS - 32 && p.swz != 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_k)) : "memory");
@@ -363,7 +350,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         }
     }
     __syncthreads();
-    OMMX_TR(251);
     // Stage 2 is launched as a programmatic dependent: it may start its own prologue (residual-row
     // logits, which do not depend on this kernel) as soon as SM resources free up, and waits for this
     // grid to finish before it reads the split partials.
@@ -380,12 +366,10 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         for (int it = 0; it < n_iters; ++it) {
             const int s = ring_slot(it, NS);
             const uint32_t ph = ring_phase(it, NS);
-            OMMX_TR(4 * it);
             if (!mbar_wait(bar_empty + 8 * s, ph ^ 1)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
             }
-            OMMX_TR(4 * it + 1);
             const int lg0 = it * GS;
             uint32_t total = full_total;
             if (lg0 + GS > whole_groups) {                              // last stage: fewer groups or a partial group
@@ -410,7 +394,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     else tma_2d_g2s(sbase + d.dst, kind == 1 ? &p.tmap_k : &p.tmap_v, 0, (int32_t)idx * p.rows_per_page, bar_full + 8 * s);
                 }
             }
-            OMMX_TR(4 * it + 2);
         }
         // fall through to the two CTA-wide barriers of the epilogue
         __syncthreads();
@@ -443,7 +426,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             const int it = n / (2 * NCW), unit = (n >> 1) % NCW, hf = n & 1;
             const int trk = 8 * ((n - dw) / NDW);
             (void)trk;
-            OMMX_TR(trk);
             const int h = unit & (H - 1), gsel = unit >> p.hshift;       // H is a power of two
             uint8_t *tile = s_tiles + unit * DT_BYTES;
             const int s = ring_slot(it, NS);
@@ -467,7 +449,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
             }
-            OMMX_TR(trk + 1);
             const int lg = it * GS + gsel;                           // local group of this unit
             if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
                 // Tile `it` of a unit may be written once the MMA warp has read tile it-1.  Decode warps
@@ -481,7 +462,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                     break;
                 }
-                OMMX_TR(trk + 2);
                 bool clamped_any = false;
                 const bool splice = k_out > 0 && !no_outlier;
                 // ---- first the rows the code MMAs and the softmax read (K factors, q.zp sums, V factors and
@@ -553,7 +533,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_trows + 8 * unit);
-                OMMX_TR(trk + 3);
                 // ---- then the outlier deltas of this half's columns ----
                 if (splice) {
                     // clear this half's columns of token rows 0..31 (128 bytes per row)
@@ -689,7 +668,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 }
                 if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
                 __syncwarp();
-                OMMX_TR(trk + 4);
                 if (lane == 0) mbar_arrive(bar_tfull + 8 * unit);
             }
             __syncwarp();
@@ -769,11 +747,9 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     const bool do_k = !(p.abl & ABL_NO_K), do_v = !(p.abl & ABL_NO_V);
     const bool has_delta = !(k_out == 0 || no_outlier);
 
-    OMMX_TR(252);
     for (int it = 0; it < n_iters; ++it) {
         const int s = ring_slot(it, NS);
         const uint32_t ph = ring_phase(it, NS);
-        OMMX_TR(8 * it);
         const int lg = it * GS + gsel;                               // local group of this warp
         const bool active = lg < ngroups && !(p.abl & ABL_NO_COMPUTE);
         if (!mbar_wait(bar_full + 8 * s, ph)) {
@@ -781,7 +757,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
             break;
         }
-        OMMX_TR(8 * it + 1);
         if (active) {
             uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
             const uint8_t *vreg = gb + p.o_vm;                      // v_main region of the group (1 KB aligned)
@@ -794,7 +769,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 kw[nt] = make_uint2(0u, 0u);
                 if (do_k) kw[nt] = *reinterpret_cast<const uint2 *>(gb + swz128((uint32_t)((8 * nt + g) * TS + h * 32 + 8 * j), p.swz));
             }
-            OMMX_TR(8 * it + 2);
             // The unit's sidecar tile arrives in two steps: first the factor and zero-point rows, then the outlier
             // deltas.  The code MMAs run on the first, while the decode warps still scatter the deltas.
             if (!mbar_wait(bar_trows + 8 * unit, consumed & 1u)) {
@@ -802,7 +776,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
                 break;
             }
-            OMMX_TR(8 * it + 3);
             float Sc[2][4], Sd[2][4], Sz[2];
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) { Sc[mt][0] = Sc[mt][1] = Sc[mt][2] = Sc[mt][3] = 0.f; Sd[mt][0] = Sd[mt][1] = Sd[mt][2] = Sd[mt][3] = 0.f; }
@@ -835,7 +808,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
                     break;
                 }
-                OMMX_TR(8 * it + 7);
                 uint32_t d0f[4], d1f[4];                         // delta fragments of m-tile 0 / 1
                 ldsm_x4(a_delta, d0f[0], d0f[1], d0f[2], d0f[3]);
 #pragma unroll
@@ -849,7 +821,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot((int)consumed, NS)));   // the next tile may be built
             ++consumed;
-            OMMX_TR(8 * it + 4);
 
             // ======================= online softmax =======================
             // x[mt][r]: token 16mt + g + 8(r>>1), head 2j + (r&1)
@@ -905,7 +876,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 T[mt][0] = movmatrix_trans(pack_f16x2(pr[mt][0], pr[mt][1]));
                 T[mt][1] = movmatrix_trans(pack_f16x2(pr[mt][2], pr[mt][3]));
             }
-            OMMX_TR(8 * it + 5);
 
             // ======================= P.V =======================
             if (do_v) {
@@ -959,9 +929,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         // release the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-        OMMX_TR(8 * it + 6);
     }
-    OMMX_TR(253);
 
     // ---- epilogue: this lane holds 16 channels of heads 2j and 2j+1; merge warps that share a head ----
     float l_tot[2];
@@ -1027,7 +995,6 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             }
         }
     }
-    OMMX_TR(254);
 }
 
 // =================================================================================================
@@ -1620,16 +1587,3 @@ extern "C" int ommx_b200_merge_states(const float *o_parts, const float *lse_par
     count_launch();
     return 0;
 }
-
-#ifdef OMMX_TC_TRACE
-extern "C" int ommx_b200_debug_read_tc_trace(long long *host_out) {
-    return cudaMemcpyFromSymbol(host_out, ommx::g_tc_trace, sizeof(long long) * 8 * 512) == cudaSuccess ? 0 : OMMX_E_CUDA;
-}
-#endif
-
-#ifdef OMMX_TRACE
-// Development builds only: copy the probe array (32 warps x 256 slots of SM clock values) to the host.
-extern "C" int ommx_b200_debug_read_trace(long long *host_out) {
-    return cudaMemcpyFromSymbol(host_out, ommx::g_trace, sizeof(long long) * 32 * 256) == cudaSuccess ? 0 : OMMX_E_CUDA;
-}
-#endif

@@ -63,18 +63,6 @@ constexpr int TB_FULL = 0, TB_EMPTY = TC_MAX_STAGES, TB_KREADY = 2 * TC_MAX_STAG
 constexpr int TM_TMEM = 0, TM_ABORT = 1, TM_NEED = 2 /* [2][4] */, TM_CORR = 10 /* [2][4][8] */, TM_FM = 74 /* [8][8] */,
               TM_FL = 138 /* [8][8] */, TM_FB = 202 /* [8][32] */, TM_WORDS = 458;
 
-// Development builds (-DOMMX_TC_TRACE) stamp the SM clock at fixed points of one CTA into a device array;
-// service builds compile the probes away.
-#ifdef OMMX_TC_TRACE
-__device__ long long g_tc_trace[8 * 512];
-#define TCTR(role, slot)                                                                                        \
-    do {                                                                                                        \
-        if (blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (role) < 8 && (slot) >= 0 && (slot) < 512) g_tc_trace[(role) * 512 + (slot)] = clock64(); \
-    } while (0)
-#else
-#define TCTR(role, slot) do { } while (0)
-#endif
-
 struct TcParams {
     S1Params s;
     int32_t nb;                      // output accumulator blocks in tensor memory: max(H, 4)
@@ -371,12 +359,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             s_q16[row * 128 + tc_pos_of(ch)] = q16;
         }
     }
-    if (warp == 0) TCTR(6, 0);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 0) TCTR(6, 1);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // Register budget per role (setmaxnreg, warpgroup granularity; the CTA was launched with 768 x 80): the softmax
     // warpgroup (warps 4..7) carries the per-block sums, everyone else needs little.  128 x 120 + 640 x 72 = 768 x 80.
@@ -395,7 +381,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
                 break;
             }
-            TCTR(0, g);
             uint32_t mine = 0;
             for (int c = lane; c < cpg; c += 32) {
                 const CopyDesc d = s_desc[c];
@@ -428,7 +413,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 bool ok = mbar_wait(TBAR(TB_KREADY + x), (uint32_t)(i >> 1) & 1u);
                 if (ok && i >= 2) ok = mbar_wait(TBAR(TB_DQFREE + x), (uint32_t)((i >> 1) - 1) & 1u);
                 if (!ok) { dead = true; break; }
-                TCTR(1, 4 * i);
                 tc_fence_after();
                 if (lane == 0) {
                     const int ksteps = k_out > 0 ? TC_KCHUNKS / 2 : 8;      // the residual positions exist only with outliers
@@ -441,15 +425,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                     umma_commit(TBAR(TB_KFREE + (i & 3)));
                 }
                 __syncwarp();
-                TCTR(1, 4 * i + 1);
             }
             if (step >= 1) {
                 const int i = step - 1, x = i & 1, vb = i % P.nvb;
                 bool ok = mbar_wait(TBAR(TB_PREADY + (i & 3)), (uint32_t)(i >> 2) & 1u);
-                TCTR(1, 4 * i + 2);
                 if (ok) ok = mbar_wait(TBAR(TB_VREADY + vb), (uint32_t)(i / P.nvb) & 1u);
                 if (!ok) { dead = true; break; }
-                TCTR(1, 4 * i + 3);
                 tc_fence_after();
                 if (lane == 0) {
                     for (int ub = 0; ub < 4; ++ub) {
@@ -495,9 +476,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             uint32_t raw[GQAP];
 #pragma unroll
             for (int j = 0; j < GQAP; ++j) raw[j] = 0u;
-            if (w == 0) TCTR(2, 4 * i);
             if (mbar_wait(TBAR(TB_DQFULL + x), (uint32_t)(i >> 1) & 1u)) {
-                if (w == 0) TCTR(2, 4 * i + 1);
                 tc_fence_after();
                 tmem_ld<GQAP>(tm_dqk + lane_base + x * N_QK + w * GQAP, raw);
                 tc_fence_before();
@@ -544,7 +523,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 }
             }
             asm volatile("bar.sync 2, 128;" ::: "memory");
-            if (w == 0) TCTR(2, 4 * i + 2);
             if (s_misc[TM_ABORT] != 0) { dead = true; return; }
             uint32_t anyneed = 0;
 #pragma unroll
@@ -615,7 +593,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(TBAR(TB_PREADY + (i & 3)));
-            if (w == 0) TCTR(2, 4 * i + 3);
         };
 
         for (int i = 0; i < n_items && !dead; ++i) {
@@ -697,10 +674,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
         bool dead = false;
         for (int task = dw; task < n_items * 16 && !dead; task += TC_NDW) {
             const int i = task >> 4, ub = (task >> 2) & 3, qt = task & 3, x = i & 1;
-            const int trn = 6 * ((task - dw) / TC_NDW), trr = dw == 0 ? 3 : (dw == 5 ? 4 : (dw == 17 ? 5 : 8)), tr8 = dw == 1 ? 8 * ((task - dw) / TC_NDW) : -1000;
-            (void)tr8;
-            (void)trn; (void)trr;
-            TCTR(trr, trn);
             const int u = 4 * i + ub;
             const bool valid = u < n_units;
             const int g = valid ? u / H : 0, h = valid ? u - g * H : 0;
@@ -711,8 +684,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
             if (i >= 2 && !mbar_wait(TBAR(TB_KFREE + ((i - 2) & 3)), (uint32_t)((i - 2) >> 2) & 1u)) { dead = true; break; }
             if (i >= 2 && !mbar_wait(TBAR(TB_PREADY + ((i - 2) & 3)), (uint32_t)((i - 2) >> 2) & 1u)) { dead = true; break; }
             if (valid && !mbar_wait(TBAR(TB_FULL + s), (uint32_t)(g / NS) & 1u)) { dead = true; break; }
-            TCTR(trr, trn + 1);
-            TCTR(7, tr8);
             const uint8_t *gb = s_stage + (size_t)s * p.stage_bytes;
             uint8_t *ktile = s_ktile + x * TC_KTILE;
             uint8_t *side = s_side + x * TC_SIDE_BYTES;
@@ -728,7 +699,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                     *reinterpret_cast<uint4 *>(row + 4096) = make_uint4((kw.y << 8) & M, (kw.y << 6) & M, (kw.y << 4) & M, (kw.y << 2) & M);
                     *reinterpret_cast<uint4 *>(row + 6144) = make_uint4(kw.y & M, (kw.y >> 2) & M, (kw.y >> 4) & M, (kw.y >> 6) & M);
                 }
-                TCTR(7, tr8 + 1);
                 // ---- B tile rows of this unit (query x 2^(e_k + FBQ)) and the fp32 q.zp sums of positions 32qt .. 32qt+31:
                 //      lane = (8-position chunk c of 4, head j of 8) ----
                 {
@@ -765,7 +735,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
                     if (c == 0 && j < GQAP) reinterpret_cast<float *>(side + TC_SIDE_QZ)[ub * 32 + qt * 8 + j] = sum;
                 }
-                TCTR(7, tr8 + 2);
                 // ---- V factors of tokens 8qt .. 8qt+7: lane = (token, scale group) ----
                 {
                     const int tk = 8 * qt + (lane & 7), cg = lane >> 3;
@@ -779,10 +748,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                     *reinterpret_cast<uint16_t *>(side + TC_SIDE_VF + (ub * 32 + tk) * 8 + 2 * cg) = (uint16_t)fbits;
                     *reinterpret_cast<uint16_t *>(side + TC_SIDE_VZ + (ub * 32 + tk) * 8 + 2 * cg) = (uint16_t)zbits;
                 }
-                TCTR(7, tr8 + 3);
                 // ---- outliers of channel 32qt + lane, written over their slots of the K tile (after the codes) ----
                 __syncwarp();
-                TCTR(7, tr8 + 4);
                 if (k_out > 0) {
                     switch (k_out) {
                         case 2: tc_splice<2>(p, gb, ktile, s_bq + x * BQ_BYTES, s_q16, s_lut, h, ub, qt, lane, GQAP, N_QK, clamped_any); break;
@@ -794,12 +761,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 }
             }
             if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
-            TCTR(trr, trn + 2);
-            TCTR(7, tr8 + 5);
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(TBAR(TB_KREADY + x));
-            TCTR(trr, trn + 3);
 
             // ---- V codes of this quarter into the V tile (channel-major), once the tile's previous user is done ----
             const int vb = i % P.nvb;
@@ -807,7 +771,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 const int jdone = i - P.nvb;
                 if (!mbar_wait(TBAR(TB_PVDONE + (jdone & 3)), (uint32_t)(jdone >> 2) & 1u)) { dead = true; break; }
             }
-            TCTR(trr, trn + 4);
             if (valid) {
                 uint2 vw = make_uint2(0u, 0u);
                 if (32 * g + lane < ntok) vw = *reinterpret_cast<const uint2 *>(gb + p.o_vm + swz128((uint32_t)(lane * TS + h * 32 + 8 * qt), p.swz));
@@ -823,14 +786,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
                 mbar_arrive(TBAR(TB_VREADY + vb));
                 if (valid) mbar_arrive(TBAR(TB_EMPTY + s));
             }
-            TCTR(trr, trn + 5);
         }
         if (dead && lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
     }
-    if (warp == TC_W_SOFTMAX) TCTR(6, 2);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) TCTR(6, 3);
     if (warp == TC_W_MMA) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P.tmem_cols));
 #undef TBAR
 }

@@ -8,7 +8,8 @@ import pytest
 from oracle import ommx_oracle as O
 from helpers import GOLDEN, PLANES, load_golden
 
-PACK_CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, "pack_*.npz")))
+PACK_CASES = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, "pack_*.npz"))
+                    if "relidx7" not in os.path.basename(p))        # those have tests of their own
 
 
 def _pack_from_golden(g):
