@@ -235,14 +235,28 @@ def ommx_paged_decode_attention_canonical(
         num_kv_splits = _auto_num_kv_splits(max(max_seq, 1), batch, device=q.device, kv_heads=n_kv_heads)
     num_kv_splits = max(1, int(num_kv_splits))
     if static_workspace:
+        if int(_stage) != 0:
+            raise ValueError("static_workspace=True runs both stages on the library's own workspace; _stage must be 0")
         attn_logits = None
     else:
         if attn_logits is None:
             attn_logits = _make_attn_logits(batch, head_num, num_kv_splits + 1, D, q.device)
+        if attn_logits.dtype != torch.float32 or attn_logits.device != q.device or attn_logits.dim() != 4:
+            raise ValueError("attn_logits must be a float32 [batch, heads, splits, head_dim+1] tensor on q's device")
+        if int(attn_logits.shape[0]) < batch or int(attn_logits.shape[1]) < head_num:
+            raise ValueError(f"attn_logits {tuple(attn_logits.shape)} is smaller than batch={batch} x heads={head_num}")
         if int(attn_logits.shape[-1]) != D + 1 or attn_logits.stride(-1) != 1:
             raise ValueError(f"attn_logits last dim must be head_dim+1={D + 1} and contiguous")
         if int(attn_logits.shape[2]) < num_kv_splits:
             raise ValueError(f"attn_logits holds {attn_logits.shape[2]} split slots, fewer than num_kv_splits={num_kv_splits}")
+    if o.dim() != 3 or int(o.shape[0]) < batch or int(o.shape[1]) < head_num or int(o.shape[2]) != D:
+        raise ValueError(f"o must be [batch>={batch}, heads>={head_num}, {D}]; got {tuple(o.shape)}")
+    if lse.dim() != 2 or int(lse.shape[0]) < batch or int(lse.shape[1]) < head_num or lse.stride(1) != 1:
+        raise ValueError(f"lse must be [batch>={batch}, heads>={head_num}] with a unit last stride; got {tuple(lse.shape)}")
+    for name, t in (("o", o), ("lse", lse), ("b_seq_len", b_seq_len), ("req_to_token", req_to_token), ("req_to_group", req_to_group),
+                    ("k_tail", k_tail), ("v_tail", v_tail), ("b_tail_len", b_tail_len)):
+        if t is not None and t.device != q.device:
+            raise ValueError(f"{name} is on {t.device}, q on {q.device}")
     if q.dtype != torch.bfloat16:
         raise NotImplementedError(f"q dtype {q.dtype}: this build serves bfloat16 queries")
     if q.stride(-1) != 1 or o.stride(-1) != 1:

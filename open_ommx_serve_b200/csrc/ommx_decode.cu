@@ -248,6 +248,10 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_v)) : "memory");
     }
 
+    // The launch lets this grid start while the kernel before it in the stream is still running (its blocks are
+    // placed, shared memory is carved): nothing that kernel may have written - lengths, tables, the query, the
+    // planes, the split workspace a previous layer's combine still reads - is touched before this returns.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // ---- split range (same rounding as the reference, paged_decode.py:1428-1432) ----
     const int seq = p.b_seq_len[b];
     if (seq <= 0) return;
@@ -1033,6 +1037,9 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
     __shared__ float s_w[S2_MAX_SPLITS];
     __shared__ float s_red[S2_WARPS];
     __shared__ float s_acc[S2_WARPS][HD];
+    // the next kernel in the stream (the following layer's stage 1) may be placed as SMs free up; it waits for
+    // this grid to finish before it touches memory
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int hq = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = hq / p.gqa;
@@ -1313,6 +1320,23 @@ static size_t stage1_smem(const S1Params &p) {
            + (size_t)p.GS * (4 * p.ppg + 6) * sizeof(CopyDesc);       // the copy roles of one stage come last
 }
 
+// Launch as a programmatic dependent of whatever precedes it in the stream: the grid may be placed while that
+// kernel drains, and the kernel itself waits (griddepcontrol.wait) before it reads or writes global memory.
+template <typename Kernel, typename Params>
+static cudaError_t launch_overlapping_previous(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t st, const Params &p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 constexpr int MAX_DEVICES = 64;
 static int current_device(int *dev) {
     OMMX_CUDA_TRY(cudaGetDevice(dev));
@@ -1340,8 +1364,7 @@ static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st)
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_smem[dev].store(smem, std::memory_order_release);
     }
-    decode_stage1_kernel<KOUT><<<grid, S1_THREADS, smem, st>>>(p);
-    OMMX_CUDA_TRY(cudaGetLastError());
+    OMMX_CUDA_TRY(launch_overlapping_previous(decode_stage1_kernel<KOUT>, grid, S1_THREADS, smem, st, p));
     count_launch();
     return 0;
 }
@@ -1451,6 +1474,17 @@ static int launch_stage2(const ommx_decode_args *a, cudaStream_t st, bool after_
     p.o = a->o; p.o_bf16 = (a->o_dtype == OMMX_DT_BF16); p.o_sb = a->o_stride_b; p.o_sh = a->o_stride_h;
     p.lse = a->lse; p.lse_sb = a->lse_stride_b;
     p.sm_scale = a->sm_scale; p.logit_cap = a->logit_cap;
+    {
+        // Stage 1 runs with the largest shared-memory carve-out; asking for the same split here spares the SMs a
+        // reconfiguration between the two kernels of every layer.
+        static std::atomic<int> carve_set[MAX_DEVICES];
+        int dev = 0;
+        if (int rc = current_device(&dev)) return rc;
+        if (carve_set[dev].load(std::memory_order_acquire) == 0) {
+            OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage2_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+            carve_set[dev].store(1, std::memory_order_release);
+        }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a->n_q_heads, a->batch);
     cfg.blockDim = dim3(S2_THREADS);

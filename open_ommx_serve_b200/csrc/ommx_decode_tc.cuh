@@ -118,6 +118,19 @@ __device__ __forceinline__ float redux_max_f32(float x) {
     asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(y) : "f"(x));
     return y;
 }
+// probe without blocking / block for at most `ns` nanoseconds (the plain try_wait may block for an unspecified time)
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_ns(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint32_t dup16(uint32_t h) { return h | (h << 16); }
 // fp16 bits of 2^(e + bias): 0 below the subnormal range of interest (e + bias < -14), clamped at 2^15
 __device__ __forceinline__ uint32_t tc_pow2_f16(int e, int bias, bool &clamped, int limit = 30) {
@@ -238,6 +251,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
     const int split = blockIdx.x, b = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // placed while the previous kernel of the stream drains; no global memory is touched before this returns
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // ---- split range (same rounding as the reference, paged_decode.py:1428-1432) ----
     const int seq = p.b_seq_len[b];
     if (seq <= 0) return;
@@ -406,48 +421,63 @@ __global__ void __launch_bounds__(TC_THREADS, 1) decode_stage1_tc_kernel(const _
         constexpr uint32_t ID_PV = umma_idesc_f16(128, N_PV, 1, 1);
         const uint32_t a_k = smem_u32(s_ktile), a_v = smem_u32(s_vtile), a_bq = smem_u32(s_bq), a_pt = smem_u32(s_pt);
         bool dead = false;
-        // PV of item i is issued after the logits of item i + 1, so that the softmax of i overlaps them
-        for (int step = 0; step <= n_items && !dead; ++step) {
-            if (step < n_items) {
-                const int i = step, x = i & 1;
-                bool ok = mbar_wait(TBAR(TB_KREADY + x), (uint32_t)(i >> 1) & 1u);
-                if (ok && i >= 2) ok = mbar_wait(TBAR(TB_DQFREE + x), (uint32_t)((i >> 1) - 1) & 1u);
-                if (!ok) { dead = true; break; }
-                tc_fence_after();
-                if (lane == 0) {
-                    const int ksteps = k_out > 0 ? TC_KCHUNKS / 2 : 8;      // the residual positions exist only with outliers
+        // Event driven: whichever of "logits of item qk" and "output of item pv" has its operands ready is issued
+        // next, the output first (it frees the V tile and the P' tiles).  Probes do not block; the loop gives up
+        // when nothing became ready for about a second of SM clock.
+        int qk = 0, pv = 0;
+        long long t_last = clock64();
+        uint32_t idle = 0;
+        while (pv < n_items) {
+            bool did = false;
+            if (pv < qk) {
+                const int i = pv, x = i & 1, vb = i % P.nvb;
+                if (mbar_test(TBAR(TB_PREADY + (i & 3)), (uint32_t)(i >> 2) & 1u) &&
+                    mbar_test(TBAR(TB_VREADY + vb), (uint32_t)(i / P.nvb) & 1u)) {
+                    tc_fence_after();
+                    if (lane == 0) {
+                        for (int ub = 0; ub < 4; ++ub) {
+                            if (4 * i + ub >= n_units) break;
+                            const int blk = ub + (NB8 ? 4 * (i & 1) : 0);
+                            const bool first = i < (NB8 ? 2 : 1);
+                            const uint32_t d = tm_dpv + blk * N_PV;
+                            const uint32_t av = a_v + vb * TC_VTILE + ub * TC_UNIT_TILE;
+                            const uint32_t bp = a_pt + (x * 4 + ub) * PT_BYTES;
 #pragma unroll
-                    for (int ks = 0; ks < TC_KCHUNKS / 2; ++ks)
-                        if (ks < ksteps)
-                        umma_f16(tm_dqk + x * N_QK, umma_desc(a_k + x * TC_KTILE + ks * 4096, 2048, 128),
-                                 umma_desc(a_bq + x * BQ_BYTES + ks * 2 * (16 * N_QK), 16 * N_QK, 128), ID_QK, ks > 0 ? 1u : 0u);
-                    umma_commit(TBAR(TB_DQFULL + x));
-                    umma_commit(TBAR(TB_KFREE + (i & 3)));
-                }
-                __syncwarp();
-            }
-            if (step >= 1) {
-                const int i = step - 1, x = i & 1, vb = i % P.nvb;
-                bool ok = mbar_wait(TBAR(TB_PREADY + (i & 3)), (uint32_t)(i >> 2) & 1u);
-                if (ok) ok = mbar_wait(TBAR(TB_VREADY + vb), (uint32_t)(i / P.nvb) & 1u);
-                if (!ok) { dead = true; break; }
-                tc_fence_after();
-                if (lane == 0) {
-                    for (int ub = 0; ub < 4; ++ub) {
-                        if (4 * i + ub >= n_units) break;
-                        const int blk = ub + (NB8 ? 4 * (i & 1) : 0);
-                        const bool first = i < (NB8 ? 2 : 1);
-                        const uint32_t d = tm_dpv + blk * N_PV;
-                        const uint32_t av = a_v + vb * TC_VTILE + ub * TC_UNIT_TILE;
-                        const uint32_t bp = a_pt + (x * 4 + ub) * PT_BYTES;
-#pragma unroll
-                        for (int ks = 0; ks < 2; ++ks)
-                            umma_f16(d, umma_desc(av + ks * 256, 128, 512), umma_desc(bp + ks * 256, 128, 512), ID_PV, (first && ks == 0) ? 0u : 1u);
+                            for (int ks = 0; ks < 2; ++ks)
+                                umma_f16(d, umma_desc(av + ks * 256, 128, 512), umma_desc(bp + ks * 256, 128, 512), ID_PV, (first && ks == 0) ? 0u : 1u);
+                        }
+                        umma_commit(TBAR(TB_PVDONE + (i & 3)));
                     }
-                    umma_commit(TBAR(TB_PVDONE + (i & 3)));
+                    __syncwarp();
+                    ++pv;
+                    did = true;
                 }
-                __syncwarp();
             }
+            if (!did && qk < n_items) {
+                const int i = qk, x = i & 1;
+                if (mbar_test(TBAR(TB_KREADY + x), (uint32_t)(i >> 1) & 1u) &&
+                    (i < 2 || mbar_test(TBAR(TB_DQFREE + x), (uint32_t)((i >> 1) - 1) & 1u))) {
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const int ksteps = k_out > 0 ? TC_KCHUNKS / 2 : 8;      // the residual positions exist only with outliers
+#pragma unroll
+                        for (int ks = 0; ks < TC_KCHUNKS / 2; ++ks)
+                            if (ks < ksteps)
+                                umma_f16(tm_dqk + x * N_QK, umma_desc(a_k + x * TC_KTILE + ks * 4096, 2048, 128),
+                                         umma_desc(a_bq + x * BQ_BYTES + ks * 2 * (16 * N_QK), 16 * N_QK, 128), ID_QK, ks > 0 ? 1u : 0u);
+                        umma_commit(TBAR(TB_DQFULL + x));
+                        umma_commit(TBAR(TB_KFREE + (i & 3)));
+                    }
+                    __syncwarp();
+                    ++qk;
+                    did = true;
+                }
+            }
+            if (did) { idle = 0; t_last = clock64(); continue; }
+            // nothing to issue: park on the event most likely to come next, for a fraction of a microsecond at most
+            if (pv < qk) mbar_try_wait_ns(TBAR(TB_PREADY + (pv & 3)), (uint32_t)(pv >> 2) & 1u, 128u);
+            else mbar_try_wait_ns(TBAR(TB_KREADY + (qk & 1)), (uint32_t)(qk >> 1) & 1u, 128u);
+            if ((++idle & 63u) == 0 && (clock64() - t_last > WAIT_LIMIT_CYCLES || s_misc[TM_ABORT] != 0)) { dead = true; break; }
         }
         if (dead && lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); s_misc[TM_ABORT] = 1; }
     } else if (warp >= TC_W_SOFTMAX && warp < TC_W_SOFTMAX + 4) {
@@ -859,8 +889,7 @@ static int launch_tc(const TcParams &P, dim3 grid, size_t smem, cudaStream_t st)
         regs_state[dev].store(regs_ok, std::memory_order_release);
     }
     if (regs_ok != 1) return fail(OMMX_E_CUDA, "the tensor-core stage 1 was compiled with fewer registers than its warp roles need");
-    decode_stage1_tc_kernel<GQAP, NB8><<<grid, TC_THREADS, smem, st>>>(P);
-    OMMX_CUDA_TRY(cudaGetLastError());
+    OMMX_CUDA_TRY(launch_overlapping_previous(decode_stage1_tc_kernel<GQAP, NB8>, grid, TC_THREADS, smem, st, P));
     count_launch();
     return 0;
 }

@@ -302,47 +302,92 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_lane_kernel(PackKParam
     const bool store_f32 = (p.scale_kind == OMMX_SCALE_F32);
 
     bool bad = false;
-    uint32_t cand[32];                        // order keys; 0 marks a picked token (no finite value has key 0)
-#pragma unroll
-    for (int t = 0; t < 32; ++t) {
-        bad |= !isfinite(x[t]);
-        cand[t] = f32_key(x[t]);
-    }
-    // ---- outlier selection: r-th pick = extreme key over unpicked tokens, ties -> lowest token ----
     uint32_t omask = 0;
     uint32_t pick_key[K > 0 ? K : 1];
     int pick_tok[K > 0 ? K : 1];
+    uint32_t kmax = 0u, kmin = 0u;
+    bool rounds = true;                       // take the selection rounds below
+    if constexpr (sizeof(T) == 2) {
+        // One pass.  A value that came from 16 bits leaves the low 13 bits of its order key the same for every
+        // token of a sign, so the token number can ride there: (key | 31 - t) orders tokens for the picks from the
+        // top, (key | t) for the picks from the bottom, both with ties going to the lowest token, and all 32
+        // composites differ.  Sorted insertion keeps the KT + 1 largest and the KB + 1 smallest; the entries
+        // behind the picks are the extremes of what was not picked.  When a token is picked from both ends (a
+        // group with fewer than K + 1 distinct values) the rule "bottom picks skip the top picks" matters, and the
+        // warp takes the rounds.
+        uint32_t top[KT + 1], bot[KB + 1];
 #pragma unroll
-    for (int r = 0; r < K; ++r) {
-        uint32_t m;
-        if (r < KT) {
-            m = cand[0];
+        for (int i = 0; i <= KT; ++i) top[i] = 0u;
 #pragma unroll
-            for (int t = 1; t < 32; ++t) m = max(m, cand[t]);
-        } else {
-            // a picked token (0) must lose the min scan: compare key - 1, which wraps 0 to the top
-            m = cand[0] - 1u;
-#pragma unroll
-            for (int t = 1; t < 32; ++t) m = min(m, cand[t] - 1u);
-            m += 1u;
-        }
-        bool found = false;
-        int tok = 0;
+        for (int i = 0; i <= KB; ++i) bot[i] = 0xFFFFFFFFu;
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
-            const bool hit = !found && cand[t] == m;
-            if (hit) { tok = t; cand[t] = 0u; }
-            found |= hit;
-        }
-        pick_key[r] = m;
-        pick_tok[r] = tok;
-        omask |= 1u << tok;
-    }
-    // ---- base affine over the tokens that were not picked ----
-    uint32_t kmax = cand[0], kmin = cand[0] - 1u;
+            // order key of x + 0 (the sign bit set for x >= 0, all bits flipped below), low five bits cleared
+            const uint32_t u = __float_as_uint(x[t] + 0.0f);
+            const uint32_t key = (u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u)) & ~31u;
+            uint32_t c = key | (uint32_t)(31 - t);
 #pragma unroll
-    for (int t = 1; t < 32; ++t) { kmax = max(kmax, cand[t]); kmin = min(kmin, cand[t] - 1u); }
-    kmin += 1u;
+            for (int i = 0; i <= KT; ++i) { const uint32_t hi = max(top[i], c); c = min(top[i], c); top[i] = hi; }
+            c = key | (uint32_t)t;
+#pragma unroll
+            for (int i = 0; i <= KB; ++i) { const uint32_t lo = min(bot[i], c); c = max(bot[i], c); bot[i] = lo; }
+        }
+        // the key's own low bits: ones below zero, zeros from zero up
+        auto full_key = [](uint32_t comp) { return (comp & ~31u) | ((comp & 0x80000000u) ? 0u : 31u); };
+#pragma unroll
+        for (int r = 0; r < K; ++r) {
+            const uint32_t comp = r < KT ? top[r < KT ? r : 0] : bot[r < KT ? 0 : r - KT];
+            pick_tok[r] = r < KT ? 31 - (int)(comp & 31u) : (int)(comp & 31u);
+            pick_key[r] = full_key(comp);
+            omask |= 1u << pick_tok[r];
+        }
+        kmax = full_key(top[KT]);
+        kmin = full_key(bot[KB]);
+        // an infinity or a NaN is the largest (smallest) key of its sign: the two ends of the order tell
+        bad = top[0] >= 0xFF800000u || bot[0] < 0x00800000u;
+        rounds = __any_sync(0xFFFFFFFFu, __popc(omask) != K || bad);
+    }
+    if (rounds) {
+        uint32_t cand[32];                    // order keys; 0 marks a picked token (no finite value has key 0)
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            bad |= !isfinite(x[t]);
+            cand[t] = f32_key(x[t]);
+        }
+        // ---- outlier selection: r-th pick = extreme key over unpicked tokens, ties -> lowest token ----
+        omask = 0;
+#pragma unroll
+        for (int r = 0; r < K; ++r) {
+            uint32_t m;
+            if (r < KT) {
+                m = cand[0];
+#pragma unroll
+                for (int t = 1; t < 32; ++t) m = max(m, cand[t]);
+            } else {
+                // a picked token (0) must lose the min scan: compare key - 1, which wraps 0 to the top
+                m = cand[0] - 1u;
+#pragma unroll
+                for (int t = 1; t < 32; ++t) m = min(m, cand[t] - 1u);
+                m += 1u;
+            }
+            bool found = false;
+            int tok = 0;
+#pragma unroll
+            for (int t = 0; t < 32; ++t) {
+                const bool hit = !found && cand[t] == m;
+                if (hit) { tok = t; cand[t] = 0u; }
+                found |= hit;
+            }
+            pick_key[r] = m;
+            pick_tok[r] = tok;
+            omask |= 1u << tok;
+        }
+        // ---- base affine over the tokens that were not picked ----
+        kmax = cand[0]; kmin = cand[0] - 1u;
+#pragma unroll
+        for (int t = 1; t < 32; ++t) { kmax = max(kmax, cand[t]); kmin = min(kmin, cand[t] - 1u); }
+        kmin += 1u;
+    }
     const float mn = key_f32(kmin), mx = key_f32(kmax);
     int e;
     const float scale = snap_scale(__fsub_rn(mx, mn), p.use_pow2, p.scale_kind, e);
@@ -351,12 +396,21 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_lane_kernel(PackKParam
     const bool by_mul = p.use_pow2 && e >= -126 && e <= 126;
     const float inv = __uint_as_float((uint32_t)(by_mul ? 127 - e : 127) << 23);
     uint32_t cw0 = 0, cw1 = 0;                // this channel's codes, token t at bits 2t
+    if (__all_sync(0xFFFFFFFFu, by_mul)) {    // the usual case, without a division in sight
 #pragma unroll
-    for (int t = 0; t < 32; ++t) {
-        const float d = __fsub_rn(x[t], zp);
-        const uint32_t c = code_0_3(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
-        if (t < 16) cw0 = c * (1u << (2 * t)) + cw0;
-        else cw1 = c * (1u << (2 * (t - 16))) + cw1;
+        for (int t = 0; t < 32; ++t) {
+            const uint32_t c = code_0_3(__fmul_rn(__fsub_rn(x[t], zp), inv));
+            if (t < 16) cw0 = c * (1u << (2 * t)) + cw0;
+            else cw1 = c * (1u << (2 * (t - 16))) + cw1;
+        }
+    } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            const float d = __fsub_rn(x[t], zp);
+            const uint32_t c = code_0_3(by_mul ? __fmul_rn(d, inv) : __fdiv_rn(d, scale));
+            if (t < 16) cw0 = c * (1u << (2 * t)) + cw0;
+            else cw1 = c * (1u << (2 * (t - 16))) + cw1;
+        }
     }
     // ---- outlier values ----
     float ms = 0.f, mc = 0.f;
@@ -381,8 +435,42 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_lane_kernel(PackKParam
             val |= fp4 << (4 * rank);
         }
     }
-    // ---- per-channel planes: consecutive lanes, consecutive entries ----
-    if (slot_ok) {
+    // ---- per-channel planes ----
+    // With head_dim 128 the four warps of the block hold the four channel blocks of one (group, head): their plane
+    // entries go through shared memory and leave as whole 16-byte pieces of contiguous rows (the standard planes:
+    // int8 exponents, bf16 zero-points and map), one plane per warp.  Other shapes write lane by lane.
+    __shared__ __align__(16) uint8_t s_rows[PACK_WARPS == 4 ? 128 * (1 + 2 + 2 + 2 + 4 + 4) : 16];
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(p.k_scale) | reinterpret_cast<uintptr_t>(p.k_zp) | reinterpret_cast<uintptr_t>(p.k_mapscale) |
+                             reinterpret_cast<uintptr_t>(p.k_mapcenter) | reinterpret_cast<uintptr_t>(p.k_obmp) | reinterpret_cast<uintptr_t>(p.k_oval)) & 15u) == 0;
+    const bool staged = nblk == PACK_WARPS && p.scale_kind == OMMX_SCALE_INT8_EXP && K > 0 && p.outlier_map && NB <= 4 && aligned16;
+    if (staged) {
+        // every warp of the block is here: g, h and the pool decisions above are the same for all four
+        const int d = blk * 32 + lane;
+        s_rows[d] = (uint8_t)(int8_t)e;
+        reinterpret_cast<uint16_t *>(s_rows + 128)[d] = (uint16_t)f32_to_bf16_bits(zp);
+        reinterpret_cast<uint16_t *>(s_rows + 384)[d] = (uint16_t)f32_to_bf16_bits(ms);
+        reinterpret_cast<uint16_t *>(s_rows + 640)[d] = (uint16_t)f32_to_bf16_bits(mc);
+        reinterpret_cast<uint32_t *>(s_rows + 896)[d] = omask;
+#pragma unroll
+        for (int i = 0; i < NB; ++i) s_rows[1408 + d * NB + i] = (uint8_t)(val >> (8 * i));
+        __syncthreads();
+        if (slot_ok) {
+            const int64_t row = ((int64_t)slot * p.H + h) * D;           // first channel of the (slot, head) row
+            const uint4 *src = reinterpret_cast<const uint4 *>(s_rows);
+            if (warp == 0) {
+                if (lane < 8) reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.k_scale) + row)[lane] = src[lane];
+                else if (lane < 24) reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.k_zp) + 2 * row)[lane - 8] = src[lane];
+            } else if (warp == 1) {
+                if (lane < 16) reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.k_mapscale) + 2 * row)[lane] = src[24 + lane];
+                else reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.k_mapcenter) + 2 * row)[lane - 16] = src[40 + lane - 16];
+            } else if (warp == 2) {
+                reinterpret_cast<uint4 *>(p.k_obmp + 4 * row)[lane] = src[56 + lane];
+            } else {
+                // 128 * NB bytes: a multiple of 16 only for even NB; the row start is 16-byte aligned when 128 * NB is
+                for (int i = lane; i < 8 * NB; i += 32) reinterpret_cast<uint4 *>(p.k_oval + row * NB)[i] = src[88 + i];
+            }
+        }
+    } else if (slot_ok) {
         const int64_t off = ((int64_t)slot * p.H + h) * D + blk * 32 + lane;
         if (p.scale_kind == OMMX_SCALE_INT8_EXP) reinterpret_cast<int8_t *>(p.k_scale)[off] = (int8_t)e;
         else if (p.scale_kind == OMMX_SCALE_BF16) reinterpret_cast<uint16_t *>(p.k_scale)[off] = (uint16_t)f32_to_bf16_bits(scale);

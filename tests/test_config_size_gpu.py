@@ -94,6 +94,9 @@ class _FastCase(Case):
                                               outlier_repr="bitmap", outlier_select="signed", use_pow2=True,
                                               kv_outlier_map=True, page_size=16)
             npl = {n: plane_to_numpy(pl[n]) for n in PLANES}
+            T = edge - 8
+            npl.update(head_dim=K.shape[2], n_kv_heads=K.shape[1], num_tokens=T, n_groups=T // 32, page_size=16,
+                       outliers_per_vector=6, kv_outlier_map=True, kv_int8_scale=True, scale_bf16=True)
             q = self.q[b].float().numpy()
             if kernel_arith:
                 o, lse, _ = O.decode_split_kv(q, npl, K[tail].numpy(), V[tail].numpy(), self.sm_scale, splits, split_pv=True)

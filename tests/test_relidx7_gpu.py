@@ -56,7 +56,12 @@ def test_outlier_index_convert_round_trip(k):
 def test_decode_relidx7_planes_equal_bitmask_planes(k, H, Hq):
     case = Case([3000, 500], H=H, Hq=Hq, seed=k + H, k=k)
     o_bm, lse_bm = case.run(num_kv_splits=9)
-    oidx = torch.from_numpy(O.relidx7_from_bitmask(case.pooled_np["k_obmp"], k)).cuda()
+    obmp = case.pooled_np["k_obmp"]                                # pooled plane: slots no sequence owns are all zero
+    words = obmp.reshape(-1, 4).copy().view(np.uint32)[:, 0]
+    used = np.array([bin(int(w)).count("1") == k for w in words])
+    flat = np.zeros((words.shape[0], (7 * k + 7) // 8), dtype=np.uint8)
+    flat[used] = O.relidx7_from_bitmask(obmp.reshape(-1, 4)[used], k)
+    oidx = torch.from_numpy(flat.reshape(obmp.shape[:-1] + (flat.shape[1],))).cuda()
     from open_ommx_serve_b200.attention.paged_decode import ommx_paged_decode_attention_canonical
     p = case.planes
     o = torch.zeros_like(o_bm)
