@@ -60,7 +60,7 @@ constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // about a second of SM 
 struct S1Params {
     const __nv_bfloat16 *q;
     int64_t q_sb, q_sh;
-    int32_t B, Hq, H, gqa, q_pair_ok;    // q_pair_ok: two adjacent q elements may be fetched as one 32-bit word
+    int32_t B, Hq, H, gqa, q_vec_ok;     // q_vec_ok: eight adjacent q elements may be fetched as one 16-byte word
     const uint8_t *k_base, *v_main, *v_scale, *v_zp, *k_scale, *k_zp, *k_ms, *k_mc, *k_obmp, *k_oval;
     int32_t ps, ppg, num_pages, num_slots, k_out, nb, use_map;
     int32_t nbi;                         // bytes of outlier index per channel: 4 (flat bitmask) or ceil(7k/8) (relidx7, idx7 = 1)
@@ -434,19 +434,23 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             uint8_t *tile = s_tiles + unit * DT_BYTES;
             const int s = ring_slot(it, NS);
             const uint32_t ph = ring_phase(it, NS);
-            // This lane's two raw query values (channels 64hf + 2*lane, +1) of the kv head's query heads, for the
-            // fp32 q.zp sums; requested before the waits below so that the loads are in flight meanwhile.
-            uint32_t qpair[8];
-            {
-                const __nv_bfloat16 *qh = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa) * p.q_sh + 64 * hf + 2 * lane;
-#pragma unroll
-                for (int hd = 0; hd < 8; ++hd) {
-                    qpair[hd] = 0u;
-                    if (hd < p.gqa) {
-                        const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qh + (int64_t)hd * p.q_sh);
-                        if (p.q_pair_ok) qpair[hd] = __ldg(reinterpret_cast<const uint32_t *>(q16));
-                        else qpair[hd] = (uint32_t)__ldg(q16) | ((uint32_t)__ldg(q16 + 1) << 16);
-                    }
+            // The fp32 q.zp sums of this half's 64 channels: lane = (query head of the kv head, block of 8 or 16
+            // channels).  The lane's raw query values are requested before the waits below, so that the loads are
+            // in flight meanwhile.
+            const bool gq8 = p.gqa > 4;                               // 8 heads x 4 blocks of 16, else 4 heads x 8 blocks of 8
+            const int zq_head = gq8 ? lane >> 2 : lane >> 3, zq_blk = gq8 ? lane & 3 : lane & 7;
+            const int zq_c0 = 64 * hf + zq_blk * (gq8 ? 16 : 8);
+            uint4 qv0 = make_uint4(0u, 0u, 0u, 0u), qv1 = make_uint4(0u, 0u, 0u, 0u);
+            if (zq_head < p.gqa) {
+                const __nv_bfloat16 *qp = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + zq_head) * p.q_sh + zq_c0;
+                if (p.q_vec_ok) {
+                    qv0 = __ldg(reinterpret_cast<const uint4 *>(qp));
+                    if (gq8) qv1 = __ldg(reinterpret_cast<const uint4 *>(qp) + 1);
+                } else {
+                    const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qp);
+                    auto pair = [&](int i) { return (uint32_t)__ldg(q16 + i) | ((uint32_t)__ldg(q16 + i + 1) << 16); };
+                    qv0 = make_uint4(pair(0), pair(2), pair(4), pair(6));
+                    if (gq8) qv1 = make_uint4(pair(8), pair(10), pair(12), pair(14));
                 }
             }
             if (!mbar_wait(bar_full + 8 * s, ph)) {
@@ -482,37 +486,24 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     clamped_any |= cl;
                     *reinterpret_cast<uint16_t *>(tile + kf_off + 4 * c) = (uint16_t)fb;
                 }
-                {   // q.zp of this half's 64 channels for the (up to 8) query heads of the kv head, in fp32 from the
-                    // raw bf16 query, as the reference forms it.  The 8 per-lane partials are summed over the warp by a
-                    // halving exchange (lane bits 4, 3, 2 select the head, then two plain steps): 9 shuffles.
-                    const float zp0 = bf16_bits_to_f32(z2 & 0xFFFFu), zp1 = bf16_bits_to_f32(z2 >> 16);
-                    float v[8];
+                {   // q.zp in fp32 from the raw bf16 query, as the reference forms it: 8 (16) products per lane, then the
+                    // lanes of a head are summed by 3 (2) exchanges
+                    auto dot4 = [](const uint4 &q, const uint4 &z, float acc) {
+                        const uint32_t qw[4] = {q.x, q.y, q.z, q.w}, zw[4] = {z.x, z.y, z.z, z.w};
 #pragma unroll
-                    for (int hd = 0; hd < 8; ++hd)
-                        v[hd] = fmaf(bf16_bits_to_f32(qpair[hd] & 0xFFFFu), zp0, bf16_bits_to_f32(qpair[hd] >> 16) * zp1);
-                    float w4[4], w2[2];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const bool up = (lane & 16) != 0;
-                        const float give = up ? v[i] : v[i + 4], keep = up ? v[i + 4] : v[i];
-                        w4[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, give, 16);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        const bool up = (lane & 8) != 0;
-                        const float give = up ? w4[i] : w4[i + 2], keep = up ? w4[i + 2] : w4[i];
-                        w2[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, give, 8);
-                    }
-                    float w1;
-                    {
-                        const bool up = (lane & 4) != 0;
-                        const float give = up ? w2[0] : w2[1], keep = up ? w2[1] : w2[0];
-                        w1 = keep + __shfl_xor_sync(0xFFFFFFFFu, give, 4);
-                    }
-                    w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 2);
-                    w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 1);
-                    if ((lane & 3) == 0)                             // lane bits 4,3,2 = head bits 2,1,0
-                        reinterpret_cast<float *>(tile + ROW_ZP * DT_STRIDE)[8 * hf + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)] = w1;
+                        for (int i = 0; i < 4; ++i) {
+                            acc = fmaf(__uint_as_float(qw[i] << 16), __uint_as_float(zw[i] << 16), acc);
+                            acc = fmaf(__uint_as_float(qw[i] & 0xFFFF0000u), __uint_as_float(zw[i] & 0xFFFF0000u), acc);
+                        }
+                        return acc;
+                    };
+                    const uint8_t *zrow = gb + p.o_kz + h * 256 + 2 * zq_c0;
+                    float sum = dot4(qv0, *reinterpret_cast<const uint4 *>(zrow), 0.f);
+                    if (gq8) sum = dot4(qv1, *reinterpret_cast<const uint4 *>(zrow + 16), sum);
+                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+                    if (!gq8) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+                    if (zq_blk == 0) reinterpret_cast<float *>(tile + ROW_ZP * DT_STRIDE)[8 * hf + zq_head] = sum;   // heads past gqa: 0
                 }
                 {   // V side: one token, two scale groups: power-of-two factor and zero-point of each
                     const int copy = it & 1;
@@ -1389,7 +1380,7 @@ static int launch_stage1(const ommx_decode_args *a, cudaStream_t st) {
     S1Params p;
     p.q = (const __nv_bfloat16 *)a->q; p.q_sb = a->q_stride_b; p.q_sh = a->q_stride_h;
     p.B = a->batch; p.Hq = a->n_q_heads; p.H = pl.n_kv_heads; p.gqa = a->n_q_heads / pl.n_kv_heads;
-    p.q_pair_ok = (((uintptr_t)a->q & 3) == 0 && a->q_stride_b % 2 == 0 && a->q_stride_h % 2 == 0) ? 1 : 0;
+    p.q_vec_ok = (((uintptr_t)a->q & 15) == 0 && a->q_stride_b % 8 == 0 && a->q_stride_h % 8 == 0) ? 1 : 0;
     p.k_base = (const uint8_t *)pl.k_base; p.v_main = (const uint8_t *)pl.v_main;
     p.v_scale = (const uint8_t *)pl.v_scale; p.v_zp = (const uint8_t *)pl.v_zp;
     p.k_scale = (const uint8_t *)pl.k_scale; p.k_zp = (const uint8_t *)pl.k_zp;
