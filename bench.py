@@ -303,7 +303,7 @@ class LayerStack:
         self.splits = _auto_num_kv_splits(max(P, 1), self.batch, device=self.device, kv_heads=self.hkv)
         self.ws = torch.empty(self.batch, self.hq, self.splits + 1, D + 1, dtype=torch.float32, device=self.device)
 
-    def decode_layer(self, i, q=None, stage=0, fn=None, o=None, lse=None):
+    def decode_layer(self, i, q=None, stage=0, fn=None, o=None, lse=None, head_gather=None):
         """One decode call on layer i through this package's entry, or through `fn` (the reference's
         Triton launcher, which takes the same arguments)."""
         L = self.layers[i]
@@ -311,7 +311,7 @@ class LayerStack:
         kw = {}
         if fn is None:
             from open_ommx_serve_b200.attention.paged_decode import ommx_paged_decode_attention_canonical as fn
-            kw = dict(num_kv_splits=self.splits, attn_logits=self.ws, _stage=stage)
+            kw = dict(num_kv_splits=self.splits, attn_logits=self.ws, _stage=stage, head_gather=head_gather)
         fn(L["q"] if q is None else q, p["k_base"], p["k_scale"], p["k_zp"], None, p["k_oval"],
            p["v_main"], p["v_scale"], p["v_zp"], L["k_tail"], L["v_tail"], self.b_tail_len,
            self.o[i] if o is None else o, self.lse[i] if lse is None else lse,
@@ -424,11 +424,22 @@ def run_ours(args, rank, world, local_rank):
     lib = _lib.load()
     triton_ref = TritonReference() if (rank == 0 and not args.no_triton) else None
 
+    peer = None
+    if world > 1 and args.gather == "peer":
+        peer = sharding.PeerHeadGather(world, rank, max(2, LAYERS), 1, hq, D, device)
+
     def step_full():
         for i in range(LAYERS):
-            stack.decode_layer(i)
-            if world > 1:
-                sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
+            if peer is not None:
+                stack.decode_layer(i, head_gather=peer.plan(i))       # stage 2 stores the rows into every rank's buffer
+            else:
+                stack.decode_layer(i)
+                if world > 1:
+                    sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
+
+    def step_stage2_gather():
+        for i in range(LAYERS):
+            stack.decode_layer(i, stage=2, head_gather=peer.plan(i))
 
     def step_stage1():
         for i in range(LAYERS):
@@ -475,11 +486,16 @@ def run_ours(args, rank, world, local_rank):
             sampler.__exit__()
         t_s2 = timed_graph(step_stage2, max(3, k_steps // 2), args.warmup, flush, torch)
         barrier()
-        ms_ag = None
+        ms_ag = ms_nccl = None
         if world > 1:
             t_ag = timed_graph(step_gather, max(3, k_steps // 2), args.warmup, flush, torch)
             barrier()
-            ms_ag = reduce_max(sum(t_ag) / len(t_ag))
+            ms_nccl = ms_ag = reduce_max(sum(t_ag) / len(t_ag))
+            if peer is not None:
+                # what the exchange adds to stage 2: stage 2 with the peer stores and the arrival wait, minus stage 2 alone
+                t_pg = timed_graph(step_stage2_gather, max(3, k_steps // 2), args.warmup, flush, torch)
+                barrier()
+                ms_ag = max(0.0, reduce_max(sum(t_pg) / len(t_pg)) - reduce_max(sum(t_s2) / len(t_s2)))
         ms_step = reduce_max(sum(t_full) / len(t_full))
         ms_s1 = reduce_max(sum(t_s1) / len(t_s1))
         ms_s2 = reduce_max(sum(t_s2) / len(t_s2))
@@ -491,6 +507,7 @@ def run_ours(args, rank, world, local_rank):
             "stage1_us": ms_s1 * 1e3 / LAYERS, "stage1_gbs": bytes_launch / (ms_s1 / LAYERS) / 1e6,
             "stage2_us": ms_s2 * 1e3 / LAYERS,
             "allgather_us": None if ms_ag is None else ms_ag * 1e3 / LAYERS,
+            "nccl_allgather_us": None if ms_nccl is None else ms_nccl * 1e3 / LAYERS,
             "splits": stack.splits, "bytes_per_layer": bytes_layer,
             "triton_b200_us": None if tri is None else tri["us"],
             "triton_b200": tri,
@@ -513,10 +530,14 @@ def run_ours(args, rank, world, local_rank):
         stack.k_tail_all[:, 0, new_row].copy_(in_dev[:, n_q:n_q + n_kv].view(LAYERS, hkv, D))
         stack.v_tail_all[:, 0, new_row].copy_(in_dev[:, n_q + n_kv:].view(LAYERS, hkv, D))
         for i in range(LAYERS):
-            stack.decode_layer(i, q=in_dev[i, :n_q].view(1, hq, D))
-            if world > 1:
-                sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
-        o_host.copy_(gathered if world > 1 else stack.o, non_blocking=True)     # device -> host, once per step
+            if peer is not None:
+                stack.decode_layer(i, q=in_dev[i, :n_q].view(1, hq, D), head_gather=peer.plan(i))
+            else:
+                stack.decode_layer(i, q=in_dev[i, :n_q].view(1, hq, D))
+                if world > 1:
+                    sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
+        # device -> host, once per step
+        o_host.copy_(peer.all_buffers()[:LAYERS] if peer is not None else (gathered if world > 1 else stack.o), non_blocking=True)
 
     for _ in range(max(3, args.warmup)):
         step_e2e()
@@ -538,6 +559,17 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms_e2e = reduce_max(sum(e2e_graph_times) / len(e2e_graph_times))
 
+    gather_check = None
+    if peer is not None:
+        # the exchanged rows against an NCCL all-gather of the same outputs, once, outside any timed region
+        for i in range(LAYERS):
+            stack.decode_layer(i, head_gather=peer.plan(i))
+            sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
+        torch.cuda.synchronize()
+        same = all(torch.equal(peer.gathered(i), gathered[i]) for i in range(LAYERS))
+        gather_check = "equal to the NCCL all-gather" if reduce_max(0.0 if same else 1.0) == 0.0 else "MISMATCH against the NCCL all-gather"
+        peer.close()
+        peer = None
     # ---- the other configurations, as sub-records of the same line ----
     workloads = {}
     del stack
@@ -571,7 +603,10 @@ def run_ours(args, rank, world, local_rank):
                    "ctx": args.ctx, "batch": 1, "kv_heads_per_gpu": hkv, "splits": per_ctx[str(args.ctx)]["splits"],
                    "l2": "flushed between timed steps (256 MiB memset); one step reads 32 distinct plane sets",
                    "timing": "CUDA-graph replay of the whole step, CUDA events per step, mean of K, max over ranks",
-                   "collective": "one NCCL all-gather of [1, Hq/N, D] f32 per layer inside the step" if world > 1 else "none"},
+                   "collective": ("none" if world == 1 else
+                                  "stage 2 stores its [1, Hq/N, D] f32 rows into every rank's buffer (peer-mapped memory over NVLink, "
+                                  "one arrival count per rank, bounded wait); nccl_allgather_us is the NCCL all-gather of the same rows timed alone"
+                                  if peer is not None else "one NCCL all-gather of [1, Hq/N, D] f32 per layer inside the step")},
         "hbm_gbs": results["bytes_layer"] / (results["ms_step"] / LAYERS) / 1e6,
         "tokens_per_s": 1.0 / (results["ms_step"] * 1e-3),
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
@@ -591,6 +626,7 @@ def run_ours(args, rank, world, local_rank):
                         "per layer, one copy of all outputs back; the whole step replayed from a CUDA graph; "
                         "eager_value is the same step launched from Python"},
         "gpu_launches": results["launches_step"] * args.steps,
+        "gather_check": gather_check,
         "contexts": per_ctx,
         "triton_reference": None if triton_ref is None else {"available": triton_ref.fn is not None, "note": triton_ref.why,
                                                              "seconds_spent": round(triton_ref.spent, 1)},
@@ -756,6 +792,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton", action="store_true", help="skip timing the reference's Triton kernels")
     ap.add_argument("--no-workloads", action="store_true", help="skip the sub-record workloads")
+    ap.add_argument("--gather", default="peer", choices=("peer", "nccl"),
+                    help="N > 1: head outputs exchanged by stage 2's peer stores (default) or by an NCCL all-gather")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers in the stack (32 = the benchmark)")
     ap.add_argument("--profile", action="store_true", help="eager launches only, for ncu (use a small --layers)")
     ap.add_argument("--k", type=int, default=K_OUT, help="outliers per K vector (the headline recipe has 6)")

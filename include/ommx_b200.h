@@ -15,13 +15,14 @@
 #ifndef OMMX_B200_H_
 #define OMMX_B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
 extern "C" {
 #endif
 
-#define OMMX_B200_ABI_VERSION 3
+#define OMMX_B200_ABI_VERSION 4
 
 /* host-side argument errors (return values) */
 #define OMMX_E_ARG          (-1)   /* null pointer, bad size, misaligned plane */
@@ -124,6 +125,25 @@ int ommx_b200_outlier_index_convert(const void *src, void *dst, int64_t frames, 
  * b_seq_len holds PACKED token counts; split s covers tokens [s*per, min((s+1)*per, seq)) with
  * per = ceil(ceil(seq/num_kv_splits)/32)*32, exactly as the reference.
  */
+/*
+ * Head-output exchange fused into stage 2, for kv heads sharded over the GPUs of one node (the split vLLM
+ * tensor parallelism applies to the reference backend, ommx_gpu_serve/integration/vllm/backend.py:859-873;
+ * it stands where that stack runs a collective on the attention output).  Every rank's stage 2 stores its
+ * [batch, n_q_heads, head_dim] f32 rows into slot `rank` of EVERY rank's output buffer
+ * [world, batch, n_q_heads, head_dim] through peer-mapped pointers (plain stores over NVLink, no multicast),
+ * then its last thread block publishes the call count to each peer's flag word and waits - for about a second
+ * of SM clock at most, then OMMX_ST_TIMEOUT - until every peer's count has reached its own.  When the call's
+ * kernels have finished, the local buffer holds all ranks' rows.  All ranks must make the same sequence of
+ * calls on a gather; consecutive calls must alternate between at least two destination buffers (a peer may be
+ * one call ahead).  Buffers, flag words and state live in memory from ommx_b200_peer_alloc.
+ */
+typedef struct ommx_head_gather {
+    int32_t world, rank;            /* 2..32 ranks */
+    float *const *dst;              /* device array [world]: rank r's output buffer for this call (dst[rank]: own) */
+    uint32_t *const *flags;         /* device array [world]: rank r's flag words [world] u32, zero at start */
+    uint32_t *state;                /* this rank's own 2 words (calls made, block ticket), zero at start */
+} ommx_head_gather;
+
 typedef struct ommx_decode_args {
     const void *q;                /* bf16 [batch, n_q_heads, head_dim] */
     int32_t q_dtype;              /* OMMX_DT_BF16 */
@@ -155,6 +175,7 @@ typedef struct ommx_decode_args {
     int32_t abl_flags;            /* differential-timing ablations (break parity), 0 in service:
                                      1 skip outlier splice, 2 skip V/PV, 4 skip K code dequant
                                      (reference: OMMX_ABL_* knobs, attention/paged_decode.py:3267-3279) */
+    const ommx_head_gather *gather; /* optional: exchange the head outputs with the other ranks in stage 2 */
 } ommx_decode_args;
 
 int ommx_b200_decode(const ommx_decode_args *args, void *stream);          /* stage 1 + stage 2 */
@@ -246,6 +267,16 @@ int ommx_b200_kv_gather_tail(const ommx_kv_pool *pool, const void *sel, const vo
  * device.  Replaces _auto_num_kv_splits (attention/paged_decode.py:409-461), which callers
  * use to size attn_logits once.
  */
+/*
+ * Device memory that other processes of the node can map (CUDA IPC), for ommx_head_gather.  `alloc` returns a
+ * zero-filled allocation and its 64-byte handle; `open` maps another process's allocation into this one (peer
+ * access over NVLink) and `close` unmaps it; `free` releases an own allocation.  Call them outside stream capture.
+ */
+int ommx_b200_peer_alloc(size_t bytes, void **ptr, void *handle64);
+int ommx_b200_peer_open(const void *handle64, void **ptr);
+int ommx_b200_peer_close(void *ptr);
+int ommx_b200_peer_free(void *ptr);
+
 int ommx_b200_auto_num_kv_splits(int32_t max_seq_len, int32_t batch, int32_t n_kv_heads);
 /* Smallest split count ommx_b200_decode accepts for a context of max_seq_len packed tokens. */
 int ommx_b200_min_num_kv_splits(int32_t max_seq_len, int32_t page_size);

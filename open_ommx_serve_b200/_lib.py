@@ -40,6 +40,10 @@ class PackArgs(C.Structure):
                 ("planes", KVPlanes), ("status", C.c_void_p)]
 
 
+class HeadGather(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("dst", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p)]
+
+
 class DecodeArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("q_dtype", C.c_int32), ("batch", C.c_int32), ("n_q_heads", C.c_int32),
                 ("q_stride_b", C.c_int64), ("q_stride_h", C.c_int64),
@@ -56,7 +60,7 @@ class DecodeArgs(C.Structure):
                 ("num_kv_splits", C.c_int32), ("max_seq_len", C.c_int32), ("max_tail_len", C.c_int32),
                 ("seg_group_base", C.c_int32), ("packed_start_offset", C.c_int32),
                 ("sm_scale", C.c_float), ("logit_cap", C.c_float), ("status", C.c_void_p),
-                ("abl_flags", C.c_int32)]
+                ("abl_flags", C.c_int32), ("gather", C.c_void_p)]
 
 
 class KVPool(C.Structure):
@@ -88,6 +92,10 @@ SYMBOLS = {
     "ommx_b200_kv_append_decode": (C.c_int, [C.POINTER(KVAppendArgs), C.c_void_p]),
     "ommx_b200_kv_gather_tail": (C.c_int, [C.POINTER(KVPool), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                            C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ommx_b200_peer_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),
+    "ommx_b200_peer_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "ommx_b200_peer_close": (C.c_int, [C.c_void_p]),
+    "ommx_b200_peer_free": (C.c_int, [C.c_void_p]),
     "ommx_b200_auto_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32, C.c_int32]),
     "ommx_b200_min_num_kv_splits": (C.c_int, [C.c_int32, C.c_int32]),
     "ommx_b200_merge_states": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,

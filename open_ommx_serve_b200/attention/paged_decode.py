@@ -140,6 +140,7 @@ def ommx_paged_decode_attention_canonical(
     status: Any = None,
     _stage: int = 0,
     static_workspace: bool = False,
+    head_gather: Any = None,
 ) -> None:
     """Decode attention of one query row per sequence. Writes ``o`` / ``lse`` in place.
 
@@ -159,6 +160,10 @@ def ommx_paged_decode_attention_canonical(
     into the library (``ommx_b200_decode_static_ws``).  ``batch * Hq * num_kv_splits * (D+1)`` must
     stay within 2 Mi floats (``ValueError`` beyond); calls that overlap on the GPU share the array
     and race; make the first call on a device outside stream capture.
+
+    ``head_gather`` (not in the reference): the ``(PeerHeadGather, layer)`` plan of a kv-head sharded run
+    (``sharding.PeerHeadGather.plan``); stage 2 then also stores this rank's rows into every rank's
+    gathered buffer and returns when all ranks' rows of the layer have arrived in this rank's.
     """
     lib = _lib.load()
     if not q.is_cuda:
@@ -306,6 +311,10 @@ def ommx_paged_decode_attention_canonical(
     # ablation knobs (differential timing only; recorded so a leaked export cannot pass as served)
     abl = sum(1 << i for i, n in enumerate(ABL_FLAG_NAMES) if env_truthy(os.environ.get(n)))
     a.abl_flags = abl
+    if head_gather is not None:
+        if int(_stage) == 1:
+            raise ValueError("head_gather belongs to stage 2; _stage=1 runs stage 1 alone")
+        a.gather = head_gather.check(batch, head_num, D, q.device)
     _LAUNCHES["abl"] |= abl
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream

@@ -1012,6 +1012,12 @@ struct S2Params {
     float *lse;
     int64_t lse_sb;
     float sm_scale, logit_cap;
+    // head-output exchange (g_world <= 1: none)
+    int32_t g_world, g_rank;
+    float *const *g_dst;
+    uint32_t *const *g_flags;
+    uint32_t *g_state;
+    int32_t *status;
 };
 
 constexpr int S2_THREADS = 512;
@@ -1163,6 +1169,46 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
         if (p.o_bf16) reinterpret_cast<__nv_bfloat16 *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = __float2bfloat16_rn(out);
         else reinterpret_cast<float *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = out;
         if (tid == 0) p.lse[(int64_t)b * p.lse_sb + hq] = g_max + logf(den);
+        // sharded heads: this row goes to slot g_rank of every rank's buffer [world, batch, Hq, D] (peer stores)
+        if (p.g_world > 1) {
+            const int64_t at = (((int64_t)p.g_rank * gridDim.y + b) * p.Hq + hq) * D + tid;
+            for (int r = 0; r < p.g_world; ++r) p.g_dst[r][at] = out;
+        }
+    }
+    if (p.g_world > 1) {
+        // Rows first, then the count: every block fences its stores system-wide and draws a ticket; the block that
+        // draws the last one publishes this rank's call count to each peer and waits for theirs.
+        __threadfence_system();
+        __syncthreads();
+        __shared__ uint32_t s_last;
+        if (tid == 0) {
+            const uint32_t total = gridDim.x * gridDim.y;
+            const uint32_t t = atomicAdd(&p.g_state[1], 1u);
+            s_last = (t == total - 1u) ? 1u : 0u;
+        }
+        __syncthreads();
+        if (s_last && warp == 0) {
+            __threadfence_system();
+            uint32_t epoch = 0;
+            if (lane == 0) {
+                p.g_state[1] = 0u;
+                epoch = p.g_state[0] + 1u;
+                p.g_state[0] = epoch;
+            }
+            epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
+            if (lane < p.g_world && lane != p.g_rank) {
+                uint32_t *theirs = p.g_flags[lane] + p.g_rank;                 // my word in the peer's flags
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+                const uint32_t *mine = p.g_flags[p.g_rank] + lane;             // the peer's word in my flags
+                const long long t_end = clock64() + WAIT_LIMIT_CYCLES;
+                for (uint32_t i = 1;; ++i) {
+                    uint32_t seen;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                    if ((int32_t)(seen - epoch) >= 0) break;
+                    if ((i & 63u) == 0 && clock64() > t_end) { or_status(p.status, OMMX_ST_TIMEOUT); break; }
+                }
+            }
+        }
     }
 }
 
@@ -1465,6 +1511,13 @@ static int launch_stage2(const ommx_decode_args *a, cudaStream_t st, bool after_
     p.o = a->o; p.o_bf16 = (a->o_dtype == OMMX_DT_BF16); p.o_sb = a->o_stride_b; p.o_sh = a->o_stride_h;
     p.lse = a->lse; p.lse_sb = a->lse_stride_b;
     p.sm_scale = a->sm_scale; p.logit_cap = a->logit_cap;
+    p.g_world = 0; p.g_rank = 0; p.g_dst = nullptr; p.g_flags = nullptr; p.g_state = nullptr; p.status = a->status;
+    if (a->gather) {
+        const ommx_head_gather *g = a->gather;
+        if (g->world < 2 || g->world > 32 || g->rank < 0 || g->rank >= g->world || !g->dst || !g->flags || !g->state)
+            return fail(OMMX_E_ARG, "head gather: world must be 2..32, rank inside it, and dst / flags / state set");
+        p.g_world = g->world; p.g_rank = g->rank; p.g_dst = g->dst; p.g_flags = g->flags; p.g_state = g->state;
+    }
     {
         // Stage 1 runs with the largest shared-memory carve-out; asking for the same split here spares the SMs a
         // reconfiguration between the two kernels of every layer.

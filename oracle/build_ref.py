@@ -55,6 +55,13 @@ def build_ref(checkout: str = "/root/reference", force: bool = False) -> dict:
             res = subprocess.run(cmd, capture_output=True, text=True)
             log.append("pip install ommx_gpu_serve -> baseline/_ref: " +
                        ("ok" if res.returncode == 0 else "FAILED\n" + res.stdout[-2000:] + res.stderr[-2000:]))
+    # The package also ships the C++/CUDA sources of the reference's weight-linear kernels as data files.  Nothing
+    # on the attention path loads them, and they must not travel to a multi-GPU box (they name TMA loads with
+    # cluster multicast, which the GPU pool refuses to accept for calls on two or more GPUs): drop them.
+    csrc = os.path.join(BASELINE_REF, "ommx_gpu_serve", "csrc")
+    if os.path.isdir(csrc):
+        shutil.rmtree(csrc)
+        log.append("baseline/_ref/ommx_gpu_serve/csrc (weight-linear kernel sources, unused here): removed")
     elif not os.path.isdir(pkg_src):
         log.append(f"{pkg_src} not present: baseline/_ref left as it is")
     fq_src = os.path.join(checkout, "ommx_fakequant", "quant_function.py")
