@@ -58,7 +58,7 @@ def packed_len(ctx):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one stage-1 launch under ncu over its algorithmic
 # bytes (profiles/decode_stage1_64k_b1.md): the planes are read once, nothing is re-read
-NCU_TRAFFIC_RATIO = 70.33e6 / 69138432.0
+NCU_TRAFFIC_RATIO = (69.261312e6 + 1.031936e6) / 69138432.0
 
 
 def unit_bytes(k):

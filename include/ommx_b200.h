@@ -128,19 +128,22 @@ int ommx_b200_outlier_index_convert(const void *src, void *dst, int64_t frames, 
 /*
  * Head-output exchange fused into stage 2, for kv heads sharded over the GPUs of one node (the split vLLM
  * tensor parallelism applies to the reference backend, ommx_gpu_serve/integration/vllm/backend.py:859-873;
- * it stands where that stack runs a collective on the attention output).  Every rank's stage 2 stores its
- * [batch, n_q_heads, head_dim] f32 rows into slot `rank` of EVERY rank's output buffer
- * [world, batch, n_q_heads, head_dim] through peer-mapped pointers (plain stores over NVLink, no multicast),
- * then its last thread block publishes the call count to each peer's flag word and waits - for about a second
- * of SM clock at most, then OMMX_ST_TIMEOUT - until every peer's count has reached its own.  When the call's
- * kernels have finished, the local buffer holds all ranks' rows.  All ranks must make the same sequence of
- * calls on a gather; consecutive calls must alternate between at least two destination buffers (a peer may be
- * one call ahead).  Buffers, flag words and state live in memory from ommx_b200_peer_alloc.
+ * it stands where that stack runs a collective on the attention output).  Every output element of a rank's
+ * stage 2 goes, as one 8-byte word (value, call count), into slot `rank` of every OTHER rank's receive buffer
+ * [world, batch, n_q_heads, head_dim] through peer-mapped pointers (plain 8-byte stores over NVLink: a word
+ * arrives whole, so no fence and no separate flag; no multicast).  The same thread block then waits for the words
+ * of its (sequence, head) row from every peer - their count must equal this call's; about a second of SM clock at
+ * most, then OMMX_ST_TIMEOUT - and writes the values to `out`, this rank's plain [world, batch, n_q_heads, head_dim]
+ * f32 buffer (its own rows go there directly).  When the call's kernels have finished, `out` holds all ranks' rows.
+ * All ranks must make the same sequence of calls on a gather, and consecutive calls must use different receive
+ * buffers in turn (a peer may be one call ahead): recv[r] is rank r's buffer for THIS call.  Receive buffers come
+ * from ommx_b200_peer_alloc (zero-filled: count 0 is never current); `state` is 2 zero-initialised words of this
+ * rank's own memory, shared by all calls of the gather.
  */
 typedef struct ommx_head_gather {
     int32_t world, rank;            /* 2..32 ranks */
-    float *const *dst;              /* device array [world]: rank r's output buffer for this call (dst[rank]: own) */
-    uint32_t *const *flags;         /* device array [world]: rank r's flag words [world] u32, zero at start */
+    uint64_t *const *recv;          /* device array [world]: rank r's receive buffer for this call (recv[rank]: own) */
+    float *out;                     /* this rank's [world, batch, n_q_heads, head_dim] f32 result of this call */
     uint32_t *state;                /* this rank's own 2 words (calls made, block ticket), zero at start */
 } ommx_head_gather;
 

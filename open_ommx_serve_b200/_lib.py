@@ -41,7 +41,7 @@ class PackArgs(C.Structure):
 
 
 class HeadGather(C.Structure):
-    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("dst", C.c_void_p), ("flags", C.c_void_p), ("state", C.c_void_p)]
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("recv", C.c_void_p), ("out", C.c_void_p), ("state", C.c_void_p)]
 
 
 class DecodeArgs(C.Structure):

@@ -1014,8 +1014,8 @@ struct S2Params {
     float sm_scale, logit_cap;
     // head-output exchange (g_world <= 1: none)
     int32_t g_world, g_rank;
-    float *const *g_dst;
-    uint32_t *const *g_flags;
+    uint64_t *const *g_recv;
+    float *g_out;
     uint32_t *g_state;
     int32_t *status;
 };
@@ -1161,52 +1161,56 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
     s_acc[warp][lane] = a0; s_acc[warp][lane + 32] = a1;
     s_acc[warp][lane + 64] = a2; s_acc[warp][lane + 96] = a3;
     __syncthreads();
+    float out = 0.f;
     if (tid < D) {
         float acc = 0.f;
 #pragma unroll
         for (int w = 0; w < S2_WARPS; ++w) acc += s_acc[w][tid];
-        const float out = acc / (den > 0.f ? den : 1.f);
+        out = acc / (den > 0.f ? den : 1.f);
         if (p.o_bf16) reinterpret_cast<__nv_bfloat16 *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = __float2bfloat16_rn(out);
         else reinterpret_cast<float *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = out;
         if (tid == 0) p.lse[(int64_t)b * p.lse_sb + hq] = g_max + logf(den);
-        // sharded heads: this row goes to slot g_rank of every rank's buffer [world, batch, Hq, D] (peer stores)
-        if (p.g_world > 1) {
-            const int64_t at = (((int64_t)p.g_rank * gridDim.y + b) * p.Hq + hq) * D + tid;
-            for (int r = 0; r < p.g_world; ++r) p.g_dst[r][at] = out;
-        }
     }
     if (p.g_world > 1) {
-        // Rows first, then the count: every block fences its stores system-wide and draws a ticket; the block that
-        // draws the last one publishes this rank's call count to each peer and waits for theirs.
-        __threadfence_system();
+        // Sharded heads: the row travels to every peer as 8-byte words (value, call count); a word arrives whole,
+        // so the count tells the receiver that the value beside it is this call's.  Then this block collects the
+        // same row of every peer from its own receive buffer.
+        __shared__ uint32_t s_epoch;
+        if (tid == 0) s_epoch = *reinterpret_cast<volatile uint32_t *>(&p.g_state[0]) + 1u;
         __syncthreads();
-        __shared__ uint32_t s_last;
-        if (tid == 0) {
-            const uint32_t total = gridDim.x * gridDim.y;
-            const uint32_t t = atomicAdd(&p.g_state[1], 1u);
-            s_last = (t == total - 1u) ? 1u : 0u;
+        const uint32_t epoch = s_epoch;
+        const int64_t slot = (int64_t)gridDim.y * p.Hq * D;            // elements of one rank's slot
+        const int64_t row = ((int64_t)b * p.Hq + hq) * D;
+        if (tid < D) {
+            const uint64_t word = ((uint64_t)epoch << 32) | (uint64_t)__float_as_uint(out);
+            for (int r = 0; r < p.g_world; ++r)
+                if (r != p.g_rank)
+                    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.g_recv[r] + (int64_t)p.g_rank * slot + row + tid), "l"(word) : "memory");
+            p.g_out[(int64_t)p.g_rank * slot + row + tid] = out;
         }
-        __syncthreads();
-        if (s_last && warp == 0) {
-            __threadfence_system();
-            uint32_t epoch = 0;
-            if (lane == 0) {
-                p.g_state[1] = 0u;
-                epoch = p.g_state[0] + 1u;
-                p.g_state[0] = epoch;
+        const uint64_t *mine = p.g_recv[p.g_rank];
+        const long long t_end = clock64() + WAIT_LIMIT_CYCLES;
+        for (int idx = tid; idx < (p.g_world - 1) * D; idx += S2_THREADS) {
+            int r = idx / D;
+            const int e = idx - r * D;
+            r += (r >= p.g_rank) ? 1 : 0;                              // skip the own slot
+            const uint64_t *src = mine + (int64_t)r * slot + row + e;
+            uint64_t word = 0;
+            for (uint32_t i = 1;; ++i) {
+                asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
+                if ((uint32_t)(word >> 32) == epoch) break;
+                if ((i & 63u) == 0 && clock64() > t_end) { or_status(p.status, OMMX_ST_TIMEOUT); break; }
             }
-            epoch = __shfl_sync(0xFFFFFFFFu, epoch, 0);
-            if (lane < p.g_world && lane != p.g_rank) {
-                uint32_t *theirs = p.g_flags[lane] + p.g_rank;                 // my word in the peer's flags
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
-                const uint32_t *mine = p.g_flags[p.g_rank] + lane;             // the peer's word in my flags
-                const long long t_end = clock64() + WAIT_LIMIT_CYCLES;
-                for (uint32_t i = 1;; ++i) {
-                    uint32_t seen;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-                    if ((int32_t)(seen - epoch) >= 0) break;
-                    if ((i & 63u) == 0 && clock64() > t_end) { or_status(p.status, OMMX_ST_TIMEOUT); break; }
-                }
+            p.g_out[(int64_t)r * slot + row + e] = __uint_as_float((uint32_t)word);
+        }
+        // the call count moves on once every block has read it: each block reads it before it draws its ticket
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            const uint32_t t = atomicAdd(&p.g_state[1], 1u);
+            if (t == gridDim.x * gridDim.y - 1u) {
+                p.g_state[1] = 0u;
+                p.g_state[0] = epoch;
             }
         }
     }
@@ -1511,12 +1515,12 @@ static int launch_stage2(const ommx_decode_args *a, cudaStream_t st, bool after_
     p.o = a->o; p.o_bf16 = (a->o_dtype == OMMX_DT_BF16); p.o_sb = a->o_stride_b; p.o_sh = a->o_stride_h;
     p.lse = a->lse; p.lse_sb = a->lse_stride_b;
     p.sm_scale = a->sm_scale; p.logit_cap = a->logit_cap;
-    p.g_world = 0; p.g_rank = 0; p.g_dst = nullptr; p.g_flags = nullptr; p.g_state = nullptr; p.status = a->status;
+    p.g_world = 0; p.g_rank = 0; p.g_recv = nullptr; p.g_out = nullptr; p.g_state = nullptr; p.status = a->status;
     if (a->gather) {
         const ommx_head_gather *g = a->gather;
-        if (g->world < 2 || g->world > 32 || g->rank < 0 || g->rank >= g->world || !g->dst || !g->flags || !g->state)
-            return fail(OMMX_E_ARG, "head gather: world must be 2..32, rank inside it, and dst / flags / state set");
-        p.g_world = g->world; p.g_rank = g->rank; p.g_dst = g->dst; p.g_flags = g->flags; p.g_state = g->state;
+        if (g->world < 2 || g->world > 32 || g->rank < 0 || g->rank >= g->world || !g->recv || !g->out || !g->state)
+            return fail(OMMX_E_ARG, "head gather: world must be 2..32, rank inside it, and recv / out / state set");
+        p.g_world = g->world; p.g_rank = g->rank; p.g_recv = g->recv; p.g_out = g->out; p.g_state = g->state;
     }
     {
         // Stage 1 runs with the largest shared-memory carve-out; asking for the same split here spares the SMs a

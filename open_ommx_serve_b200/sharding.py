@@ -67,25 +67,17 @@ def gather_head_outputs(o_local: torch.Tensor, world: int, group=None,
     return stacked.permute(1, 0, 2, 3).reshape(B, world * hq, D)
 
 
-class _DeviceView:
-    """A device allocation of the library as something ``torch.as_tensor`` can wrap without a copy."""
-
-    def __init__(self, ptr: int, shape, typestr: str):
-        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
-                                         "version": 2, "strides": None}
-
-
 class _GatherPlan:
-    """One layer's ``ommx_head_gather`` descriptor plus the geometry it was built for."""
+    """One call's ``ommx_head_gather`` descriptor plus the geometry it was built for."""
 
-    def __init__(self, owner, layer):
-        self.owner, self.layer = owner, layer
+    def __init__(self, owner, index):
+        self.owner, self.index = owner, index
 
     def check(self, batch, n_q_heads, head_dim, device):
         o = self.owner
         if (batch, n_q_heads, head_dim) != (o.batch, o.hq_local, o.head_dim) or device != o.device:
             raise ValueError(f"head_gather was built for batch {o.batch} x {o.hq_local} heads x {o.head_dim} on {o.device}")
-        return C.addressof(o._structs[self.layer])
+        return C.addressof(o._structs[self.index])
 
 
 class PeerHeadGather:
@@ -93,11 +85,12 @@ class PeerHeadGather:
 
     Stands where the reference's serving stack runs a collective on the attention output of its tensor-parallel
     ranks (ommx_gpu_serve/integration/vllm/backend.py:859-873 shards the heads; the gather itself is vLLM's).
-    Every rank allocates ``buffers`` output buffers ``[world, batch, Hq/n, D]`` f32 plus flag words in memory the
-    other processes of the node map over NVLink (CUDA IPC); handles travel once through ``torch.distributed``.
-    A decode call given ``head_gather=gather.plan(i)`` leaves all ranks' rows in ``gather.gathered(i)`` when its
-    kernels are done.  Every rank must make the same sequence of such calls, and consecutive calls must use
-    different buffers (layers of a stack do).  NCCL (``gather_head_outputs``) remains the plain alternative.
+    Every rank allocates ``buffers`` receive buffers ``[world, batch, Hq/n, D]`` of 8-byte (value, call count)
+    words in memory the other processes of the node map over NVLink (CUDA IPC); handles travel once through
+    ``torch.distributed``.  A decode call given ``head_gather=gather.plan(i)`` leaves all ranks' rows in
+    ``gather.gathered(i)`` (a plain local f32 tensor) when its kernels are done.  Every rank must make the same
+    sequence of such calls, and consecutive calls must use different buffers (layers of a stack do).  NCCL
+    (``gather_head_outputs``) remains the plain alternative.
     """
 
     def __init__(self, world: int, rank: int, buffers: int, batch: int, hq_local: int, head_dim: int,
@@ -111,19 +104,15 @@ class PeerHeadGather:
         self.world, self.rank, self.buffers = world, rank, buffers
         self.batch, self.hq_local, self.head_dim, self.device = batch, hq_local, head_dim, torch.device(device)
         self._lib = lib = _lib.load()
-        self.buf_floats = world * batch * hq_local * head_dim
-        self.flags_off = (buffers * self.buf_floats * 4 + 255) // 256 * 256
-        self.state_off = self.flags_off + 256
-        self.bytes = self.state_off + 256
+        self.buf_words = world * batch * hq_local * head_dim
+        self.bytes = buffers * self.buf_words * 8
         self._own = C.c_void_p()
         handle = (C.c_uint8 * 64)()
         with torch.cuda.device(self.device):
             _lib.check(lib.ommx_b200_peer_alloc(self.bytes, C.byref(self._own), handle), "ommx_b200_peer_alloc")
-        mine = bytes(handle)
         handles = [None] * world
-        dist.all_gather_object(handles, mine, group=group)
-        self._bases = []
-        self._opened = []
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self._bases, self._opened = [], []
         for r in range(world):
             if r == rank:
                 self._bases.append(int(self._own.value))
@@ -134,23 +123,18 @@ class PeerHeadGather:
                 _lib.check(lib.ommx_b200_peer_open(h, C.byref(ptr)), "ommx_b200_peer_open")
             self._bases.append(int(ptr.value))
             self._opened.append(int(ptr.value))
-        # device-side pointer tables: dst[layer][r], flags[r]
-        dst = torch.tensor([[b + i * self.buf_floats * 4 for b in self._bases] for i in range(buffers)], dtype=torch.int64)
-        flg = torch.tensor([b + self.flags_off for b in self._bases], dtype=torch.int64)
-        self._dst = dst.to(self.device)
-        self._flags = flg.to(self.device)
+        # device-side pointer table recv[buffer][r]; results and the two state words are plain local tensors
+        self._recv = torch.tensor([[b + i * self.buf_words * 8 for b in self._bases] for i in range(buffers)],
+                                  dtype=torch.int64).to(self.device)
+        self._out = torch.zeros(buffers, world, batch, hq_local, head_dim, dtype=torch.float32, device=self.device)
+        self._state = torch.zeros(2, dtype=torch.int32, device=self.device)
         self._structs = (_lib.HeadGather * buffers)()
         for i in range(buffers):
             g = self._structs[i]
             g.world, g.rank = world, rank
-            g.dst = self._dst[i].data_ptr()
-            g.flags = self._flags.data_ptr()
-            g.state = self._bases[rank] + self.state_off
-        self._views = [torch.as_tensor(_DeviceView(self._bases[rank] + i * self.buf_floats * 4,
-                                                   (world, batch, hq_local, head_dim), "<f4"), device=self.device)
-                       for i in range(buffers)]
-        self._all = torch.as_tensor(_DeviceView(self._bases[rank], (buffers, world, batch, hq_local, head_dim), "<f4"),
-                                    device=self.device)
+            g.recv = self._recv[i].data_ptr()
+            g.out = self._out[i].data_ptr()
+            g.state = self._state.data_ptr()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                                 # every rank has mapped every buffer
 
@@ -158,12 +142,12 @@ class PeerHeadGather:
         return _GatherPlan(self, i % self.buffers)
 
     def gathered(self, i: int) -> torch.Tensor:
-        """``[world, batch, Hq/n, D]`` f32 view of buffer ``i``: rank r's heads in slot r."""
-        return self._views[i % self.buffers]
+        """``[world, batch, Hq/n, D]`` f32 result of buffer ``i``: rank r's heads in slot r."""
+        return self._out[i % self.buffers]
 
     def all_buffers(self) -> torch.Tensor:
-        """``[buffers, world, batch, Hq/n, D]`` f32 view of every buffer (they lie back to back)."""
-        return self._all
+        """``[buffers, world, batch, Hq/n, D]`` f32: every buffer's result."""
+        return self._out
 
     def full_heads(self, i: int) -> torch.Tensor:
         """``[batch, Hq, D]`` (rank order = head order), a copy."""
@@ -176,7 +160,6 @@ class PeerHeadGather:
         from . import _lib
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                                 # nobody stores into a buffer that is going away
-        self._views, self._all = [], None
         with torch.cuda.device(self.device):
             for p in self._opened:
                 _lib.check(self._lib.ommx_b200_peer_close(p), "ommx_b200_peer_close")
