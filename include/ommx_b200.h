@@ -176,8 +176,10 @@ typedef struct ommx_decode_args {
     float sm_scale, logit_cap;
     int32_t *status;              /* optional */
     int32_t abl_flags;            /* differential-timing ablations (break parity), 0 in service:
-                                     1 skip outlier splice, 2 skip V/PV, 4 skip K code dequant
-                                     (reference: OMMX_ABL_* knobs, attention/paged_decode.py:3267-3279) */
+                                     1 skip outlier splice, 2 skip V/PV, 4 skip K code dequant, 8 stream only
+                                     (reference: OMMX_ABL_* knobs, attention/paged_decode.py:3267-3279);
+                                     16 is for tests of the give-up path: stage-1 waits last 2 ms and one ring
+                                     fill is announced but not issued, so the call ends with OMMX_ST_TIMEOUT */
     const ommx_head_gather *gather; /* optional: exchange the head outputs with the other ranks in stage 2 */
 } ommx_decode_args;
 

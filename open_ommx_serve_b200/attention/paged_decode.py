@@ -26,7 +26,8 @@ from .pack import planes_struct
 _LAUNCHES = {"stage1": 0, "bitmap": 0, "abl": 0}
 
 ABL_FLAG_NAMES = ("OMMX_ABL_NO_OUTLIER", "OMMX_ABL_V_NODEQUANT", "OMMX_ABL_K_NODEQUANT",
-                  "OMMX_ABL_NO_UNPACK")          # here bit 3 streams the planes and computes nothing
+                  "OMMX_ABL_NO_UNPACK",          # here bit 3 streams the planes and computes nothing
+                  "OMMX_ABL_TEST_STALL")         # tests of the give-up path: short waits, one ring fill announced but not issued
 RECIPE_ALTERING_ENV_PREFIXES = ("OMMX_ABL_", "OMMX_W_ABL_")
 RECIPE_ALTERING_ENV_KEYS = ("OMMX_ATTN_V_BF16", "OMMX_ATTN_FP8_QK")
 

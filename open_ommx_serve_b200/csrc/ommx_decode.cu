@@ -116,11 +116,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // try_wait already parks the warp in hardware for a short while.  The limit is counted on the SM
 // clock (cheap to read); nanosleep or the global timer in this loop would put their own latency
 // on every producer/consumer hand-off.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit = WAIT_LIMIT_CYCLES) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
-    const long long t_end = clock64() + WAIT_LIMIT_CYCLES;
+    const long long t_end = clock64() + limit;
 #pragma unroll 1
     for (uint32_t i = 1;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -188,6 +188,10 @@ __device__ __forceinline__ int64_t load_index(const void *tbl, int is64, int64_t
 // OMMX_ABL_* knobs, paged_decode.py:3267-3279): 1 = skip the outlier splice, 2 = skip V dequant
 // and P.V, 4 = skip the K code dequant and its MMAs.
 constexpr int ABL_NO_OUTLIER = 1, ABL_NO_V = 2, ABL_NO_K = 4, ABL_NO_COMPUTE = 8;   // 8: stream the planes only
+// 16 (tests of the give-up path only): waits give up after about 2 ms and the producer announces the bytes of its
+// second ring fill without issuing the copies, so that every role runs out of patience and leaves through the epilogue
+constexpr int ABL_TEST_STALL = 16;
+constexpr long long TEST_WAIT_LIMIT_CYCLES = 4000000ll;
 
 // fp16 bits of 2^(e + FBIAS).  Exponents below -18 give 0 (such a scale step is under 2^-18 and the
 // term it multiplies is dropped); exponents above 11 are clamped and reported.
@@ -268,6 +272,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     const int H = p.H, GS = p.GS, NS = p.nstages;
     const int n_iters = (ngroups + GS - 1) / GS;
     const int k_out = KOUT >= 0 ? KOUT : p.k_out;
+    const long long wait_limit = (p.abl & ABL_TEST_STALL) ? TEST_WAIT_LIMIT_CYCLES : WAIT_LIMIT_CYCLES;
 
     // ---- shared memory carve-up ----
     uint8_t *s_stage = smem;                                            // nstages * stage_bytes
@@ -370,7 +375,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         for (int it = 0; it < n_iters; ++it) {
             const int s = ring_slot(it, NS);
             const uint32_t ph = ring_phase(it, NS);
-            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1)) {
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, wait_limit)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
             }
@@ -392,7 +397,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 const CopyDesc d = s_desc[c];
                 const int lg = lg0 + (d.gi & 0xFF);
                 const int kind = d.gi >> 8;
-                if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) {
+                if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok && !((p.abl & ABL_TEST_STALL) && it == 1)) {
                     const int64_t idx = s_tab[d.tbase + lg * d.tmul];
                     if (kind == 0) bulk_g2s(sbase + d.dst, d.src + idx * d.unit, d.unit, bar_full + 8 * s);
                     else tma_2d_g2s(sbase + d.dst, kind == 1 ? &p.tmap_k : &p.tmap_v, 0, (int32_t)idx * p.rows_per_page, bar_full + 8 * s);
@@ -453,7 +458,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                     if (gq8) qv1 = make_uint4(pair(8), pair(10), pair(12), pair(14));
                 }
             }
-            if (!mbar_wait(bar_full + 8 * s, ph)) {
+            if (!mbar_wait(bar_full + 8 * s, ph, wait_limit)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 break;
             }
@@ -466,7 +471,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 // for, never an older phase of the same parity.
                 uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
                 const int d0 = 64 * hf + 2 * lane;                   // first of this lane's two channels
-                if (it > 0 && !mbar_wait(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot(it - 1, NS)), ring_phase(it - 1, NS))) {
+                if (it > 0 && !mbar_wait(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot(it - 1, NS)), ring_phase(it - 1, NS), wait_limit)) {
                     if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                     break;
                 }
@@ -747,7 +752,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         const uint32_t ph = ring_phase(it, NS);
         const int lg = it * GS + gsel;                               // local group of this warp
         const bool active = lg < ngroups && !(p.abl & ABL_NO_COMPUTE);
-        if (!mbar_wait(bar_full + 8 * s, ph)) {
+        if (!mbar_wait(bar_full + 8 * s, ph, wait_limit)) {
             if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
             m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
             break;
@@ -766,7 +771,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             }
             // The unit's sidecar tile arrives in two steps: first the factor and zero-point rows, then the outlier
             // deltas.  The code MMAs run on the first, while the decode warps still scatter the deltas.
-            if (!mbar_wait(bar_trows + 8 * unit, consumed & 1u)) {
+            if (!mbar_wait(bar_trows + 8 * unit, consumed & 1u, wait_limit)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                 m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
                 break;
@@ -798,7 +803,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
                 }
             }
             if (has_delta) {
-                if (!mbar_wait(bar_tfull + 8 * unit, consumed & 1u)) {
+                if (!mbar_wait(bar_tfull + 8 * unit, consumed & 1u, wait_limit)) {
                     if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
                     m_run[0] = m_run[1] = -INFINITY; l_run[0] = l_run[1] = 0.f;
                     break;

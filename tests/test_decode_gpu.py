@@ -298,3 +298,25 @@ def test_tensor_core_stage1_agrees_with_default_kernel(monkeypatch):
     monkeypatch.setenv("OMMX_B200_STAGE1", "tc")
     o2, l2 = case.run(num_kv_splits=24)
     assert (o1 - o2).abs().max().item() < 2e-3 and (l1 - l2).abs().max().item() < 2e-3
+
+
+def test_bounded_waits_give_up_and_the_device_stays_usable(monkeypatch):
+    """The give-up path of stage 1: with the test knob the producer announces one ring fill without issuing its
+    copies and every wait has a 2 ms limit, so all three warp roles run out of patience, report it in the status
+    word and leave through the epilogue.  Nothing traps or hangs; the next call on the device is an ordinary one."""
+    from open_ommx_serve_b200 import _lib
+    from open_ommx_serve_b200.attention import paged_decode as pd
+    case = Case([3000], seed=3)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    monkeypatch.setenv("OMMX_ABL_TEST_STALL", "1")
+    o, lse = case.run(num_kv_splits=4, status=status)
+    assert int(status.item()) & _lib.ST_TIMEOUT
+    assert torch.isfinite(o).all()                                   # what is left is the attention over the bf16 rows
+    monkeypatch.delenv("OMMX_ABL_TEST_STALL")
+    assert "OMMX_ABL_TEST_STALL" in pd.abl_flag_names(pd.launch_stats()["abl"])   # a knob that ran is on record
+    pd.reset_launch_stats()
+    status.zero_()
+    o2, lse2 = case.run(num_kv_splits=4, status=status)
+    assert int(status.item()) == 0
+    want_o, want_lse = case.oracle_kernel_arith(num_kv_splits=4, split_pv=True)
+    check_close(o2, want_o, ctx="after a timed-out call")
