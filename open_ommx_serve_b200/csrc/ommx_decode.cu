@@ -273,6 +273,32 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     const int n_iters = (ngroups + GS - 1) / GS;
     const int k_out = KOUT >= 0 ? KOUT : p.k_out;
     const long long wait_limit = (p.abl & ABL_TEST_STALL) ? TEST_WAIT_LIMIT_CYCLES : WAIT_LIMIT_CYCLES;
+    // The MMA warps' query words (bf16 pairs) are requested now and turned into operand fragments after the prologue,
+    // which hides their round trip behind the table loads: q_s = this lane's 32 consecutive channels (code MMAs),
+    // q_d = the channel pairs of the delta MMAs' fragments.  Column n = lane / 4 of every MMA is query head n.
+    uint32_t q_s[16], q_d[16];
+    if (warp < NCW) {
+        const int hq_ = (warp & (H - 1)) * p.gqa + ((lane >> 2) < p.gqa ? (lane >> 2) : 0), j_ = lane & 3;
+        const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)hq_ * p.q_sh;
+        if (p.q_vec_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 t = __ldg(reinterpret_cast<const uint4 *>(qrow + 32 * j_) + v);
+                q_s[4 * v] = t.x; q_s[4 * v + 1] = t.y; q_s[4 * v + 2] = t.z; q_s[4 * v + 3] = t.w;
+            }
+#pragma unroll
+            for (int r = 0; r < 16; ++r) q_d[r] = __ldg(reinterpret_cast<const uint32_t *>(qrow + 16 * (r >> 1) + 8 * (r & 1) + 2 * j_));
+        } else {
+            const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qrow);
+#pragma unroll
+            for (int v = 0; v < 16; ++v) q_s[v] = (uint32_t)__ldg(q16 + 32 * j_ + 2 * v) | ((uint32_t)__ldg(q16 + 32 * j_ + 2 * v + 1) << 16);
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const int c = 16 * (r >> 1) + 8 * (r & 1) + 2 * j_;
+                q_d[r] = (uint32_t)__ldg(q16 + c) | ((uint32_t)__ldg(q16 + c + 1) << 16);
+            }
+        }
+    }
 
     // ---- shared memory carve-up ----
     uint8_t *s_stage = smem;                                            // nstages * stage_bytes
@@ -294,18 +320,21 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         const float mag = mi == 0 ? 0.f : (mi == 1 ? .5f : (float)(2 + (mi & 1)) * (float)(1 << (mi >> 1)) * 0.25f);
         s_lut[c] = (c & 8) ? -mag : mag;
     }
-    if (threadIdx.x == 32) {
-        for (int s = 0; s < MAX_STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 3 * NCW);                  // 8 MMA warps + 16 tile halves
+    {
+        // one barrier per thread (56 of them: a single thread's serial inits were a microsecond of every launch)
+        const int t = (int)threadIdx.x - 32;
+        constexpr int NB_RING = 2 * MAX_STAGES, NB_ALL = NB_RING + (2 + MAX_STAGES) * NCW;
+        if (t >= 0 && t < NB_ALL) {
+            uint32_t count;
+            if (t < MAX_STAGES) count = 1;                                     // full[]
+            else if (t < NB_RING) count = 3 * NCW;                             // empty[]: 8 MMA warps + 16 tile halves
+            else if (t < NB_RING + NCW) count = 2;                             // tile_full[]: the two halves' deltas scattered
+            else if (t < NB_RING + NCW + MAX_STAGES * NCW) count = 1;          // tile_empty[][]
+            else count = 2;                                                    // tile_rows[]: the two halves' rows written
+            mbar_init(bar_full + 8 * t, count);
+            if (t == 0) *s_abort = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
-        for (int u = 0; u < NCW; ++u) {
-            mbar_init(bar_tfull + 8 * u, 2);                        // the two halves of a tile: outlier deltas scattered
-            mbar_init(bar_trows + 8 * u, 2);                        // the two halves of a tile: factor / zero-point rows written
-            for (int k2 = 0; k2 < MAX_STAGES; ++k2) mbar_init(bar_tempty + 8 * (MAX_STAGES * u + k2), 1);
-        }
-        *s_abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     const int cpg = 4 * p.ppg + 6;                                      // copies per group
     const int ncopies = GS * cpg;
@@ -364,315 +393,338 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     // grid to finish before it reads the split partials.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // ---- roles; each branch starts by resizing its warpgroups' register budget and never rejoins ----
-    if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
-    if (warp == PRODUCER_WARP) {
-        // =========================== producer warp ===========================
-        uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
-        for (int c = lane; c < ncopies; c += 32) full_total += s_desc[c].unit;
-        full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
-        const int whole_groups = ntok / 32;
-        for (int it = 0; it < n_iters; ++it) {
-            const int s = ring_slot(it, NS);
-            const uint32_t ph = ring_phase(it, NS);
-            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, wait_limit)) {
-                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
-                break;
-            }
-            const int lg0 = it * GS;
-            uint32_t total = full_total;
-            if (lg0 + GS > whole_groups) {                              // last stage: fewer groups or a partial group
-                uint32_t mine = 0;
-                for (int c = lane; c < ncopies; c += 32) {
-                    const CopyDesc d = s_desc[c];
-                    const int lg = lg0 + (d.gi & 0xFF);
-                    if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) mine += d.unit;
-                }
-                total = __reduce_add_sync(0xFFFFFFFFu, mine);
-            }
-            if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
-            __syncwarp();
-            const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
-            for (int c = lane; c < ncopies; c += 32) {
-                const CopyDesc d = s_desc[c];
-                const int lg = lg0 + (d.gi & 0xFF);
-                const int kind = d.gi >> 8;
-                if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok && !((p.abl & ABL_TEST_STALL) && it == 1)) {
-                    const int64_t idx = s_tab[d.tbase + lg * d.tmul];
-                    if (kind == 0) bulk_g2s(sbase + d.dst, d.src + idx * d.unit, d.unit, bar_full + 8 * s);
-                    else tma_2d_g2s(sbase + d.dst, kind == 1 ? &p.tmap_k : &p.tmap_v, 0, (int32_t)idx * p.rows_per_page, bar_full + 8 * s);
-                }
-            }
-        }
-        // fall through to the two CTA-wide barriers of the epilogue
-        __syncthreads();
-        __syncthreads();
-        return;
-    }
-
-    // =========================== decode + MMA warps ===========================
-    // MMA warp w owns unit w = (group-in-stage, kv head) and its softmax state.  The decode warps are
-    // stateless: work item (iteration, unit) number n goes to decode warp n % NDW.
     const int g = lane >> 2, j = lane & 3;
     const int TS = H * 32;                                          // bytes per token row (all heads)
     const float LOG2E = 1.4426950408889634f;
     const bool no_outlier = (p.abl & ABL_NO_OUTLIER) != 0;
+    const int n_items = n_iters * NCW * 2;                          // (iteration, unit, tile half) work items of the decode role
 
-    if (warp >= NCW) {
-        // =========================== decode warps ===========================
-        // Build the sidecar tile of a unit between two uses by its MMA warp.  A tile is built in two
-        // halves by two warps at once, because the MMA warp of the unit waits for it: half hf takes K
-        // channels 64hf..64hf+63 (lane l: channels 64hf + 2l, +1 - delta columns, zero-points, scale
-        // factors) and V tokens 16hf..16hf+15 (lane l: token 16hf + l%16, scale groups 2(l/16), +1).
-        const int dw = warp - NCW;
-        if (dw < NCW) {           // the first to touch tile dw clears it once (unused rows stay zero)
-            uint8_t *t0p = s_tiles + dw * DT_BYTES;
-            for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(t0p)[i] = 0u;
+    // ---- one stage of the ring: announce its bytes, issue its copies (producer warp) ----
+    uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
+    const int whole_groups = ntok / 32;
+    auto issue_stage = [&](int it) __attribute__((always_inline)) {
+        const int s = ring_slot(it, NS);
+        const int lg0 = it * GS;
+        uint32_t total = full_total;
+        if (lg0 + GS > whole_groups) {                              // last stage: fewer groups or a partial group
+            uint32_t mine = 0;
+            for (int c = lane; c < ncopies; c += 32) {
+                const CopyDesc d = s_desc[c];
+                const int lg = lg0 + (d.gi & 0xFF);
+                if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) mine += d.unit;
+            }
+            total = __reduce_add_sync(0xFFFFFFFFu, mine);
         }
-        // every tile is cleared before any half of it is written (only decode warps take part)
-        asm volatile("bar.sync 1, %0;" ::"n"(NDW * 32) : "memory");
-        for (int n = dw; n < n_iters * NCW * 2; n += NDW) {
-            const int it = n / (2 * NCW), unit = (n >> 1) % NCW, hf = n & 1;
-            const int trk = 8 * ((n - dw) / NDW);
-            (void)trk;
-            const int h = unit & (H - 1), gsel = unit >> p.hshift;       // H is a power of two
-            uint8_t *tile = s_tiles + unit * DT_BYTES;
-            const int s = ring_slot(it, NS);
-            const uint32_t ph = ring_phase(it, NS);
-            // The fp32 q.zp sums of this half's 64 channels: lane = (query head of the kv head, block of 8 or 16
-            // channels).  The lane's raw query values are requested before the waits below, so that the loads are
-            // in flight meanwhile.
-            const bool gq8 = p.gqa > 4;                               // 8 heads x 4 blocks of 16, else 4 heads x 8 blocks of 8
-            const int zq_head = gq8 ? lane >> 2 : lane >> 3, zq_blk = gq8 ? lane & 3 : lane & 7;
-            const int zq_c0 = 64 * hf + zq_blk * (gq8 ? 16 : 8);
-            uint4 qv0 = make_uint4(0u, 0u, 0u, 0u), qv1 = make_uint4(0u, 0u, 0u, 0u);
-            if (zq_head < p.gqa) {
-                const __nv_bfloat16 *qp = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + zq_head) * p.q_sh + zq_c0;
-                if (p.q_vec_ok) {
-                    qv0 = __ldg(reinterpret_cast<const uint4 *>(qp));
-                    if (gq8) qv1 = __ldg(reinterpret_cast<const uint4 *>(qp) + 1);
-                } else {
-                    const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qp);
-                    auto pair = [&](int i) { return (uint32_t)__ldg(q16 + i) | ((uint32_t)__ldg(q16 + i + 1) << 16); };
-                    qv0 = make_uint4(pair(0), pair(2), pair(4), pair(6));
-                    if (gq8) qv1 = make_uint4(pair(8), pair(10), pair(12), pair(14));
-                }
+        if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
+        __syncwarp();
+        const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
+        for (int c = lane; c < ncopies; c += 32) {
+            const CopyDesc d = s_desc[c];
+            const int lg = lg0 + (d.gi & 0xFF);
+            const int kind = d.gi >> 8;
+            if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok && !((p.abl & ABL_TEST_STALL) && it == 1)) {
+                const int64_t idx = s_tab[d.tbase + lg * d.tmul];
+                if (kind == 0) bulk_g2s(sbase + d.dst, d.src + idx * d.unit, d.unit, bar_full + 8 * s);
+                else tma_2d_g2s(sbase + d.dst, kind == 1 ? &p.tmap_k : &p.tmap_v, 0, (int32_t)idx * p.rows_per_page, bar_full + 8 * s);
             }
-            if (!mbar_wait(bar_full + 8 * s, ph, wait_limit)) {
+        }
+    };
+    // The first ring fill is on every CTA's critical path: it goes out before the register budgets are resized.
+    if (warp == PRODUCER_WARP) {
+        for (int c = lane; c < ncopies; c += 32) full_total += s_desc[c].unit;
+        full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
+        issue_stage(0);
+    }
+
+    // ---- one work item of the decode role: half hf of the sidecar tile of (iteration it, unit) ----
+    // Build the sidecar tile of a unit between two uses by its MMA warp.  A tile is built in two
+    // halves by two warps at once, because the MMA warp of the unit waits for it: half hf takes K
+    // channels 64hf..64hf+63 (lane l: channels 64hf + 2l, +1 - delta columns, zero-points, scale
+    // factors) and V tokens 16hf..16hf+15 (lane l: token 16hf + l%16, scale groups 2(l/16), +1).
+    // Returns false when a bounded wait ran out.
+    auto decode_item = [&](const int n) __attribute__((always_inline)) -> bool {
+        const int it = n / (2 * NCW), unit = (n >> 1) % NCW, hf = n & 1;
+        const int h = unit & (H - 1), gsel = unit >> p.hshift;       // H is a power of two
+        uint8_t *tile = s_tiles + unit * DT_BYTES;
+        const int s = ring_slot(it, NS);
+        const uint32_t ph = ring_phase(it, NS);
+        // The fp32 q.zp sums of this half's 64 channels: lane = (query head of the kv head, block of 8 or 16
+        // channels).  The lane's raw query values are requested before the waits below, so that the loads are
+        // in flight meanwhile.
+        const bool gq8 = p.gqa > 4;                               // 8 heads x 4 blocks of 16, else 4 heads x 8 blocks of 8
+        const int zq_head = gq8 ? lane >> 2 : lane >> 3, zq_blk = gq8 ? lane & 3 : lane & 7;
+        const int zq_c0 = 64 * hf + zq_blk * (gq8 ? 16 : 8);
+        uint4 qv0 = make_uint4(0u, 0u, 0u, 0u), qv1 = make_uint4(0u, 0u, 0u, 0u);
+        if (zq_head < p.gqa) {
+            const __nv_bfloat16 *qp = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + zq_head) * p.q_sh + zq_c0;
+            if (p.q_vec_ok) {
+                qv0 = __ldg(reinterpret_cast<const uint4 *>(qp));
+                if (gq8) qv1 = __ldg(reinterpret_cast<const uint4 *>(qp) + 1);
+            } else {
+                const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qp);
+                auto pair = [&](int i) { return (uint32_t)__ldg(q16 + i) | ((uint32_t)__ldg(q16 + i + 1) << 16); };
+                qv0 = make_uint4(pair(0), pair(2), pair(4), pair(6));
+                if (gq8) qv1 = make_uint4(pair(8), pair(10), pair(12), pair(14));
+            }
+        }
+        if (!mbar_wait(bar_full + 8 * s, ph, wait_limit)) {
+            if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+            return false;
+        }
+        const int lg = it * GS + gsel;                           // local group of this unit
+        if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
+            // Tile `it` of a unit may be written once the MMA warp has read tile it-1.  Decode warps
+            // run up to NS groups ahead and the tiles of one unit are built by different warps, so
+            // "tile k was read" events rotate over NS barriers per unit (barrier k % NS, phase
+            // k / NS): the newest event a waiter can be missing is then always the one it waits
+            // for, never an older phase of the same parity.
+            uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
+            const int d0 = 64 * hf + 2 * lane;                   // first of this lane's two channels
+            if (it > 0 && !mbar_wait(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot(it - 1, NS)), ring_phase(it - 1, NS), wait_limit)) {
                 if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
-                break;
+                return false;
             }
-            const int lg = it * GS + gsel;                           // local group of this unit
-            if (lg < ngroups && !(p.abl & ABL_NO_COMPUTE)) {
-                // Tile `it` of a unit may be written once the MMA warp has read tile it-1.  Decode warps
-                // run up to NS groups ahead and the tiles of one unit are built by different warps, so
-                // "tile k was read" events rotate over NS barriers per unit (barrier k % NS, phase
-                // k / NS): the newest event a waiter can be missing is then always the one it waits
-                // for, never an older phase of the same parity.
-                uint8_t *gb = s_stage + (size_t)s * p.stage_bytes + (size_t)gsel * p.gb_bytes;
-                const int d0 = 64 * hf + 2 * lane;                   // first of this lane's two channels
-                if (it > 0 && !mbar_wait(bar_tempty + 8 * (MAX_STAGES * unit + ring_slot(it - 1, NS)), ring_phase(it - 1, NS), wait_limit)) {
-                    if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
-                    break;
+            bool clamped_any = false;
+            const bool splice = k_out > 0 && !no_outlier;
+            // ---- first the rows the code MMAs and the softmax read (K factors, q.zp sums, V factors and
+            //      zero-points): they are cheap, and the MMA warp starts on them while the deltas are scattered ----
+            const uint32_t e2 = *reinterpret_cast<const uint16_t *>(gb + p.o_ks + h * 128 + d0);
+            const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
+            // this lane's entry in the fragment-ordered K factor row
+            const uint32_t kf_off = ROW_KF * DT_STRIDE + 64u * (2 * hf + (lane >> 4)) + 32u * ((lane >> 3) & 1) + 8u * (lane & 3) + 2u * ((lane >> 2) & 1);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int e = max((int)(int8_t)(e2 >> (8 * c)), -126);
+                bool cl;
+                const uint32_t fb = pow2_f16_bits(e, cl);
+                clamped_any |= cl;
+                *reinterpret_cast<uint16_t *>(tile + kf_off + 4 * c) = (uint16_t)fb;
+            }
+            {   // q.zp in fp32 from the raw bf16 query, as the reference forms it: 8 (16) products per lane, then the
+                // lanes of a head are summed by 3 (2) exchanges
+                auto dot4 = [](const uint4 &q, const uint4 &z, float acc) {
+                    const uint32_t qw[4] = {q.x, q.y, q.z, q.w}, zw[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc = fmaf(__uint_as_float(qw[i] << 16), __uint_as_float(zw[i] << 16), acc);
+                        acc = fmaf(__uint_as_float(qw[i] & 0xFFFF0000u), __uint_as_float(zw[i] & 0xFFFF0000u), acc);
+                    }
+                    return acc;
+                };
+                const uint8_t *zrow = gb + p.o_kz + h * 256 + 2 * zq_c0;
+                float sum = dot4(qv0, *reinterpret_cast<const uint4 *>(zrow), 0.f);
+                if (gq8) sum = dot4(qv1, *reinterpret_cast<const uint4 *>(zrow + 16), sum);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+                if (!gq8) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+                if (zq_blk == 0) reinterpret_cast<float *>(tile + ROW_ZP * DT_STRIDE)[8 * hf + zq_head] = sum;   // heads past gqa: 0
+            }
+            {   // V side: one token, two scale groups: power-of-two factor and zero-point of each
+                const int copy = it & 1;
+                const int tk = 16 * hf + (lane & 15), cg0 = 2 * (lane >> 4);
+                uint32_t ve = 0x8080u;                               // exponent -128 -> factor 0
+                uint32_t vz2 = 0u;
+                if (32 * lg + tk < ntok) {
+                    ve = *reinterpret_cast<const uint16_t *>(gb + p.o_vs + (tk * H + h) * 4 + cg0);
+                    vz2 = *reinterpret_cast<const uint32_t *>(gb + p.o_vz + (tk * H + h) * 8 + 2 * cg0);
                 }
-                bool clamped_any = false;
-                const bool splice = k_out > 0 && !no_outlier;
-                // ---- first the rows the code MMAs and the softmax read (K factors, q.zp sums, V factors and
-                //      zero-points): they are cheap, and the MMA warp starts on them while the deltas are scattered ----
-                const uint32_t e2 = *reinterpret_cast<const uint16_t *>(gb + p.o_ks + h * 128 + d0);
-                const uint32_t z2 = *reinterpret_cast<const uint32_t *>(gb + p.o_kz + h * 256 + 2 * d0);
-                // this lane's entry in the fragment-ordered K factor row
-                const uint32_t kf_off = ROW_KF * DT_STRIDE + 64u * (2 * hf + (lane >> 4)) + 32u * ((lane >> 3) & 1) + 8u * (lane & 3) + 2u * ((lane >> 2) & 1);
+                uint8_t *vfr = tile + (ROW_VF + copy) * DT_STRIDE + 64 * ((tk >> 1) & 3) + 8 * hf + 4 * ((tk >> 3) & 1) + 2 * (tk & 1) + 16 * cg0;
+                uint8_t *ztr = tile + (ROW_ZT + copy) * DT_STRIDE + 2 * tk + 64 * cg0;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    bool cl;
+                    const uint32_t fb = pow2_f16_bits((int)(int8_t)(ve >> (8 * c)), cl);
+                    clamped_any |= cl;
+                    *reinterpret_cast<uint16_t *>(vfr + 16 * c) = (uint16_t)fb;
+                    const float vz = bf16_bits_to_f32(c ? (vz2 >> 16) : (vz2 & 0xFFFFu));
+                    *reinterpret_cast<uint16_t *>(ztr + 64 * c) = (uint16_t)f16_bits_sat(vz);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_trows + 8 * unit);
+            // ---- then the outlier deltas of this half's columns ----
+            if (splice) {
+                // clear this half's columns of token rows 0..31 (128 bytes per row)
+#pragma unroll
+                for (int k2 = 0; k2 < 8; ++k2)
+                    *reinterpret_cast<uint4 *>(tile + (4 * k2 + (lane >> 3)) * DT_STRIDE + 128 * hf + 16 * (lane & 7)) = make_uint4(0, 0, 0, 0);
+                uint32_t ms2 = 0, mc2 = 0;
+                if (p.use_map) {
+                    ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
+                    mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
+                }
+                uint2 bm2;
+                if (!p.idx7) {
+                    bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
+                } else {
+                    // relidx7 (attention/codec.py:91-130 of the reference): k ascending token positions, 7 bits each,
+                    // LSB first; the outlier set as a bitmask again, the value stream is shared with that encoding
+                    uint32_t m2[2];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const uint8_t *ip = gb + p.o_bm + (h * 128 + d0 + c) * p.nbi;
+                        uint32_t w[5] = {0u, 0u, 0u, 0u, 0u};
+                        for (int i = 0; i < p.nbi; ++i) w[i >> 2] |= (uint32_t)ip[i] << (8 * (i & 3));
+                        uint32_t bits = 0u;
+                        for (int r = 0; r < k_out; ++r) {
+                            const int bp = 7 * r;
+                            const uint32_t f = __funnelshift_r(w[bp >> 5], w[(bp >> 5) + 1], bp & 31) & 0x7Fu;
+                            if (f > 31u) or_status(p.status, OMMX_ST_BAD_GROUP);
+                            else bits |= 1u << f;
+                        }
+                        m2[c] = bits;
+                    }
+                    bm2 = make_uint2(m2[0], m2[1]);
+                }
+                uint32_t st[2] = {0, 0}, sth[2] = {0, 0};            // nibble stream of each channel: outliers 0..7, 8..15
+                const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
+                const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nb;          // 2*nb bytes, 2-byte aligned
+                if (nb == 3) {
+                    const uint32_t w0 = reinterpret_cast<const uint16_t *>(ov)[0], w1 = reinterpret_cast<const uint16_t *>(ov)[1],
+                                   w2 = reinterpret_cast<const uint16_t *>(ov)[2];
+                    st[0] = w0 | ((w1 & 0xFFu) << 16);
+                    st[1] = (w1 >> 8) | (w2 << 8);
+                } else if (nb == 4) {
+                    const uint2 w = *reinterpret_cast<const uint2 *>(ov);
+                    st[0] = w.x; st[1] = w.y;
+                } else if (nb == 2) {
+                    const uint32_t w = *reinterpret_cast<const uint32_t *>(ov);
+                    st[0] = w & 0xFFFFu; st[1] = w >> 16;
+                } else if (nb > 4) {
+                    // 9..16 outliers: the two channels' streams are 2*nb bytes back to back; read them as
+                    // 16-bit pieces into a 128-bit little-endian window and cut it at bit 8*nb
+                    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (i < nb) w[i >> 1] |= (uint32_t) reinterpret_cast<const uint16_t *>(ov)[i] << (16 * (i & 1));
+                    const int sh = nb > 4 ? 8 * (nb - 4) : 8;        // 8..32 bits of a stream lie above its first word
+                    const uint32_t hmask = sh == 32 ? 0xFFFFFFFFu : ((1u << sh) - 1u);
+                    st[0] = w[0]; sth[0] = w[1] & hmask;
+                    if (sh == 32) { st[1] = w[2]; sth[1] = w[3]; }
+                    else { st[1] = __funnelshift_r(w[1], w[2], sh); sth[1] = __funnelshift_r(w[2], w[3], sh) & hmask; }
+                } else {
+                    const uint32_t w = *reinterpret_cast<const uint16_t *>(ov);
+                    st[0] = w & 0xFFu; st[1] = w >> 8;
+                }
+                __syncwarp();                                        // the cleared rows before any delta lands in them
+                const uint32_t bmv[2] = {bm2.x, bm2.y};
+                // The code byte holding this lane's channels, row pz: byte pz*TS + h*32 + d0/4 of the (1 KB aligned)
+                // k_base block, with the 16-byte chunk bits XOR-ed by the row's swizzle term.  h*32 + d0/4 splits
+                // into a part above bit 7 (added to the row) and a part below (the XOR operand).
+                const uint32_t k_hi_rel = (uint32_t)(h >> 2) * 128u;
+                const uint8_t *k_hi = gb + k_hi_rel;
+                const uint32_t k_lo = (uint32_t)((h & 3) * 32 + (d0 >> 2));
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int e = max((int)(int8_t)(e2 >> (8 * c)), -126);
-                    bool cl;
-                    const uint32_t fb = pow2_f16_bits(e, cl);
-                    clamped_any |= cl;
-                    *reinterpret_cast<uint16_t *>(tile + kf_off + 4 * c) = (uint16_t)fb;
-                }
-                {   // q.zp in fp32 from the raw bf16 query, as the reference forms it: 8 (16) products per lane, then the
-                    // lanes of a head are summed by 3 (2) exchanges
-                    auto dot4 = [](const uint4 &q, const uint4 &z, float acc) {
-                        const uint32_t qw[4] = {q.x, q.y, q.z, q.w}, zw[4] = {z.x, z.y, z.z, z.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            acc = fmaf(__uint_as_float(qw[i] << 16), __uint_as_float(zw[i] << 16), acc);
-                            acc = fmaf(__uint_as_float(qw[i] & 0xFFFF0000u), __uint_as_float(zw[i] & 0xFFFF0000u), acc);
-                        }
-                        return acc;
-                    };
-                    const uint8_t *zrow = gb + p.o_kz + h * 256 + 2 * zq_c0;
-                    float sum = dot4(qv0, *reinterpret_cast<const uint4 *>(zrow), 0.f);
-                    if (gq8) sum = dot4(qv1, *reinterpret_cast<const uint4 *>(zrow + 16), sum);
-                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-                    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-                    if (!gq8) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
-                    if (zq_blk == 0) reinterpret_cast<float *>(tile + ROW_ZP * DT_STRIDE)[8 * hf + zq_head] = sum;   // heads past gqa: 0
-                }
-                {   // V side: one token, two scale groups: power-of-two factor and zero-point of each
-                    const int copy = it & 1;
-                    const int tk = 16 * hf + (lane & 15), cg0 = 2 * (lane >> 4);
-                    uint32_t ve = 0x8080u;                               // exponent -128 -> factor 0
-                    uint32_t vz2 = 0u;
-                    if (32 * lg + tk < ntok) {
-                        ve = *reinterpret_cast<const uint16_t *>(gb + p.o_vs + (tk * H + h) * 4 + cg0);
-                        vz2 = *reinterpret_cast<const uint32_t *>(gb + p.o_vz + (tk * H + h) * 8 + 2 * cg0);
-                    }
-                    uint8_t *vfr = tile + (ROW_VF + copy) * DT_STRIDE + 64 * ((tk >> 1) & 3) + 8 * hf + 4 * ((tk >> 3) & 1) + 2 * (tk & 1) + 16 * cg0;
-                    uint8_t *ztr = tile + (ROW_ZT + copy) * DT_STRIDE + 2 * tk + 64 * cg0;
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        bool cl;
-                        const uint32_t fb = pow2_f16_bits((int)(int8_t)(ve >> (8 * c)), cl);
-                        clamped_any |= cl;
-                        *reinterpret_cast<uint16_t *>(vfr + 16 * c) = (uint16_t)fb;
-                        const float vz = bf16_bits_to_f32(c ? (vz2 >> 16) : (vz2 & 0xFFFFu));
-                        *reinterpret_cast<uint16_t *>(ztr + 64 * c) = (uint16_t)f16_bits_sat(vz);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_trows + 8 * unit);
-                // ---- then the outlier deltas of this half's columns ----
-                if (splice) {
-                    // clear this half's columns of token rows 0..31 (128 bytes per row)
-#pragma unroll
-                    for (int k2 = 0; k2 < 8; ++k2)
-                        *reinterpret_cast<uint4 *>(tile + (4 * k2 + (lane >> 3)) * DT_STRIDE + 128 * hf + 16 * (lane & 7)) = make_uint4(0, 0, 0, 0);
-                    uint32_t ms2 = 0, mc2 = 0;
+                    const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
+                    const float zp = bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu));
+                    // delta between the outlier value and the base value it replaces, rounded once
+                    float A = sc, Bc = 0.f;                     // shared map: lvl*s + zp - (code*s + zp)
                     if (p.use_map) {
-                        ms2 = *reinterpret_cast<const uint32_t *>(gb + p.o_ms + h * 256 + 2 * d0);
-                        mc2 = *reinterpret_cast<const uint32_t *>(gb + p.o_mc + h * 256 + 2 * d0);
+                        const float ms = bf16_bits_to_f32(c ? (ms2 >> 16) : (ms2 & 0xFFFFu));
+                        const float mc = bf16_bits_to_f32(c ? (mc2 >> 16) : (mc2 & 0xFFFFu));
+                        A = __fdividef(1.f, ms);
+                        Bc = mc - zp;
                     }
-                    uint2 bm2;
-                    if (!p.idx7) {
-                        bm2 = *reinterpret_cast<const uint2 *>(gb + p.o_bm + h * 512 + 4 * d0);
-                    } else {
-                        // relidx7 (attention/codec.py:91-130 of the reference): k ascending token positions, 7 bits each,
-                        // LSB first; the outlier set as a bitmask again, the value stream is shared with that encoding
-                        uint32_t m2[2];
+                    uint32_t bits = bmv[c];
+                    const uint32_t stream = st[c], stream_hi = sth[c];
+                    (void)stream_hi;
+                    const int fsh = 2 * ((d0 & 3) + c);          // bit position of the channel's code in its byte
+                    uint8_t *col = tile + 2 * d0 + 2 * c;
+                    if (KOUT > 0) {
+                        if (__popc(bits) == KOUT) {
+                            // Two passes: all gathers (base-code byte, FP4 level) first, then the arithmetic and the
+                            // stores.  In one pass every load would have to follow the previous outlier's store in
+                            // program order (shared memory may alias), i.e. KOUT load round trips in a row.
+                            constexpr int KO = KOUT > 0 ? KOUT : 1;
+                            uint32_t pzs[KO], cbs[KO];
+                            float lvs[KO];
 #pragma unroll
-                        for (int c = 0; c < 2; ++c) {
-                            const uint8_t *ip = gb + p.o_bm + (h * 128 + d0 + c) * p.nbi;
-                            uint32_t w[5] = {0u, 0u, 0u, 0u, 0u};
-                            for (int i = 0; i < p.nbi; ++i) w[i >> 2] |= (uint32_t)ip[i] << (8 * (i & 3));
-                            uint32_t bits = 0u;
-                            for (int r = 0; r < k_out; ++r) {
-                                const int bp = 7 * r;
-                                const uint32_t f = __funnelshift_r(w[bp >> 5], w[(bp >> 5) + 1], bp & 31) & 0x7Fu;
-                                if (f > 31u) or_status(p.status, OMMX_ST_BAD_GROUP);
-                                else bits |= 1u << f;
-                            }
-                            m2[c] = bits;
-                        }
-                        bm2 = make_uint2(m2[0], m2[1]);
-                    }
-                    uint32_t st[2] = {0, 0}, sth[2] = {0, 0};            // nibble stream of each channel: outliers 0..7, 8..15
-                    const int nb = KOUT >= 0 ? (KOUT + 1) / 2 : p.nb;
-                    const uint8_t *ov = gb + p.o_ov + (h * 128 + d0) * nb;          // 2*nb bytes, 2-byte aligned
-                    if (nb == 3) {
-                        const uint32_t w0 = reinterpret_cast<const uint16_t *>(ov)[0], w1 = reinterpret_cast<const uint16_t *>(ov)[1],
-                                       w2 = reinterpret_cast<const uint16_t *>(ov)[2];
-                        st[0] = w0 | ((w1 & 0xFFu) << 16);
-                        st[1] = (w1 >> 8) | (w2 << 8);
-                    } else if (nb == 4) {
-                        const uint2 w = *reinterpret_cast<const uint2 *>(ov);
-                        st[0] = w.x; st[1] = w.y;
-                    } else if (nb == 2) {
-                        const uint32_t w = *reinterpret_cast<const uint32_t *>(ov);
-                        st[0] = w & 0xFFFFu; st[1] = w >> 16;
-                    } else if (nb > 4) {
-                        // 9..16 outliers: the two channels' streams are 2*nb bytes back to back; read them as
-                        // 16-bit pieces into a 128-bit little-endian window and cut it at bit 8*nb
-                        uint32_t w[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            if (i < nb) w[i >> 1] |= (uint32_t) reinterpret_cast<const uint16_t *>(ov)[i] << (16 * (i & 1));
-                        const int sh = nb > 4 ? 8 * (nb - 4) : 8;        // 8..32 bits of a stream lie above its first word
-                        const uint32_t hmask = sh == 32 ? 0xFFFFFFFFu : ((1u << sh) - 1u);
-                        st[0] = w[0]; sth[0] = w[1] & hmask;
-                        if (sh == 32) { st[1] = w[2]; sth[1] = w[3]; }
-                        else { st[1] = __funnelshift_r(w[1], w[2], sh); sth[1] = __funnelshift_r(w[2], w[3], sh) & hmask; }
-                    } else {
-                        const uint32_t w = *reinterpret_cast<const uint16_t *>(ov);
-                        st[0] = w & 0xFFu; st[1] = w >> 8;
-                    }
-                    __syncwarp();                                        // the cleared rows before any delta lands in them
-                    const uint32_t bmv[2] = {bm2.x, bm2.y};
-                    // The code byte holding this lane's channels, row pz: byte pz*TS + h*32 + d0/4 of the (1 KB aligned)
-                    // k_base block, with the 16-byte chunk bits XOR-ed by the row's swizzle term.  h*32 + d0/4 splits
-                    // into a part above bit 7 (added to the row) and a part below (the XOR operand).
-                    const uint32_t k_hi_rel = (uint32_t)(h >> 2) * 128u;
-                    const uint8_t *k_hi = gb + k_hi_rel;
-                    const uint32_t k_lo = (uint32_t)((h & 3) * 32 + (d0 >> 2));
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const int e = max((int)(int8_t)(e2 >> (8 * c)), -126);
-                        const float sc = __uint_as_float((uint32_t)(e + 127) << 23);
-                        const float zp = bf16_bits_to_f32(c ? (z2 >> 16) : (z2 & 0xFFFFu));
-                        // delta between the outlier value and the base value it replaces, rounded once
-                        float A = sc, Bc = 0.f;                     // shared map: lvl*s + zp - (code*s + zp)
-                        if (p.use_map) {
-                            const float ms = bf16_bits_to_f32(c ? (ms2 >> 16) : (ms2 & 0xFFFFu));
-                            const float mc = bf16_bits_to_f32(c ? (mc2 >> 16) : (mc2 & 0xFFFFu));
-                            A = __fdividef(1.f, ms);
-                            Bc = mc - zp;
-                        }
-                        uint32_t bits = bmv[c];
-                        const uint32_t stream = st[c], stream_hi = sth[c];
-                        (void)stream_hi;
-                        const int fsh = 2 * ((d0 & 3) + c);          // bit position of the channel's code in its byte
-                        uint8_t *col = tile + 2 * d0 + 2 * c;
-                        if (KOUT > 0) {
-                            if (__popc(bits) == KOUT) {
-                                // Two passes: all gathers (base-code byte, FP4 level) first, then the arithmetic and the
-                                // stores.  In one pass every load would have to follow the previous outlier's store in
-                                // program order (shared memory may alias), i.e. KOUT load round trips in a row.
-                                constexpr int KO = KOUT > 0 ? KOUT : 1;
-                                uint32_t pzs[KO], cbs[KO];
-                                float lvs[KO];
-#pragma unroll
-                                for (int r = KO - 1; r >= 0; --r) {
-                                    const int pz = 31 - __clz(bits);
-                                    bits ^= 1u << pz;
-                                    pzs[r] = (uint32_t)pz;
-                                    lvs[r] = s_lut[((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu];
-                                    const uint32_t row = (uint32_t)pz * (uint32_t)TS;
-                                    cbs[r] = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
-                                }
-#pragma unroll
-                                for (int r = KO - 1; r >= 0; --r) {
-                                    const float cf = (float)((cbs[r] >> fsh) & 3u);
-                                    const float X = fmaf(cf, -sc, fmaf(lvs[r], A, Bc));
-                                    *reinterpret_cast<uint16_t *>(col + pzs[r] * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
-                                }
-                            } else {
-                                or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
-                            }
-                        } else {
-                            // any other k: one pass at run time
-                            int r = __popc(bits) - 1;
-                            while (bits) {
+                            for (int r = KO - 1; r >= 0; --r) {
                                 const int pz = 31 - __clz(bits);
                                 bits ^= 1u << pz;
-                                const uint32_t nib = ((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu;
-                                --r;
+                                pzs[r] = (uint32_t)pz;
+                                lvs[r] = s_lut[((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu];
                                 const uint32_t row = (uint32_t)pz * (uint32_t)TS;
-                                const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
-                                const float cf = (float)((cb >> fsh) & 3u);
-                                const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
-                                *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
+                                cbs[r] = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
                             }
+#pragma unroll
+                            for (int r = KO - 1; r >= 0; --r) {
+                                const float cf = (float)((cbs[r] >> fsh) & 3u);
+                                const float X = fmaf(cf, -sc, fmaf(lvs[r], A, Bc));
+                                *reinterpret_cast<uint16_t *>(col + pzs[r] * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
+                            }
+                        } else {
+                            or_status(p.status, OMMX_ST_BAD_GROUP);   // bitmask and value stream disagree
+                        }
+                    } else {
+                        // any other k: one pass at run time
+                        int r = __popc(bits) - 1;
+                        while (bits) {
+                            const int pz = 31 - __clz(bits);
+                            bits ^= 1u << pz;
+                            const uint32_t nib = ((r < 8 ? stream : stream_hi) >> (4 * (r & 7))) & 0xFu;
+                            --r;
+                            const uint32_t row = (uint32_t)pz * (uint32_t)TS;
+                            const uint32_t cb = k_hi[row + (k_lo ^ (((row + k_hi_rel) >> 3) & p.swz))];
+                            const float cf = (float)((cb >> fsh) & 3u);
+                            const float X = fmaf(cf, -sc, fmaf(s_lut[nib], A, Bc));
+                            *reinterpret_cast<uint16_t *>(col + pz * DT_STRIDE) = (uint16_t)f16_bits_of_bf16_rounded(X);
                         }
                     }
                 }
-                if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tfull + 8 * unit);
             }
+            if (clamped_any) or_status(p.status, OMMX_ST_SCALE_RANGE);
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            if (lane == 0) mbar_arrive(bar_tfull + 8 * unit);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        return true;
+    };
+
+    // ---- roles; each branch starts by resizing its warpgroups' register budget and never rejoins ----
+    if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
+    bool producer_alive = true;
+    if (warp == PRODUCER_WARP) {
+        // =========================== producer warp ===========================
+        for (int it = 1; it < n_iters; ++it) {
+            // the first NS fills find their slots fresh
+            if (it >= NS && !mbar_wait(bar_empty + 8 * ring_slot(it, NS), ring_phase(it, NS) ^ 1, wait_limit)) {
+                if (lane == 0) { or_status(p.status, OMMX_ST_TIMEOUT); atomicExch(s_abort, 1); }
+                producer_alive = false;
+                break;
+            }
+            issue_stage(it);
+        }
+        // With every stage on its way this warp has nothing left to do, while the 15 decode warps share 16 items per
+        // iteration: it joins them below for the very last item, so that the last iteration's 16 halves are built side
+        // by side.
+    }
+
+    // =========================== decode + MMA warps ===========================
+    // MMA warp w owns unit w = (group-in-stage, kv head) and its softmax state.  The decode warps are
+    // stateless: work item number n goes to decode warp n % NDW, except the last one (the producer's).
+    if (warp >= NCW) {
+        // =========================== decode warps (and the producer, once it is done) ===========================
+        const int dw = warp - NCW;
+        const bool is_producer = warp == PRODUCER_WARP;
+        if (!is_producer) {
+            if (dw < NCW) {           // the first to touch tile dw clears it once (unused rows stay zero)
+                uint8_t *t0p = s_tiles + dw * DT_BYTES;
+                for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(t0p)[i] = 0u;
+            }
+            // every tile is cleared before any half of it is written; the producer learns of it without being waited for
+            asm volatile("bar.sync 1, %0;" ::"n"(NDW * 32) : "memory");
+            asm volatile("bar.arrive 2, %0;" ::"n"((NDW + 1) * 32) : "memory");
+        } else {
+            asm volatile("bar.sync 2, %0;" ::"n"((NDW + 1) * 32) : "memory");
+        }
+        const int n_first = is_producer ? n_items - 1 : dw;
+        const int n_end = is_producer ? (producer_alive ? n_items : 0) : n_items - 1;
+        for (int n = n_first; n < n_end; n += NDW)
+            if (!decode_item(n)) break;
         __syncthreads();
         __syncthreads();
         return;
@@ -690,48 +742,26 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     // channels (32j + 16wi + i, + 8), the pair a code word yields in one AND.  QD: plain bf16(q*sm_scale) for
     // the delta MMAs, whose tile columns are channels in natural order.
     uint32_t QS[16], QD[16];
-    {
-        const __nv_bfloat16 *qrow = p.q + (int64_t)b * p.q_sb + (int64_t)(h * p.gqa + (head_ok ? g : 0)) * p.q_sh;
-        // this lane's 32 channels for QS are contiguous: four 16-byte loads when the row allows it
-        uint32_t qw[16];
-        if ((reinterpret_cast<uintptr_t>(qrow) & 15u) == 0) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const uint4 t = reinterpret_cast<const uint4 *>(qrow + 32 * j)[v];
-                qw[4 * v] = t.x; qw[4 * v + 1] = t.y; qw[4 * v + 2] = t.z; qw[4 * v + 3] = t.w;
-            }
-        } else {
-#pragma unroll
-            for (int v = 0; v < 16; ++v) {
-                const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qrow + 32 * j);
-                qw[v] = (uint32_t)q16[2 * v] | ((uint32_t)q16[2 * v + 1] << 16);
-            }
+    for (int r = 0; r < 16; ++r) {
+        const int wi = r >> 3, i = r & 7;
+        const int e0 = 16 * wi + i, e1 = e0 + 8;                  // channel 32j + e0 / + e1
+        const float f = 1.f / (float)(1 << (2 * code_slot(i)));
+        float lo = 0.f, hi = 0.f;
+        if (head_ok) {
+            lo = bf16_round_f32(bf16_bits_to_f32((q_s[e0 >> 1] >> (16 * (e0 & 1))) & 0xFFFFu) * p.sm_scale) * f;
+            hi = bf16_round_f32(bf16_bits_to_f32((q_s[e1 >> 1] >> (16 * (e1 & 1))) & 0xFFFFu) * p.sm_scale) * f;
         }
+        QS[r] = pack_f16x2(lo, hi);
+    }
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int wi = r >> 3, i = r & 7;
-            const int e0 = 16 * wi + i, e1 = e0 + 8;                  // channel 32j + e0 / + e1
-            const float f = 1.f / (float)(1 << (2 * code_slot(i)));
-            float lo = 0.f, hi = 0.f;
-            if (head_ok) {
-                lo = bf16_round_f32(bf16_bits_to_f32((qw[e0 >> 1] >> (16 * (e0 & 1))) & 0xFFFFu) * p.sm_scale) * f;
-                hi = bf16_round_f32(bf16_bits_to_f32((qw[e1 >> 1] >> (16 * (e1 & 1))) & 0xFFFFu) * p.sm_scale) * f;
-            }
-            QS[r] = pack_f16x2(lo, hi);
+    for (int r = 0; r < 16; ++r) {
+        float lo = 0.f, hi = 0.f;
+        if (head_ok) {
+            lo = bf16_round_f32(bf16_bits_to_f32(q_d[r] & 0xFFFFu) * p.sm_scale);
+            hi = bf16_round_f32(bf16_bits_to_f32(q_d[r] >> 16) * p.sm_scale);
         }
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const uint16_t *q16 = reinterpret_cast<const uint16_t *>(qrow + 16 * q + 8 * half + 2 * j);
-                float lo = 0.f, hi = 0.f;
-                if (head_ok) {
-                    lo = bf16_round_f32(bf16_bits_to_f32(q16[0]) * p.sm_scale);
-                    hi = bf16_round_f32(bf16_bits_to_f32(q16[1]) * p.sm_scale);
-                }
-                QD[2 * q + half] = pack_f16x2(lo, hi);
-            }
-        }
+        QD[r] = pack_f16x2(lo, hi);
     }
     // per-lane fragment addresses inside the sidecar tile
     const uint32_t a_delta = tile_s + ((lane & 7) + 8 * ((lane >> 3) & 1)) * DT_STRIDE + 16 * (lane >> 4);
