@@ -352,6 +352,11 @@ def merge_attention_states(o_parts, lse_parts, *, valid_lens=None, out=None, lse
     res = torch.empty(R, D, dtype=torch.float32, device=o_parts.device)
     if lse_out is None:
         lse_out = torch.empty(R, dtype=torch.float32, device=o_parts.device)
+    elif (lse_out.dtype != torch.float32 or lse_out.device != o_parts.device or not lse_out.is_contiguous()
+          or int(lse_out.numel()) != R):
+        raise ValueError(f"lse_out must be a contiguous float32 tensor of {R} entries on {o_parts.device}")
+    if out is not None and (tuple(out.shape) != (R, D) or out.device != o_parts.device):
+        raise ValueError(f"out must be [R={R}, D={D}] on {o_parts.device}; got {tuple(out.shape)} on {out.device}")
     valid = None
     if valid_lens is not None:
         valid = valid_lens.to(device=o_parts.device, dtype=torch.int32).contiguous()

@@ -35,16 +35,24 @@ namespace ommx {
 
 constexpr int HD = 128;                 // head_dim this build serves
 constexpr int NCW = 8;                  // (group, head) units in flight per CTA, one MMA warp each
-constexpr int NDW = 15;                 // decode warps (stateless sidecar builders, items dealt round-robin)
-constexpr int PRODUCER_WARP = NCW + NDW;  // warp 23 streams the planes
-constexpr int S1_THREADS = (NCW + NDW + 1) * 32;
+// Two warp layouts.  Narrow (4 or 8 local kv heads: 14 copies per ring stage): 15 decode warps + 1 producer warp, which
+// also builds the last tile half once its copies are out.  Wide (1 or 2 local kv heads: a stage is 8 or 4 groups, 112 or
+// 56 small copies): 16 decode warps + 4 producer warps, because one warp issues a bulk copy only every ~60 cycles and
+// the issues of different warps overlap (112 copies: 6400 cycles from one warp, 2000 from four).
+template <bool WIDE> struct WarpLayout {
+    static constexpr int NDW = WIDE ? 16 : 15;            // decode warps (stateless sidecar builders, items dealt round-robin)
+    static constexpr int NPW = WIDE ? 4 : 1;              // producer warps
+    static constexpr int PRODUCER_WARP = NCW + NDW;       // the first of them
+    static constexpr int THREADS = (NCW + NDW + NPW) * 32;
+};
 // Register budget per role (setmaxnreg, warpgroup granularity).  Only what the CTA was launched with
 // can be moved around: 768 threads x 80 = 61440 = 256*128 (MMA) + 512*56 (decode + producer).  The
 // launch refuses to run if the compiled kernel holds fewer registers than the roles ask for, because
 // setmaxnreg.inc would then wait forever.
 #define OMMX_REGS_MMA "128"
 #define OMMX_REGS_DECODE "56"
-constexpr int REGS_MMA = 128, REGS_DECODE = 56;
+#define OMMX_REGS_PRODUCER "24"
+constexpr int REGS_MMA = 128, REGS_DECODE = 56, REGS_PRODUCER = 24;
 constexpr int MAX_STAGES = 4;           // ring depth (3 when the planes of a stage are large)
 constexpr int DT_STRIDE = 272;          // bytes per sidecar-tile row (256 data + 16 pad)
 constexpr int ROW_ZP = 32;              // q.zp partial sums, fp32: [channel half][8 query heads of the kv head]
@@ -239,8 +247,10 @@ __device__ __forceinline__ uint32_t ring_phase(int it, int ns) { return (uint32_
 //                              + vz^T[group][token] . P[token][head]
 // The power-of-two factors, zero-points and deltas of a unit are laid out for these fragments by the
 // decode warps (the sidecar tile), so the MMA warps multiply and accumulate and do little else.
-template <int KOUT>
-__global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __grid_constant__ S1Params p) {
+template <int KOUT, bool WIDE>
+__global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_kernel(const __grid_constant__ S1Params p) {
+    constexpr int NDW = WarpLayout<WIDE>::NDW, NPW = WarpLayout<WIDE>::NPW, PRODUCER_WARP = WarpLayout<WIDE>::PRODUCER_WARP;
+    constexpr int S1_THREADS = WarpLayout<WIDE>::THREADS;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // swizzle atoms are 1 KB: align the ring by hand (the launch adds 1 KB of slack)
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -402,23 +412,28 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     // ---- one stage of the ring: announce its bytes, issue its copies (producer warp) ----
     uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
     const int whole_groups = ntok / 32;
+    const int pw = warp - PRODUCER_WARP;                            // producer warp index (meaningful for those warps only)
     auto issue_stage = [&](int it) __attribute__((always_inline)) {
         const int s = ring_slot(it, NS);
         const int lg0 = it * GS;
-        uint32_t total = full_total;
-        if (lg0 + GS > whole_groups) {                              // last stage: fewer groups or a partial group
-            uint32_t mine = 0;
-            for (int c = lane; c < ncopies; c += 32) {
-                const CopyDesc d = s_desc[c];
-                const int lg = lg0 + (d.gi & 0xFF);
-                if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) mine += d.unit;
+        if (pw == 0) {                                              // the first producer warp announces the stage's bytes
+            uint32_t total = full_total;
+            if (lg0 + GS > whole_groups) {                          // last stage: fewer groups or a partial group
+                uint32_t mine = 0;
+                for (int c = lane; c < ncopies; c += 32) {
+                    const CopyDesc d = s_desc[c];
+                    const int lg = lg0 + (d.gi & 0xFF);
+                    if (d.unit && lg < ngroups && 32 * lg + d.tok0 < ntok) mine += d.unit;
+                }
+                total = __reduce_add_sync(0xFFFFFFFFu, mine);
             }
-            total = __reduce_add_sync(0xFFFFFFFFu, mine);
+            if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
+            __syncwarp();
         }
-        if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * s, total);
-        __syncwarp();
+        // (A copy of another producer warp may land before the announcement: the phase cannot complete without the
+        // announcing arrival, and the transaction count may run negative meanwhile.)
         const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
-        for (int c = lane; c < ncopies; c += 32) {
+        for (int c = lane * NPW + pw; c < ncopies; c += 32 * NPW) {
             const CopyDesc d = s_desc[c];
             const int lg = lg0 + (d.gi & 0xFF);
             const int kind = d.gi >> 8;
@@ -430,7 +445,7 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
         }
     };
     // The first ring fill is on every CTA's critical path: it goes out before the register budgets are resized.
-    if (warp == PRODUCER_WARP) {
+    if (warp >= PRODUCER_WARP) {
         for (int c = lane; c < ncopies; c += 32) full_total += s_desc[c].unit;
         full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
         issue_stage(0);
@@ -685,10 +700,15 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
     };
 
     // ---- roles; each branch starts by resizing its warpgroups' register budget and never rejoins ----
-    if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
+    if constexpr (WIDE) {
+        if (warp >= PRODUCER_WARP) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_PRODUCER ";");
+        else if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
+    } else {
+        if (warp >= NCW) asm volatile("setmaxnreg.dec.sync.aligned.u32 " OMMX_REGS_DECODE ";");
+    }
     bool producer_alive = true;
-    if (warp == PRODUCER_WARP) {
-        // =========================== producer warp ===========================
+    if (warp >= PRODUCER_WARP) {
+        // =========================== producer warp(s) ===========================
         for (int it = 1; it < n_iters; ++it) {
             // the first NS fills find their slots fresh
             if (it >= NS && !mbar_wait(bar_empty + 8 * ring_slot(it, NS), ring_phase(it, NS) ^ 1, wait_limit)) {
@@ -698,31 +718,38 @@ __global__ void __launch_bounds__(S1_THREADS, 1) decode_stage1_kernel(const __gr
             }
             issue_stage(it);
         }
-        // With every stage on its way this warp has nothing left to do, while the 15 decode warps share 16 items per
-        // iteration: it joins them below for the very last item, so that the last iteration's 16 halves are built side
-        // by side.
+        if constexpr (WIDE) {
+            // fall through to the two CTA-wide barriers of the epilogue
+            __syncthreads();
+            __syncthreads();
+            return;
+        }
+        // Narrow layout: with every stage on its way this warp has nothing left to do, while the 15 decode warps share
+        // 16 items per iteration: it joins them below for the very last item, so that the last iteration's 16 halves are
+        // built side by side.
     }
 
     // =========================== decode + MMA warps ===========================
     // MMA warp w owns unit w = (group-in-stage, kv head) and its softmax state.  The decode warps are
-    // stateless: work item number n goes to decode warp n % NDW, except the last one (the producer's).
+    // stateless: work item number n goes to decode warp n % NDW (narrow layout: except the last one, the producer's).
     if (warp >= NCW) {
-        // =========================== decode warps (and the producer, once it is done) ===========================
+        // =========================== decode warps (narrow layout: and the producer, once it is done) ===========================
         const int dw = warp - NCW;
-        const bool is_producer = warp == PRODUCER_WARP;
+        const bool is_producer = !WIDE && warp == PRODUCER_WARP;
         if (!is_producer) {
             if (dw < NCW) {           // the first to touch tile dw clears it once (unused rows stay zero)
                 uint8_t *t0p = s_tiles + dw * DT_BYTES;
                 for (int i = lane; i < DT_BYTES / 4; i += 32) reinterpret_cast<uint32_t *>(t0p)[i] = 0u;
             }
-            // every tile is cleared before any half of it is written; the producer learns of it without being waited for
+            // every tile is cleared before any half of it is written; the narrow layout's producer learns of it without
+            // being waited for
             asm volatile("bar.sync 1, %0;" ::"n"(NDW * 32) : "memory");
-            asm volatile("bar.arrive 2, %0;" ::"n"((NDW + 1) * 32) : "memory");
+            if constexpr (!WIDE) asm volatile("bar.arrive 2, %0;" ::"n"((NDW + 1) * 32) : "memory");
         } else {
             asm volatile("bar.sync 2, %0;" ::"n"((NDW + 1) * 32) : "memory");
         }
         const int n_first = is_producer ? n_items - 1 : dw;
-        const int n_end = is_producer ? (producer_alive ? n_items : 0) : n_items - 1;
+        const int n_end = WIDE ? n_items : (is_producer ? (producer_alive ? n_items : 0) : n_items - 1);
         for (int n = n_first; n < n_end; n += NDW)
             if (!decode_item(n)) break;
         __syncthreads();
@@ -1420,8 +1447,9 @@ static int current_device(int *dev) {
     return 0;
 }
 
-template <int KOUT>
-static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st) {
+template <int KOUT, bool WIDE>
+static int launch_s1_layout(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st) {
+    using L = WarpLayout<WIDE>;
     // function attributes belong to (kernel instantiation, device): one entry per device ordinal
     static std::atomic<size_t> attr_smem[MAX_DEVICES];
     static std::atomic<int> regs_state[MAX_DEVICES];   // 0 unknown, 1 enough, 2 too few
@@ -1430,19 +1458,27 @@ static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st)
     int regs_ok = regs_state[dev].load(std::memory_order_acquire);
     if (regs_ok == 0) {
         cudaFuncAttributes fa;
-        OMMX_CUDA_TRY(cudaFuncGetAttributes(&fa, decode_stage1_kernel<KOUT>));
-        regs_ok = fa.numRegs * S1_THREADS >= NCW * 32 * REGS_MMA + (S1_THREADS - NCW * 32) * REGS_DECODE ? 1 : 2;
+        OMMX_CUDA_TRY(cudaFuncGetAttributes(&fa, decode_stage1_kernel<KOUT, WIDE>));
+        // setmaxnreg.inc must find the registers the other roles gave back
+        const int need = NCW * 32 * REGS_MMA + (WIDE ? L::NDW * 32 * REGS_DECODE + L::NPW * 32 * REGS_PRODUCER
+                                                     : (L::THREADS - NCW * 32) * REGS_DECODE);
+        regs_ok = fa.numRegs * L::THREADS >= need ? 1 : 2;
         regs_state[dev].store(regs_ok, std::memory_order_release);
     }
     if (regs_ok != 1) return fail(OMMX_E_CUDA, "stage 1 was compiled with fewer registers than its warp roles need");
     if (smem > attr_smem[dev].load(std::memory_order_acquire)) {
-        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel<KOUT>,
+        OMMX_CUDA_TRY(cudaFuncSetAttribute(decode_stage1_kernel<KOUT, WIDE>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_smem[dev].store(smem, std::memory_order_release);
     }
-    OMMX_CUDA_TRY(launch_overlapping_previous(decode_stage1_kernel<KOUT>, grid, S1_THREADS, smem, st, p));
+    OMMX_CUDA_TRY(launch_overlapping_previous(decode_stage1_kernel<KOUT, WIDE>, grid, L::THREADS, smem, st, p));
     count_launch();
     return 0;
+}
+// one or two local kv heads: many small copies per ring stage, the wide layout's four producer warps issue them
+template <int KOUT>
+static int launch_s1(const S1Params &p, dim3 grid, size_t smem, cudaStream_t st) {
+    return p.H <= 2 ? launch_s1_layout<KOUT, true>(p, grid, smem, st) : launch_s1_layout<KOUT, false>(p, grid, smem, st);
 }
 
 }  // namespace ommx
