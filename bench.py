@@ -424,9 +424,12 @@ def run_ours(args, rank, world, local_rank):
     lib = _lib.load()
     triton_ref = TritonReference() if (rank == 0 and not args.no_triton) else None
 
-    peer = None
+    peer, peer_note = None, None
     if world > 1 and args.gather == "peer":
-        peer = sharding.PeerHeadGather(world, rank, max(2, LAYERS), 1, hq, D, device)
+        try:
+            peer = sharding.PeerHeadGather(world, rank, max(2, LAYERS), 1, hq, D, device)
+        except RuntimeError as exc:                                # every rank raises together: all fall back together
+            peer_note = f"peer-mapped exchange unavailable ({exc}); NCCL all-gather used"
 
     def step_full():
         for i in range(LAYERS):
@@ -560,6 +563,7 @@ def run_ours(args, rank, world, local_rank):
     ms_e2e = reduce_max(sum(e2e_graph_times) / len(e2e_graph_times))
 
     gather_check = None
+    used_peer = peer is not None
     if peer is not None:
         # the exchanged rows against an NCCL all-gather of the same outputs, once, outside any timed region
         for i in range(LAYERS):
@@ -606,7 +610,7 @@ def run_ours(args, rank, world, local_rank):
                    "collective": ("none" if world == 1 else
                                   "stage 2 stores its [1, Hq/N, D] f32 rows into every rank's buffer (peer-mapped memory over NVLink, "
                                   "one arrival count per rank, bounded wait); nccl_allgather_us is the NCCL all-gather of the same rows timed alone"
-                                  if peer is not None else "one NCCL all-gather of [1, Hq/N, D] f32 per layer inside the step")},
+                                  if used_peer else "one NCCL all-gather of [1, Hq/N, D] f32 per layer inside the step")},
         "hbm_gbs": results["bytes_layer"] / (results["ms_step"] / LAYERS) / 1e6,
         "tokens_per_s": 1.0 / (results["ms_step"] * 1e-3),
         "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
@@ -626,7 +630,7 @@ def run_ours(args, rank, world, local_rank):
                         "per layer, one copy of all outputs back; the whole step replayed from a CUDA graph; "
                         "eager_value is the same step launched from Python"},
         "gpu_launches": results["launches_step"] * args.steps,
-        "gather_check": gather_check,
+        "gather_check": gather_check if peer_note is None else peer_note,
         "contexts": per_ctx,
         "triton_reference": None if triton_ref is None else {"available": triton_ref.fn is not None, "note": triton_ref.why,
                                                              "seconds_spent": round(triton_ref.spent, 1)},

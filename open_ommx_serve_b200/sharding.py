@@ -108,11 +108,16 @@ class PeerHeadGather:
         self.bytes = buffers * self.buf_words * 8
         self._own = C.c_void_p()
         handle = (C.c_uint8 * 64)()
+        # Every step that can fail on one rank alone is followed by a vote, so that all ranks raise together instead
+        # of one leaving the others inside a collective.
         with torch.cuda.device(self.device):
-            _lib.check(lib.ommx_b200_peer_alloc(self.bytes, C.byref(self._own), handle), "ommx_b200_peer_alloc")
+            rc = lib.ommx_b200_peer_alloc(self.bytes, C.byref(self._own), handle)
+        why = "" if rc == 0 else _lib.last_error()
+        self._vote(rc == 0, "ommx_b200_peer_alloc: " + why, group)
         handles = [None] * world
         dist.all_gather_object(handles, bytes(handle), group=group)
         self._bases, self._opened = [], []
+        ok, why = True, ""
         for r in range(world):
             if r == rank:
                 self._bases.append(int(self._own.value))
@@ -120,9 +125,13 @@ class PeerHeadGather:
             ptr = C.c_void_p()
             h = (C.c_uint8 * 64).from_buffer_copy(handles[r])
             with torch.cuda.device(self.device):
-                _lib.check(lib.ommx_b200_peer_open(h, C.byref(ptr)), "ommx_b200_peer_open")
+                rc = lib.ommx_b200_peer_open(h, C.byref(ptr))
+            if rc != 0:
+                ok, why = False, _lib.last_error()
+                break
             self._bases.append(int(ptr.value))
             self._opened.append(int(ptr.value))
+        self._vote(ok, "ommx_b200_peer_open: " + why, group)
         # device-side pointer table recv[buffer][r]; results and the two state words are plain local tensors
         self._recv = torch.tensor([[b + i * self.buf_words * 8 for b in self._bases] for i in range(buffers)],
                                   dtype=torch.int64).to(self.device)
@@ -137,6 +146,23 @@ class PeerHeadGather:
             g.state = self._state.data_ptr()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                                 # every rank has mapped every buffer
+
+    def _vote(self, ok: bool, what: str, group):
+        """All ranks learn whether any of them failed; on failure each releases what it holds and raises."""
+        import torch.distributed as dist
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 1:
+            return
+        with torch.cuda.device(self.device):
+            for p in getattr(self, "_opened", []):
+                self._lib.ommx_b200_peer_close(p)
+            self._opened = []
+            if self._own.value:
+                self._lib.ommx_b200_peer_free(self._own)
+                self._own = C.c_void_p()
+        raise RuntimeError("PeerHeadGather: peer memory could not be set up on every rank"
+                           + ("" if ok else f" (this rank: {what})"))
 
     def plan(self, i: int) -> _GatherPlan:
         return _GatherPlan(self, i % self.buffers)
