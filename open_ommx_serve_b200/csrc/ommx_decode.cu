@@ -1110,36 +1110,54 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
     const int nsplit = per > 0 ? min(p.S, (seq + per - 1) / per) : 0;    // splits s with s*per < seq
     const float *base = p.al + (int64_t)b * p.al_sb + (int64_t)hq * p.al_sh;
 
+    constexpr int PRE_T = 5, PRE_S = 10;                                 // rows / splits per warp held in registers
     // ---- bf16 residual rows: logits of this q head (independent of stage 1) ----
+    // The K rows of this warp (rows warp, warp+16, ...) are requested together, before the query is in shared memory:
+    // this part runs after stage 1 whenever stage 1 fills every SM, so each round trip saved is a round trip per layer.
     if (tail > 0) {
+        const __nv_bfloat16 *kt = p.k_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
+        uint2 kpre[PRE_T];
+#pragma unroll
+        for (int k = 0; k < PRE_T; ++k) {
+            const int r = warp + k * S2_WARPS;
+            kpre[k] = make_uint2(0u, 0u);
+            if (r < tail) kpre[k] = *reinterpret_cast<const uint2 *>(kt + (int64_t)r * p.t_st + 4 * lane);
+        }
         if (tid < D) s_q[tid] = __bfloat162float(p.q[(int64_t)b * p.q_sb + (int64_t)hq * p.q_sh + tid]);
         __syncthreads();
-        const __nv_bfloat16 *kt = p.k_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
-        for (int r = warp; r < tail; r += S2_WARPS) {
-            const uint2 kv = *reinterpret_cast<const uint2 *>(kt + (int64_t)r * p.t_st + 4 * lane);
-            float d = s_q[4 * lane] * bf16_bits_to_f32(kv.x & 0xFFFFu) + s_q[4 * lane + 1] * bf16_bits_to_f32(kv.x >> 16)
-                    + s_q[4 * lane + 2] * bf16_bits_to_f32(kv.y & 0xFFFFu) + s_q[4 * lane + 3] * bf16_bits_to_f32(kv.y >> 16);
+        const float q0 = s_q[4 * lane], q1 = s_q[4 * lane + 1], q2 = s_q[4 * lane + 2], q3 = s_q[4 * lane + 3];
+        auto logit_of = [&](const uint2 kv) {
+            float d = q0 * bf16_bits_to_f32(kv.x & 0xFFFFu) + q1 * bf16_bits_to_f32(kv.x >> 16)
+                    + q2 * bf16_bits_to_f32(kv.y & 0xFFFFu) + q3 * bf16_bits_to_f32(kv.y >> 16);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
-            if (lane == 0) {
-                float x = d * p.sm_scale;
-                if (p.logit_cap > 0.f) x = p.logit_cap * tanhf(x / p.logit_cap);
-                s_logit[r] = x;
+            float x = d * p.sm_scale;
+            if (p.logit_cap > 0.f) x = p.logit_cap * tanhf(x / p.logit_cap);
+            return x;
+        };
+#pragma unroll
+        for (int k = 0; k < PRE_T; ++k) {
+            const int r = warp + k * S2_WARPS;
+            if (r < tail) {                                              // warp-uniform
+                const float x = logit_of(kpre[k]);
+                if (lane == 0) s_logit[r] = x;
             }
         }
+        for (int r = warp + PRE_T * S2_WARPS; r < tail; r += S2_WARPS) {
+            const float x = logit_of(*reinterpret_cast<const uint2 *>(kt + (int64_t)r * p.t_st + 4 * lane));
+            if (lane == 0) s_logit[r] = x;
+        }
     }
-    // residual V rows of this warp (rows warp, warp+16, ...), fetched now: they do not depend on stage 1
+    // residual V rows of this warp (rows warp, warp+16, ...), requested before the wait below: they do not depend on stage 1
     const __nv_bfloat16 *vt = p.v_tail + (int64_t)b * p.t_sb + (int64_t)kvh * p.t_sh;
-    constexpr int PRE_T = 5, PRE_S = 10;                                 // rows / splits per warp held in registers
-    float vpre[PRE_T][4];
+    uint32_t vpre[PRE_T][4];                                             // raw bf16 bits: turned into floats where they are used
 #pragma unroll
     for (int k = 0; k < PRE_T; ++k) {
         const int r = warp + k * S2_WARPS;
-        vpre[k][0] = vpre[k][1] = vpre[k][2] = vpre[k][3] = 0.f;
+        vpre[k][0] = vpre[k][1] = vpre[k][2] = vpre[k][3] = 0u;
         if (r < tail) {
-            const __nv_bfloat16 *row = vt + (int64_t)r * p.t_st;
-            vpre[k][0] = __bfloat162float(row[lane]); vpre[k][1] = __bfloat162float(row[lane + 32]);
-            vpre[k][2] = __bfloat162float(row[lane + 64]); vpre[k][3] = __bfloat162float(row[lane + 96]);
+            const uint16_t *row = reinterpret_cast<const uint16_t *>(vt + (int64_t)r * p.t_st);
+            vpre[k][0] = row[lane]; vpre[k][1] = row[lane + 32]; vpre[k][2] = row[lane + 64]; vpre[k][3] = row[lane + 96];
         }
     }
     // ---- everything below reads what stage 1 wrote: wait for that grid (no-op without a
@@ -1209,7 +1227,8 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
             const int r = warp + k * S2_WARPS;
             if (r < tail) {
                 const float w = s_logit[r];
-                a0 += w * vpre[k][0]; a1 += w * vpre[k][1]; a2 += w * vpre[k][2]; a3 += w * vpre[k][3];
+                a0 += w * bf16_bits_to_f32(vpre[k][0]); a1 += w * bf16_bits_to_f32(vpre[k][1]);
+                a2 += w * bf16_bits_to_f32(vpre[k][2]); a3 += w * bf16_bits_to_f32(vpre[k][3]);
             }
         }
 #pragma unroll 4
