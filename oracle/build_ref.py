@@ -30,6 +30,8 @@ import tempfile
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BASELINE_REF = os.path.join(ROOT, "baseline", "_ref")
 ORACLE_REF = os.path.join(ROOT, "oracle", "_ref")
+# where a reference checkout is looked for when none is named: OMMX_REFERENCE_CHECKOUT, else "reference" beside this repository
+DEFAULT_CHECKOUT = os.environ.get("OMMX_REFERENCE_CHECKOUT") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def have_triton_reference() -> bool:
@@ -40,9 +42,10 @@ def have_fakequant_reference() -> bool:
     return os.path.isfile(os.path.join(ORACLE_REF, "ommx_fakequant", "quant_function.py"))
 
 
-def build_ref(checkout: str = "/root/reference", force: bool = False) -> dict:
+def build_ref(checkout: str = "", force: bool = False) -> dict:
     """Install / copy the reference pieces; returns {'triton': bool, 'fakequant': bool, 'log': str}."""
     log = []
+    checkout = checkout or DEFAULT_CHECKOUT
     pkg_src = os.path.join(checkout, "ommx_gpu_serve")
     if os.path.isdir(pkg_src) and (force or not have_triton_reference()):
         with tempfile.TemporaryDirectory() as tmp:
@@ -76,6 +79,6 @@ def build_ref(checkout: str = "/root/reference", force: bool = False) -> dict:
 
 
 if __name__ == "__main__":
-    out = build_ref(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv)
+    out = build_ref(next((a for a in sys.argv[1:] if not a.startswith("--")), ""), force="--force" in sys.argv)
     print(out["log"])
     print({k: v for k, v in out.items() if k != "log"})
