@@ -58,8 +58,7 @@ __host__ __device__ inline int fp4_encode_tbl(float m, const uint32_t *th) {
 #pragma unroll
     for (int i = 0; i < 7; ++i) idx += (a >= th[i]) ? 1 : 0;
     int sign = (m < 0.0f) ? 1 : 0;
-    int ex = (idx >= 2) + (idx >= 4) + (idx >= 6);
-    return (sign << 3) | (ex << 1) | (idx & 1);
+    return (sign << 3) | idx;          // idx = exp * 2 + mant: the level's rank among the eight magnitudes is its code
 }
 
 // ---- device-side bf16 helpers -----------------------------------------------------------------

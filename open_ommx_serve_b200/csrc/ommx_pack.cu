@@ -397,12 +397,21 @@ __global__ void __launch_bounds__(PACK_WARPS * 32) pack_k_lane_kernel(PackKParam
     const float inv = __uint_as_float((uint32_t)(by_mul ? 127 - e : 127) << 23);
     uint32_t cw0 = 0, cw1 = 0;                // this channel's codes, token t at bits 2t
     if (__all_sync(0xFFFFFFFFu, by_mul)) {    // the usual case, without a division in sight
+        // clamp, then add 1.5 * 2^23: the code sits in the low bits of the sum's pattern 0x4B400000 + code.  The
+        // patterns are accumulated shifted as they are; what the constant part adds up to (mod 2^32) leaves once.
+        constexpr uint32_t MAGIC = 0x4B400000u;
+        uint32_t magic_sum = 0;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) magic_sum += MAGIC << (2 * t);
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
-            const uint32_t c = code_0_3(__fmul_rn(__fsub_rn(x[t], zp), inv));
-            if (t < 16) cw0 = c * (1u << (2 * t)) + cw0;
-            else cw1 = c * (1u << (2 * (t - 16))) + cw1;
+            const float c = fminf(fmaxf(__fmul_rn(__fsub_rn(x[t], zp), inv), 0.f), 3.f);       // NaN -> 0
+            const uint32_t bits = __float_as_uint(__fadd_rn(c, 12582912.f));
+            if (t < 16) cw0 = bits * (1u << (2 * t)) + cw0;
+            else cw1 = bits * (1u << (2 * (t - 16))) + cw1;
         }
+        cw0 -= magic_sum;
+        cw1 -= magic_sum;
     } else {
 #pragma unroll
         for (int t = 0; t < 32; ++t) {
