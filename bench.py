@@ -655,12 +655,21 @@ def workload_llama70b(args, device, world, flush, reduce_max, barrier, peak, gat
     stack = LayerStack(ctx, B, hkv, hq, device, seed=7, layers=layers)
     stack.set_context(ctx)
     gathered = torch.zeros(layers, world, B, hq, D, dtype=torch.float32, device=device) if world > 1 else None
+    peer = None
+    if world > 1 and args.gather == "peer":
+        try:
+            peer = sharding.PeerHeadGather(world, int(os.environ.get("RANK", "0")), layers, B, hq, D, device)
+        except RuntimeError:
+            peer = None                                               # every rank raises together: NCCL for all
 
     def step():
         for i in range(layers):
-            stack.decode_layer(i)
-            if world > 1:
-                sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
+            if peer is not None:
+                stack.decode_layer(i, head_gather=peer.plan(i))
+            else:
+                stack.decode_layer(i)
+                if world > 1:
+                    sharding.gather_head_outputs(stack.o[i], world, out=gathered[i])
 
     def step_s1():
         for i in range(layers):
@@ -677,11 +686,15 @@ def workload_llama70b(args, device, world, flush, reduce_max, barrier, peak, gat
     bytes_launch = B * p * hkv * unit_bytes(K_OUT)
     ach = bytes_launch / (ms1 / layers) / 1e6
     rec = {"config": {"workload": f"llama3.1-70b head geometry (64 q heads, 8 kv heads), batch {B}, ctx {ctx}, {layers}-layer stack "
-                                  f"standing for 80 layers, {hkv} kv head(s) per GPU", "splits": stack.splits},
+                                  f"standing for 80 layers, {hkv} kv head(s) per GPU", "splits": stack.splits,
+                      "collective": "none" if world == 1 else ("head outputs exchanged inside stage 2 (peer-mapped memory)"
+                                                                if peer is not None else "NCCL all-gather per layer")},
            "us_per_layer": ms * 1e3 / layers, "hbm_gbs": bytes_layer / (ms / layers) / 1e6,
            "tokens_per_s_80_layers": B / (ms / layers * 80 * 1e-3),
            "roofline": {"bound": "hbm", "kernel": "decode_stage1_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
                         "frac": ach / peak, "us_per_launch": ms1 * 1e3 / layers, "algorithmic_bytes_per_launch": bytes_launch}}
+    if peer is not None:
+        peer.close()
     del stack
     torch.cuda.empty_cache()
     return rec
