@@ -82,3 +82,19 @@ def test_package_fails_loudly_without_cuda_tensors():
     with pytest.raises(RuntimeError):
         ommx_pack_kv_canonical_block(torch.zeros(32, 1, 128), torch.zeros(32, 1, 128),
                                      outliers_per_vector=6, outlier_repr="bitmap", use_pow2=True)
+
+
+def test_auto_split_count_fills_whole_waves():
+    """The split count minimises (waves of CTAs over the SMs) x (groups per CTA + fixed cost): with 148 SMs (the
+    value used when no device is present) batch 8 takes 18 splits - 144 CTAs, one wave - not ceil(148 / 8) = 19."""
+    lib = _lib.load()
+    f = lib.ommx_b200_auto_num_kv_splits
+    assert f(65472, 1, 8) in (147, 148)
+    assert f(131008, 1, 8) in (147, 148)
+    assert f(32704, 8, 8) == 18
+    assert f(960, 1, 8) == 30                     # one group per CTA, no more splits than groups
+    assert f(0, 1, 8) == 1
+    for seq, b in ((65472, 2), (8000, 4), (32704, 32), (65472, 148)):
+        s = f(seq, b, 8)
+        assert 1 <= s <= max(1, (seq + 31) // 32)
+        assert s >= lib.ommx_b200_min_num_kv_splits(seq, 16)
