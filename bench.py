@@ -24,8 +24,10 @@ achieved HBM GB/s (packed-KV bytes / time) and the contexts 1K..128K are reporte
              the reference's CPU path - its own fake quantizer (oracle/_ref, unmodified) on K and V,
              then dense attention - timed on the host cores on ONE layer of the same context
 
-With N > 1 (torchrun) the 8 KV heads are sharded over the ranks, there is no collective inside
-attention, and one NCCL all-gather per layer reassembles the head outputs (timed inside the step).
+With N > 1 (torchrun) the 8 KV heads are sharded over the ranks and nothing is exchanged during
+attention; the head outputs of a layer are exchanged inside stage 2 (--gather peer, the default:
+every rank's stage 2 stores its rows into all ranks' buffers through peer-mapped memory) or by one
+NCCL all-gather per layer (--gather nccl); both are timed on every run, inside the step or beside it.
 Synthetic data throughout: seeded N(0,1) K/V with 4 K channels per head scaled x12.
 """
 from __future__ import annotations
