@@ -413,10 +413,11 @@ __global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_ke
     uint32_t full_total = 0;                                        // bytes of a stage with GS whole groups
     const int whole_groups = ntok / 32;
     const int pw = warp - PRODUCER_WARP;                            // producer warp index (meaningful for those warps only)
-    auto issue_stage = [&](int it) __attribute__((always_inline)) {
+    // `nshare` warps split the copies of a stage, this one taking share `share`; the `lead` among them announces the bytes
+    auto issue_stage = [&](int it, int nshare, int share, bool lead) __attribute__((always_inline)) {
         const int s = ring_slot(it, NS);
         const int lg0 = it * GS;
-        if (pw == 0) {                                              // the first producer warp announces the stage's bytes
+        if (lead) {
             uint32_t total = full_total;
             if (lg0 + GS > whole_groups) {                          // last stage: fewer groups or a partial group
                 uint32_t mine = 0;
@@ -433,7 +434,7 @@ __global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_ke
         // (A copy of another producer warp may land before the announcement: the phase cannot complete without the
         // announcing arrival, and the transaction count may run negative meanwhile.)
         const uint32_t sbase = smem_u32(s_stage + (size_t)s * p.stage_bytes);
-        for (int c = lane * NPW + pw; c < ncopies; c += 32 * NPW) {
+        for (int c = lane * nshare + share; c < ncopies; c += 32 * nshare) {
             const CopyDesc d = s_desc[c];
             const int lg = lg0 + (d.gi & 0xFF);
             const int kind = d.gi >> 8;
@@ -445,10 +446,16 @@ __global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_ke
         }
     };
     // The first ring fill is on every CTA's critical path: it goes out before the register budgets are resized.
+    // A warp issues a bulk copy only about every 60 cycles and different warps overlap, so in the narrow layout the three
+    // decode warps of the producer's warpgroup (idle until the data lands) take a quarter of the first fill each.
     if (warp >= PRODUCER_WARP) {
         for (int c = lane; c < ncopies; c += 32) full_total += s_desc[c].unit;
         full_total = __reduce_add_sync(0xFFFFFFFFu, full_total);
-        issue_stage(0);
+    }
+    if constexpr (WIDE) {
+        if (warp >= PRODUCER_WARP) issue_stage(0, NPW, pw, pw == 0);
+    } else {
+        if (warp >= PRODUCER_WARP - 3) issue_stage(0, 4, warp - (PRODUCER_WARP - 3), warp == PRODUCER_WARP);
     }
 
     // ---- one work item of the decode role: half hf of the sidecar tile of (iteration it, unit) ----
@@ -716,7 +723,7 @@ __global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_ke
                 producer_alive = false;
                 break;
             }
-            issue_stage(it);
+            issue_stage(it, NPW, pw, pw == 0);
         }
         if constexpr (WIDE) {
             // fall through to the two CTA-wide barriers of the epilogue
