@@ -726,9 +726,8 @@ __global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_ke
             issue_stage(it, NPW, pw, pw == 0);
         }
         if constexpr (WIDE) {
-            // fall through to the two CTA-wide barriers of the epilogue
-            __syncthreads();
-            __syncthreads();
+            // with several groups per stage, the epilogue's two CTA-wide barriers
+            if (GS > 1) { __syncthreads(); __syncthreads(); }
             return;
         }
         // Narrow layout: with every stage on its way this warp has nothing left to do, while the 15 decode warps share
@@ -759,8 +758,7 @@ __global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_ke
         const int n_end = WIDE ? n_items : (is_producer ? (producer_alive ? n_items : 0) : n_items - 1);
         for (int n = n_first; n < n_end; n += NDW)
             if (!decode_item(n)) break;
-        __syncthreads();
-        __syncthreads();
+        if (GS > 1) { __syncthreads(); __syncthreads(); }          // the epilogue's two CTA-wide barriers (see there)
         return;
     }
 
@@ -1020,16 +1018,19 @@ __global__ void __launch_bounds__(WarpLayout<WIDE>::THREADS, 1) decode_stage1_ke
         }
     }
 
-    // Wait for every warp (and the producer) before the ring memory is reused as scratch.
-    __syncthreads();
+    // Several groups per stage (fewer than 8 local kv heads): the warps that share a head merge through the ring memory,
+    // once every warp (and the producer) is done with it.  With 8 heads every warp owns its head and writes straight away.
     float *scratch = reinterpret_cast<float *>(s_stage);             // [NCW][32 lanes][36]
-    if (GS > 1 && gsel > 0) {
-        float *my = scratch + ((size_t)unit * 32 + lane) * 36;
-        my[0] = m_run[0]; my[1] = m_run[1]; my[2] = l_tot[0]; my[3] = l_tot[1];
+    if (GS > 1) {
+        __syncthreads();
+        if (gsel > 0) {
+            float *my = scratch + ((size_t)unit * 32 + lane) * 36;
+            my[0] = m_run[0]; my[1] = m_run[1]; my[2] = l_tot[0]; my[3] = l_tot[1];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { my[4 + i] = outv[0][i]; my[20 + i] = outv[1][i]; }
+            for (int i = 0; i < 16; ++i) { my[4 + i] = outv[0][i]; my[20 + i] = outv[1][i]; }
+        }
+        __syncthreads();
     }
-    __syncthreads();
     if (gsel == 0) {
         for (int o = 1; o < GS; ++o) {
             const float *ot = scratch + ((size_t)(o * H + h) * 32 + lane) * 36;
