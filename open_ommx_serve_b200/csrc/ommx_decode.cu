@@ -1279,18 +1279,35 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
         }
         const uint64_t *mine = p.g_recv[p.g_rank];
         const long long t_end = clock64() + WAIT_LIMIT_CYCLES;
-        for (int idx = tid; idx < (p.g_world - 1) * D; idx += S2_THREADS) {
-            int r = idx / D;
-            const int e = idx - r * D;
-            r += (r >= p.g_rank) ? 1 : 0;                              // skip the own slot
-            const uint64_t *src = mine + (int64_t)r * slot + row + e;
-            uint64_t word = 0;
-            for (uint32_t i = 1;; ++i) {
-                asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
-                if ((uint32_t)(word >> 32) == epoch) break;
+        const int n_words = (p.g_world - 1) * D;
+        // two words per thread and round, both requested before either is looked at
+        for (int idx = tid; idx < n_words; idx += 2 * S2_THREADS) {
+            const uint64_t *src[2];
+            float *dst[2];
+            bool pending[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int i = idx + u * S2_THREADS;
+                pending[u] = i < n_words;
+                int r = pending[u] ? i / D : 0;
+                const int e = pending[u] ? i - r * D : 0;
+                r += (r >= p.g_rank) ? 1 : 0;                          // skip the own slot
+                src[u] = mine + (int64_t)r * slot + row + e;
+                dst[u] = p.g_out + (int64_t)r * slot + row + e;
+            }
+            for (uint32_t i = 1; pending[0] || pending[1]; ++i) {
+                uint64_t word[2] = {0, 0};
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                    if (pending[u]) asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word[u]) : "l"(src[u]) : "memory");
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                    if (pending[u] && (uint32_t)(word[u] >> 32) == epoch) {
+                        *dst[u] = __uint_as_float((uint32_t)word[u]);
+                        pending[u] = false;
+                    }
                 if ((i & 63u) == 0 && clock64() > t_end) { or_status(p.status, OMMX_ST_TIMEOUT); break; }
             }
-            p.g_out[(int64_t)r * slot + row + e] = __uint_as_float((uint32_t)word);
         }
         // the call count moves on once every block has read it: each block reads it before it draws its ticket
         __syncthreads();

@@ -76,3 +76,49 @@ def test_stage2_peer_gather_two_ranks():
         assert p.exitcode == 0
     got = dict(q.get(timeout=5) for _ in range(2))
     assert got == {0: True, 1: True}
+
+
+def test_stage2_exchange_indexing_eight_ranks_on_one_gpu():
+    """Send and receive indexing of the exchange for 8 ranks, on one GPU: the seven "peers" are plain local buffers.
+    Their words are written into this rank's receive buffer beforehand with the call count the kernel will expect, so
+    nothing waits for another kernel; afterwards `out` must hold those values in the peers' slots and this rank's rows
+    in its own, and every peer buffer must hold this rank's rows as (value, call count) words in slot `rank`."""
+    import ctypes as C
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import Case
+    from open_ommx_serve_b200 import _lib
+    world, rank = 8, 3
+    case = Case([700, 300], H=1, Hq=4, seed=9)
+    B, hq, D = 2, 4, 128
+    dev = torch.device("cuda")
+    recv = [torch.zeros(world, B, hq, D, dtype=torch.int64, device=dev) for _ in range(world)]
+    gen = torch.Generator().manual_seed(3)
+    want = torch.randn(world, B, hq, D, generator=gen).to(dev)
+    words = (want.view(torch.int32).to(torch.int64) & 0xFFFFFFFF) | (1 << 32)          # call count 1
+    for r in range(world):
+        if r != rank:
+            recv[rank][r] = words[r]
+    recv_ptrs = torch.tensor([t.data_ptr() for t in recv], dtype=torch.int64, device=dev)
+    out = torch.zeros(world, B, hq, D, dtype=torch.float32, device=dev)
+    state = torch.zeros(2, dtype=torch.int32, device=dev)
+    g = _lib.HeadGather()
+    g.world, g.rank, g.recv, g.out, g.state = world, rank, recv_ptrs.data_ptr(), out.data_ptr(), state.data_ptr()
+
+    class Plan:
+        def check(self, batch, heads, head_dim, device):
+            assert (batch, heads, head_dim) == (B, hq, D)
+            return C.addressof(g)
+
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    o, _ = case.run(num_kv_splits=3, status=status, head_gather=Plan())
+    assert int(status.item()) == 0 and state.tolist() == [1, 0]
+    assert torch.equal(out[rank], o)
+    for r in range(world):
+        if r == rank:
+            continue
+        assert torch.equal(out[r], want[r]), f"slot {r} received"
+        sent = recv[r][rank]
+        assert torch.equal((sent >> 32), torch.ones_like(sent)), f"call count in peer {r}"
+        low = sent & 0xFFFFFFFF
+        bits = torch.where(low >= 2 ** 31, low - 2 ** 32, low).to(torch.int32)          # the low word as a signed pattern
+        assert torch.equal(bits.view(torch.float32), o), f"rows sent to peer {r}"
