@@ -1171,62 +1171,43 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
     // ---- everything below reads what stage 1 wrote: wait for that grid (no-op without a
     //      programmatic launch) ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // The split rows of this warp are requested together with the lse values, not after the weights are
+    // Every warp folds its own splits (warp, warp+16, ...) and its own residual rows into a private softmax state -
+    // maximum, sum of weights, weighted rows - with no exchange: the lse of a split is read by all lanes at once (one
+    // address), the residual logits of rows warp, warp+16, ... were written by this very warp.  The 16 states are
+    // merged once at the end.  The split rows are requested together with the lse values, not after the weights are
     // known: the kernel is a chain of global round trips and this takes one link out of it.
-    float spre[PRE_S][4];
+    float spre[PRE_S][4], lpre[PRE_S];
 #pragma unroll
     for (int k = 0; k < PRE_S; ++k) {
         const int s = warp + k * S2_WARPS;
         spre[k][0] = spre[k][1] = spre[k][2] = spre[k][3] = 0.f;
+        lpre[k] = -INFINITY;
         if (s < nsplit) {
             const float *row = base + (int64_t)s * p.al_ss;
             spre[k][0] = row[lane]; spre[k][1] = row[lane + 32]; spre[k][2] = row[lane + 64]; spre[k][3] = row[lane + 96];
+            lpre[k] = row[D];
         }
     }
-    float mloc = -INFINITY;
-    for (int s = tid; s < nsplit; s += S2_THREADS) {
-        const float l = base[(int64_t)s * p.al_ss + D];
-        s_w[s] = l;
-        mloc = fmaxf(mloc, l);
-    }
-    __syncthreads();
-    // ---- global max over split lse values and residual logits ----
-    for (int r = tid; r < tail; r += S2_THREADS) mloc = fmaxf(mloc, s_logit[r]);
+    __syncwarp();                                                        // s_logit rows of this warp (lane 0 wrote them)
+    float m_w = -INFINITY;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xFFFFFFFFu, mloc, o));
-    if (lane == 0) s_red[warp] = mloc;
-    __syncthreads();
-    float g_max = s_red[0];
-#pragma unroll
-    for (int w = 1; w < S2_WARPS; ++w) g_max = fmaxf(g_max, s_red[w]);
-    const float g_safe = (g_max == -INFINITY) ? 0.f : g_max;
-    __syncthreads();
-    // weights: splits enter with exp(lse_s - max), residual rows with exp(logit - max)
-    float wsum = 0.f;
-    for (int s = tid; s < nsplit; s += S2_THREADS) { const float w = __expf(s_w[s] - g_safe); s_w[s] = w; wsum += w; }
-    for (int r = tid; r < tail; r += S2_THREADS) { const float w = __expf(s_logit[r] - g_safe); s_logit[r] = w; wsum += w; }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xFFFFFFFFu, wsum, o);
-    if (lane == 0) s_red[warp] = wsum;
-    __syncthreads();
-    float den = 0.f;
-#pragma unroll
-    for (int w = 0; w < S2_WARPS; ++w) den += s_red[w];
-
-    // ---- weighted sum: warp w takes splits / rows w, w+16, ...; lane owns channels lane + 32*i ----
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int k = 0; k < PRE_S; ++k) m_w = fmaxf(m_w, lpre[k]);
+    for (int s = warp + PRE_S * S2_WARPS; s < nsplit; s += S2_WARPS) m_w = fmaxf(m_w, base[(int64_t)s * p.al_ss + D]);
+    for (int r = warp; r < tail; r += S2_WARPS) m_w = fmaxf(m_w, s_logit[r]);
+    const float m_safe = (m_w == -INFINITY) ? 0.f : m_w;
+    // weighted sum: lane owns channels lane + 32*i
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, den_w = 0.f;
 #pragma unroll
     for (int k = 0; k < PRE_S; ++k) {
-        const int s = warp + k * S2_WARPS;
-        if (s < nsplit) {
-            const float w = s_w[s];
-            a0 += w * spre[k][0]; a1 += w * spre[k][1]; a2 += w * spre[k][2]; a3 += w * spre[k][3];
-        }
+        const float w = __expf(lpre[k] - m_safe);                        // exp(-inf) = 0 for the slots past nsplit
+        den_w += w;
+        a0 += w * spre[k][0]; a1 += w * spre[k][1]; a2 += w * spre[k][2]; a3 += w * spre[k][3];
     }
 #pragma unroll 4
     for (int s = warp + PRE_S * S2_WARPS; s < nsplit; s += S2_WARPS) {
         const float *row = base + (int64_t)s * p.al_ss;
-        const float w = s_w[s];
+        const float w = __expf(row[D] - m_safe);
+        den_w += w;
         a0 += w * row[lane]; a1 += w * row[lane + 32]; a2 += w * row[lane + 64]; a3 += w * row[lane + 96];
     }
     if (tail > 0) {
@@ -1234,7 +1215,8 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
         for (int k = 0; k < PRE_T; ++k) {
             const int r = warp + k * S2_WARPS;
             if (r < tail) {
-                const float w = s_logit[r];
+                const float w = __expf(s_logit[r] - m_safe);
+                den_w += w;
                 a0 += w * bf16_bits_to_f32(vpre[k][0]); a1 += w * bf16_bits_to_f32(vpre[k][1]);
                 a2 += w * bf16_bits_to_f32(vpre[k][2]); a3 += w * bf16_bits_to_f32(vpre[k][3]);
             }
@@ -1242,19 +1224,30 @@ __global__ void __launch_bounds__(S2_THREADS) decode_stage2_kernel(const S2Param
 #pragma unroll 4
         for (int r = warp + PRE_T * S2_WARPS; r < tail; r += S2_WARPS) {
             const __nv_bfloat16 *row = vt + (int64_t)r * p.t_st;
-            const float w = s_logit[r];
+            const float w = __expf(s_logit[r] - m_safe);
+            den_w += w;
             a0 += w * __bfloat162float(row[lane]); a1 += w * __bfloat162float(row[lane + 32]);
             a2 += w * __bfloat162float(row[lane + 64]); a3 += w * __bfloat162float(row[lane + 96]);
         }
     }
     s_acc[warp][lane] = a0; s_acc[warp][lane + 32] = a1;
     s_acc[warp][lane + 64] = a2; s_acc[warp][lane + 96] = a3;
+    if (lane == 0) { s_red[warp] = m_w; s_w[warp] = den_w; }
     __syncthreads();
+    // ---- merge of the 16 states ----
     float out = 0.f;
     if (tid < D) {
-        float acc = 0.f;
+        float g_max = s_red[0];
 #pragma unroll
-        for (int w = 0; w < S2_WARPS; ++w) acc += s_acc[w][tid];
+        for (int w = 1; w < S2_WARPS; ++w) g_max = fmaxf(g_max, s_red[w]);
+        const float g_safe = (g_max == -INFINITY) ? 0.f : g_max;
+        float acc = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < S2_WARPS; ++w) {
+            const float e = __expf(s_red[w] - g_safe);                   // 0 for a warp that saw nothing
+            acc = fmaf(s_acc[w][tid], e, acc);
+            den = fmaf(s_w[w], e, den);
+        }
         out = acc / (den > 0.f ? den : 1.f);
         if (p.o_bf16) reinterpret_cast<__nv_bfloat16 *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = __float2bfloat16_rn(out);
         else reinterpret_cast<float *>(p.o)[(int64_t)b * p.o_sb + (int64_t)hq * p.o_sh + tid] = out;
